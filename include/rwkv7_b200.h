@@ -1,0 +1,233 @@
+/*
+ * rwkv7_b200.h — C ABI of the B200 (sm_100a) implementation of the rwkv-rs WKV7
+ * hot path: the fused WKV7 forward recurrence, the token-shift mixing kernels
+ * (mix6, addcmul, addcmul5, token_shift_diff) and the fused LM-head cross
+ * entropy.
+ *
+ * Every entry point replaces the body of one backend-extension trait function
+ * of the reference (paths inside the rwkv-rs repository are cited per function).
+ * Conventions shared by all entry points:
+ *
+ *  - Tensors are BORROWED: `data` is a device pointer owned by the caller, valid
+ *    until the work enqueued on `stream` has completed.  The library allocates
+ *    no tensor memory; outputs and workspaces are caller-allocated (the
+ *    reference allocates outputs with `empty_device` inside the op,
+ *    wkv7/forward.rs:368-375 — the Rust shim does that before calling in).
+ *  - Work is enqueued on `stream` and is asynchronous with respect to the host
+ *    (the reference enqueues on the CubeCL client's stream).  No entry point
+ *    synchronises the device, except rwkv7_read_device_status.
+ *  - The return value is a status code.  Non-zero codes 1..5 map 1:1 onto the
+ *    reference's `KernelInputsError` variants (kernels/check.rs:34-73) and
+ *    rwkv7_last_error_message() returns the same Display text the reference
+ *    would panic with; the reference's wrappers `check().unwrap()` and panic, a
+ *    Rust shim does `panic!("{}", rwkv7_last_error_message())` on non-zero.
+ *  - All tensors must be contiguous row-major (the reference asserts
+ *    `is_contiguous()`, wkv7/mod.rs:56-76).
+ *  - The library is re-entrant; it keeps no per-call global state apart from a
+ *    thread-local error message and a per-device status word.
+ */
+#ifndef RWKV7_B200_H_
+#define RWKV7_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKV7_MAX_DIMS 5
+#define RWKV7_ABI_VERSION 1
+
+/* Opaque CUDA stream handle (cudaStream_t); NULL is the legacy default stream. */
+typedef void *rwkv7_stream;
+
+typedef enum rwkv7_dtype {
+    RWKV7_F32 = 0,
+    RWKV7_BF16 = 1,
+    RWKV7_F16 = 2, /* recognised, not computed: returns RWKV7_ERR_UNSUPPORTED */
+    RWKV7_I32 = 3,
+    RWKV7_I64 = 4,
+    RWKV7_U32 = 5
+} rwkv7_dtype;
+
+typedef enum rwkv7_status {
+    RWKV7_OK = 0,
+    /* 1..5: KernelInputsError variants, kernels/check.rs:34-73 */
+    RWKV7_ERR_AXIS_MISMATCH = 1,
+    RWKV7_ERR_SHAPE_MISMATCH = 2,
+    RWKV7_ERR_DTYPE_MISMATCH = 3,
+    RWKV7_ERR_DEVICE_MISMATCH = 4,
+    RWKV7_ERR_EMPTY_AXIS = 5,
+    /* assertions of the reference's CubeBackend impl and io.rs */
+    RWKV7_ERR_NOT_CONTIGUOUS = 6, /* wkv7/mod.rs:56-76 */
+    RWKV7_ERR_BAD_CHUNK = 7,      /* wkv7/io.rs:187,198-201 (only chunk_len <= 0 here) */
+    /* conditions that have no counterpart in the reference */
+    RWKV7_ERR_UNSUPPORTED = 8,
+    RWKV7_ERR_NULL_POINTER = 9,
+    RWKV7_ERR_WORKSPACE_TOO_SMALL = 10,
+    RWKV7_ERR_CUDA = 11,
+    RWKV7_ERR_TIMEOUT = 12,    /* a bounded device-side wait expired */
+    RWKV7_ERR_BAD_INDEX = 13,  /* a device-side index (batch_ids, target) was out of range */
+    RWKV7_ERR_BAD_ARGUMENT = 14
+} rwkv7_status;
+
+/* Borrowed tensor view.  `stride` is in elements; `device` is the CUDA ordinal. */
+typedef struct rwkv7_tensor {
+    void *data;
+    int32_t dtype; /* rwkv7_dtype */
+    int32_t device;
+    int32_t ndim;
+    int32_t reserved;
+    int64_t shape[RWKV7_MAX_DIMS];
+    int64_t stride[RWKV7_MAX_DIMS];
+} rwkv7_tensor;
+
+/* Which kernel the WKV7 entry points dispatch to.  AUTO picks the decode sweep
+ * for short T, the chunked tensor-core kernel for N == 64 and long T, and the
+ * sequential kernel otherwise. */
+typedef enum rwkv7_wkv7_path {
+    RWKV7_WKV7_AUTO = 0,
+    RWKV7_WKV7_SEQUENTIAL = 1,
+    RWKV7_WKV7_CHUNKED = 2
+} rwkv7_wkv7_path;
+
+int rwkv7_abi_version(void);
+const char *rwkv7_status_string(int status);
+/* Thread-local text of the last non-zero status returned on this thread. */
+const char *rwkv7_last_error_message(void);
+/* Process-wide override of the WKV7 kernel choice (tests and benchmarks). */
+int rwkv7_set_wkv7_path(int path);
+int rwkv7_get_wkv7_path(void);
+/* Number of kernels this library has launched in this process (all devices,
+ * all threads).  Benchmarks read it before and after a timed region. */
+int64_t rwkv7_kernel_launch_count(void);
+
+/*
+ * Reads and clears the status word that kernels on `device` set instead of
+ * trapping (expired bounded wait, out-of-range index).  Synchronises `stream`.
+ * Returns RWKV7_OK, RWKV7_ERR_TIMEOUT or RWKV7_ERR_BAD_INDEX.
+ */
+int rwkv7_read_device_status(int device, rwkv7_stream stream);
+
+/* ------------------------------------------------------------------ WKV7 -- */
+/*
+ * Per (b,h), state S[i][j] (i value row, j key column), t = 0..T-1:
+ *   d_j = exp(-exp(w[b,t,h,j]));  sa_i = sum_j S[i][j] a[b,t,h,j];
+ *   S[i][j] = S[i][j] d_j + sa_i b[b,t,h,j] + v[b,t,h,i] k[b,t,h,j];
+ *   y[b,t,h,i] = sum_j S[i][j] r[b,t,h,j].
+ * r,w,k,v,a,b,y are [B,T,H,N] (receptance, weight_decay, replacement_key, value,
+ * removal_key_normalized, replacement), all F32 or all BF16; states are
+ * [B,H,N,N] F32.  Accumulation and the carried state are fp32.
+ *
+ * `chunk_len` is the reference's snapshot cadence (wkv7/io.rs:187); here it must
+ * only be positive, any T >= 1 is accepted (T == 1 is the decode step).
+ * `workspace` may be NULL when rwkv7_wkv7_workspace_bytes() returns 0.
+ */
+
+/* Scratch bytes the WKV7 entry points need for this shape (0 for the
+ * sequential and decode kernels). */
+size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype);
+
+/* Replaces Wkv7Backend::fused_wkv7_pretrain (wkv7/mod.rs:31, impl :55-79;
+ * host wkv7/forward.rs:348-435; kernel wkv7/kernel.rs:60-196): S0 = 0 -> y. */
+int rwkv7_fused_wkv7_pretrain(const rwkv7_tensor *receptance, const rwkv7_tensor *weight_decay,
+                              const rwkv7_tensor *replacement_key, const rwkv7_tensor *value,
+                              const rwkv7_tensor *removal_key_normalized,
+                              const rwkv7_tensor *replacement, int64_t chunk_len,
+                              rwkv7_tensor *output, void *workspace, size_t workspace_bytes,
+                              rwkv7_stream stream);
+
+/* Replaces Wkv7Backend::fused_wkv7_statetune (wkv7/mod.rs:34-35, impl :81-90;
+ * wkv7/forward.rs:205-223): S0 given -> y, final state dropped. */
+int rwkv7_fused_wkv7_statetune(const rwkv7_tensor *initial_state, const rwkv7_tensor *receptance,
+                               const rwkv7_tensor *weight_decay,
+                               const rwkv7_tensor *replacement_key, const rwkv7_tensor *value,
+                               const rwkv7_tensor *removal_key_normalized,
+                               const rwkv7_tensor *replacement, int64_t chunk_len,
+                               rwkv7_tensor *output, void *workspace, size_t workspace_bytes,
+                               rwkv7_stream stream);
+
+/* Replaces Wkv7Backend::fused_wkv7_statepass (wkv7/mod.rs:38-40, impl :92-101;
+ * wkv7/forward.rs:245-267,437-530; kernel wkv7/kernel.rs:198-364):
+ * S0 given -> (y, S_T).  `next_state` may alias `initial_state`. */
+int rwkv7_fused_wkv7_statepass(const rwkv7_tensor *initial_state, const rwkv7_tensor *receptance,
+                               const rwkv7_tensor *weight_decay,
+                               const rwkv7_tensor *replacement_key, const rwkv7_tensor *value,
+                               const rwkv7_tensor *removal_key_normalized,
+                               const rwkv7_tensor *replacement, int64_t chunk_len,
+                               rwkv7_tensor *output, rwkv7_tensor *next_state, void *workspace,
+                               size_t workspace_bytes, rwkv7_stream stream);
+
+/* ------------------------------------------------------------------ mix6 -- */
+/* Replaces Mix6Backend::fused_mix6 (mix6/mod.rs:25-28, impl :42-73; kernel
+ * mix6/kernel.rs:25-57): prev = x[b,t-1,:] (0 at t == 0);
+ * out_i = x + (prev - x) * scale_i for i in receptance, weight_decay, key,
+ * value, learning_rate, gate.  x and out_i are [B,T,C], scale_i [1,1,C]. */
+int rwkv7_fused_mix6(const rwkv7_tensor *embedded_context, const rwkv7_tensor *const scales[6],
+                     rwkv7_tensor *const outputs[6], rwkv7_stream stream);
+
+/* Same arithmetic into one stacked tensor [6,B,T,C] (the reference's
+ * mix6_stacked_forward_kernel, mix6/kernel.rs:64-98, used under autodiff). */
+int rwkv7_fused_mix6_stacked(const rwkv7_tensor *embedded_context,
+                             const rwkv7_tensor *const scales[6], rwkv7_tensor *stacked_output,
+                             rwkv7_stream stream);
+
+/* --------------------------------------------------------------- addcmul -- */
+/* Replaces AddcmulBackend::fused_addcmul (addcmul/mod.rs:27-35, impl :49-66;
+ * kernel addcmul/kernel.rs:4-20): out = base + diff * scale; base, diff, out
+ * [B,T,C], scale [1,1,C].  `output` may alias `base` (the reference writes in
+ * place when the buffer is uniquely owned, addcmul/forward.rs:547-598). */
+int rwkv7_fused_addcmul(const rwkv7_tensor *base, const rwkv7_tensor *diff,
+                        const rwkv7_tensor *scale, rwkv7_tensor *output, rwkv7_stream stream);
+
+/* Replaces AddcmulBackend::fused_addcmul5 (addcmul/mod.rs:27-35, impl :68-84;
+ * kernel addcmul/kernel.rs:42-65): five outputs sharing base and diff, scale
+ * order receptance, weight_decay, key, value, learning_rate. */
+int rwkv7_fused_addcmul5(const rwkv7_tensor *base, const rwkv7_tensor *diff,
+                         const rwkv7_tensor *const scales[5], rwkv7_tensor *const outputs[5],
+                         rwkv7_stream stream);
+
+/* ------------------------------------------------------ token_shift_diff -- */
+/* Replaces TokenShiftDiffBackend::fused_token_shift_diff
+ * (token_shift_diff/mod.rs:27-32, impl :42-63; kernel kernel.rs:16-45):
+ *   prev[b,0,:] = state[ids[b],:]; prev[b,t,:] = x[b,t-1,:]; diff = prev - x;
+ *   state[ids[b],:] = x[b,T-1,:]   (in place; other rows untouched; T == 0: no-op).
+ * x, diff [B,T,C]; state [S,C]; batch_ids [B] of I32, I64 or U32, values valid
+ * and unique.  An out-of-range id is skipped and reported through
+ * rwkv7_read_device_status (the reference does not check). */
+int rwkv7_fused_token_shift_diff(const rwkv7_tensor *embedded_context,
+                                 rwkv7_tensor *embedded_token_shift,
+                                 const rwkv7_tensor *batch_ids, rwkv7_tensor *token_shifted_diff,
+                                 rwkv7_stream stream);
+
+/* ------------------------------------------------------------ lm_head_ce -- */
+/*
+ * Fused LM-head cross entropy.  The reference only reserves the module
+ * (kernels/train/lm_head_l2wrap_ce/mod.rs is empty; config switch
+ * rwkv-config/src/raw/train.rs:59-60), so this entry point defines the
+ * operator: z = x W^T with x [R,C] and W [V_shard,C] (BF16, fp32 accumulate);
+ * per row the partial triple over this vocabulary shard
+ *   row_max = max_v z_v, row_sumexp = sum_v exp(z_v - row_max),
+ *   row_target = z[target - vocab_offset] if the target falls in the shard else 0.
+ * Logits are never written to memory.  targets [R] are I32 or I64; a negative
+ * target marks an ignored row.  L2Wrap is a backward-only regulariser and is the
+ * identity here.  partials is [R,3] F32 (max, sumexp, target logit).
+ */
+size_t rwkv7_lm_head_ce_workspace_bytes(int64_t R, int64_t C, int64_t V_shard);
+
+int rwkv7_fused_lm_head_ce_partial(const rwkv7_tensor *x, const rwkv7_tensor *weight_shard,
+                                   const rwkv7_tensor *targets, int64_t vocab_offset,
+                                   rwkv7_tensor *partials, void *workspace,
+                                   size_t workspace_bytes, rwkv7_stream stream);
+
+/* Combines `num_shards` partial tensors laid out [num_shards,R,3] into per-row
+ * lse [R] and loss [R] (F32): M = max_g m_g; lse = M + log sum_g s_g exp(m_g-M);
+ * loss = lse - sum_g target_g (0 for ignored rows). */
+int rwkv7_lm_head_ce_finalize(const rwkv7_tensor *partials_all, const rwkv7_tensor *targets,
+                              rwkv7_tensor *lse, rwkv7_tensor *loss, rwkv7_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKV7_B200_H_ */

@@ -1,0 +1,248 @@
+/*
+ * CPU oracle for the rwkv-rs WKV7 hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file restates, in plain C, the arithmetic of the reference's tensor-op
+ * definitions.  It is the checker for the CUDA kernels and the timed CPU
+ * baseline; it is never linked into, loaded by or called from the product
+ * library.
+ *
+ * PARITY UNPINNED: the reference ships no golden vectors, known-answer files or
+ * fixtures for these operators (its tests compare a custom kernel with a
+ * tensor-op path on unseeded random inputs), and the reference itself cannot be
+ * compiled where this oracle was written (no Rust toolchain, Burn/CubeCL not
+ * vendored).  The oracle is therefore pinned only by (1) a line-by-line reading
+ * of the cited reference functions, (2) an independent fp64 torch restatement of
+ * the same formulas, and (3) closed-form known answers; see tests/.
+ *
+ * Reference functions followed (paths inside the rwkv-rs repository):
+ *   wkv7      crates/rwkv-nn/src/kernels/train/time_mixer/wkv7/mod.rs:179-242
+ *             (wkv7_reference_with_state) cross-read with kernel.rs:60-196
+ *             (index order, f32 accumulation, decay = exp(-exp(w)) :55-58)
+ *   mix6      crates/rwkv-nn/src/kernels/train/time_mixer/mix6/mod.rs:111-156,
+ *             kernel.rs:25-57
+ *   addcmul   crates/rwkv-nn/src/kernels/template/addcmul/mod.rs:122-124,
+ *             addcmul5 :165-175, kernel.rs:4-65
+ *   token_shift_diff
+ *             crates/rwkv-nn/src/kernels/template/token_shift_diff/mod.rs:114-155,
+ *             :170-200, kernel.rs:16-45
+ *   lm_head_ce  no reference implementation exists (lm_head_l2wrap_ce/mod.rs is
+ *             empty); the specification is z = x W^T, lse = log sum exp z,
+ *             loss = lse - z[target].
+ *
+ * Layouts: row-major contiguous.  Sequence tensors [B,T,H,N] index
+ * ((b*T+t)*H+h)*N+n (kernel.rs:14-25); state [B,H,N,N] index
+ * ((b*H+h)*N+i)*N+j with i the value row and j the key column (kernel.rs:27-37).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ------------------------------------------------------------------ wkv7 -- */
+
+/*
+ * fp32 restatement with the accumulation order of the reference kernel
+ * (kernel.rs:82-195): per token, per state row i:
+ *   sa_i   = sum_j S[i][j] * a[j]             (S is S_{t-1}; j ascending, f32)
+ *   S[i][j]= S[i][j]*d[j] + sa_i*b[j] + v[i]*k[j]      with d = exp(-exp(w))
+ *   y[i]   = sum_j S[i][j] * r[j]             (S is S_t;     j ascending, f32)
+ * s0 may be NULL (zero initial state, wkv7_pretrain_reference mod.rs:153-165);
+ * s_out may be NULL (statetune drops the final state, forward.rs:522-526).
+ */
+void oracle_wkv7_f32(const float *r, const float *w, const float *k, const float *v,
+                     const float *a, const float *b, const float *s0, float *y,
+                     float *s_out, int64_t B, int64_t T, int64_t H, int64_t N) {
+    const int64_t BH = B * H;
+#pragma omp parallel
+    {
+        float *S = (float *)malloc(sizeof(float) * (size_t)(N * N));
+        float *d = (float *)malloc(sizeof(float) * (size_t)N);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t bh = 0; bh < BH; ++bh) {
+            const int64_t bi = bh / H, h = bh % H;
+            if (s0)
+                memcpy(S, s0 + bh * N * N, sizeof(float) * (size_t)(N * N));
+            else
+                memset(S, 0, sizeof(float) * (size_t)(N * N));
+            for (int64_t t = 0; t < T; ++t) {
+                const int64_t o = ((bi * T + t) * H + h) * N;
+                const float *rt = r + o, *wt = w + o, *kt = k + o, *vt = v + o,
+                            *at = a + o, *bt = b + o;
+                for (int64_t j = 0; j < N; ++j) d[j] = expf(-expf(wt[j]));
+                for (int64_t i = 0; i < N; ++i) {
+                    float *Si = S + i * N;
+                    float sa = 0.0f;
+                    for (int64_t j = 0; j < N; ++j) sa += Si[j] * at[j];
+                    const float vi = vt[i];
+                    float acc = 0.0f;
+                    for (int64_t j = 0; j < N; ++j) {
+                        const float u = Si[j] * d[j] + sa * bt[j] + vi * kt[j];
+                        Si[j] = u;
+                        acc += u * rt[j];
+                    }
+                    y[o + i] = acc;
+                }
+            }
+            if (s_out) memcpy(s_out + bh * N * N, S, sizeof(float) * (size_t)(N * N));
+        }
+        free(S);
+        free(d);
+    }
+}
+
+/*
+ * fp64 restatement of the same definition (mod.rs:179-242): inputs are the
+ * exact fp32 (or bf16-representable) values the kernel under test consumes, all
+ * arithmetic in double.  This is the parity target for the CUDA kernels.
+ */
+void oracle_wkv7_f64(const float *r, const float *w, const float *k, const float *v,
+                     const float *a, const float *b, const double *s0, double *y,
+                     double *s_out, int64_t B, int64_t T, int64_t H, int64_t N) {
+    const int64_t BH = B * H;
+#pragma omp parallel
+    {
+        double *S = (double *)malloc(sizeof(double) * (size_t)(N * N));
+        double *d = (double *)malloc(sizeof(double) * (size_t)N);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t bh = 0; bh < BH; ++bh) {
+            const int64_t bi = bh / H, h = bh % H;
+            if (s0)
+                memcpy(S, s0 + bh * N * N, sizeof(double) * (size_t)(N * N));
+            else
+                memset(S, 0, sizeof(double) * (size_t)(N * N));
+            for (int64_t t = 0; t < T; ++t) {
+                const int64_t o = ((bi * T + t) * H + h) * N;
+                for (int64_t j = 0; j < N; ++j) d[j] = exp(-exp((double)w[o + j]));
+                for (int64_t i = 0; i < N; ++i) {
+                    double *Si = S + i * N;
+                    double sa = 0.0;
+                    for (int64_t j = 0; j < N; ++j) sa += Si[j] * (double)a[o + j];
+                    const double vi = (double)v[o + i];
+                    double acc = 0.0;
+                    for (int64_t j = 0; j < N; ++j) {
+                        const double u =
+                            Si[j] * d[j] + sa * (double)b[o + j] + vi * (double)k[o + j];
+                        Si[j] = u;
+                        acc += u * (double)r[o + j];
+                    }
+                    y[o + i] = acc;
+                }
+            }
+            if (s_out) memcpy(s_out + bh * N * N, S, sizeof(double) * (size_t)(N * N));
+        }
+        free(S);
+        free(d);
+    }
+}
+
+/* ------------------------------------------------------------------ mix6 -- */
+
+/*
+ * mix6 (mix6/mod.rs:111-156): prev = x[b,t-1,c] (zero at t == 0, per batch row),
+ * out_i = x + (prev - x) * mu_i[c] for the six branches, in the order
+ * receptance, weight_decay, key, value, learning_rate, gate.  out is laid out
+ * [6][B][T][C].  Computed in double from float inputs.
+ */
+void oracle_mix6_f64(const float *x, const float *const mu[6], double *out, int64_t B,
+                     int64_t T, int64_t C) {
+    const int64_t n = B * T * C;
+#pragma omp parallel for schedule(static)
+    for (int64_t bt = 0; bt < B * T; ++bt) {
+        const int64_t t = bt % T;
+        for (int64_t c = 0; c < C; ++c) {
+            const int64_t e = bt * C + c;
+            const double cur = (double)x[e];
+            const double prev = (t == 0) ? 0.0 : (double)x[e - C];
+            const double diff = prev - cur;
+            for (int s = 0; s < 6; ++s) out[(int64_t)s * n + e] = cur + diff * (double)mu[s][c];
+        }
+    }
+}
+
+/* --------------------------------------------------------------- addcmul -- */
+
+/* addcmul (addcmul/mod.rs:122-124): out = base + diff * scale[c].  nscale = 1
+ * or 5 (addcmul5, mod.rs:165-175); out is [nscale][B*T][C]. */
+void oracle_addcmul_f64(const float *base, const float *diff, const float *const *scale,
+                        int nscale, double *out, int64_t BT, int64_t C) {
+    const int64_t n = BT * C;
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < BT; ++row)
+        for (int64_t c = 0; c < C; ++c) {
+            const int64_t e = row * C + c;
+            for (int s = 0; s < nscale; ++s)
+                out[(int64_t)s * n + e] = (double)base[e] + (double)diff[e] * (double)scale[s][c];
+        }
+}
+
+/* ------------------------------------------------------ token_shift_diff -- */
+
+/*
+ * token_shift_diff (token_shift_diff/mod.rs:65-81,114-155,170-200; kernel.rs:30-44):
+ *   prev[b,0,:] = state[ids[b],:]; prev[b,t,:] = x[b,t-1,:];
+ *   diff = prev - x;  state[ids[b],:] = x[b,T-1,:]; other rows unchanged;
+ *   T == 0 leaves everything unchanged.  The subtraction of two floats is exact
+ *   in double, so rounding the result to float gives the float result.
+ * state is updated in place, as the reference kernel does.
+ */
+void oracle_token_shift_diff_f32(const float *x, float *state, const int64_t *ids,
+                                 float *diff, int64_t B, int64_t T, int64_t C) {
+    if (T == 0) return;
+    for (int64_t bi = 0; bi < B; ++bi) {
+        float *srow = state + ids[bi] * C;
+        for (int64_t t = 0; t < T; ++t) {
+            const float *cur = x + (bi * T + t) * C;
+            const float *prev = (t == 0) ? srow : cur - C;
+            float *o = diff + (bi * T + t) * C;
+            for (int64_t c = 0; c < C; ++c) o[c] = prev[c] - cur[c];
+        }
+        memcpy(srow, x + (bi * T + T - 1) * C, sizeof(float) * (size_t)C);
+    }
+}
+
+/* ------------------------------------------------------------ lm_head_ce -- */
+
+/*
+ * LM-head cross entropy (own specification; the reference file is empty):
+ *   z[row][v] = sum_c x[row][c] * W[v][c]        (double accumulation)
+ *   lse[row]  = log sum_v exp(z[row][v])
+ *   loss[row] = lse[row] - z[row][target[row]]   (target < 0 -> loss 0, ignored)
+ * W covers vocabulary rows [0, V).
+ */
+void oracle_lm_head_ce_f64(const float *x, const float *W, const int64_t *target,
+                           double *lse, double *loss, int64_t R, int64_t C, int64_t V) {
+#pragma omp parallel
+    {
+        double *z = (double *)malloc(sizeof(double) * (size_t)V);
+#pragma omp for schedule(static)
+        for (int64_t row = 0; row < R; ++row) {
+            const float *xr = x + row * C;
+            double m = -INFINITY;
+            for (int64_t vv = 0; vv < V; ++vv) {
+                const float *wr = W + vv * C;
+                double acc = 0.0;
+                for (int64_t c = 0; c < C; ++c) acc += (double)xr[c] * (double)wr[c];
+                z[vv] = acc;
+                if (acc > m) m = acc;
+            }
+            double s = 0.0;
+            for (int64_t vv = 0; vv < V; ++vv) s += exp(z[vv] - m);
+            lse[row] = m + log(s);
+            const int64_t tg = target[row];
+            loss[row] = (tg >= 0 && tg < V) ? lse[row] - z[tg] : 0.0;
+        }
+        free(z);
+    }
+}

@@ -1,0 +1,401 @@
+"""Host-side mirror of the rwkv-rs WKV7 operator interface over the C ABI.
+
+The directory name carries a hyphen, so the package is loaded under the module
+name ``rwkv_rs_stable_b200`` (``__graft_entry__.load_package()`` does that with
+:mod:`importlib`).
+
+Function and argument names follow the reference's public wrappers
+(``crates/rwkv-nn/src/kernels/train/time_mixer/wkv7/mod.rs:105-150``,
+``.../mix6/mod.rs:159-177``, ``crates/rwkv-nn/src/kernels/template/addcmul/mod.rs:100-114``,
+``.../token_shift_diff/mod.rs:82-168``).  Like the reference's wrappers, which
+``check().unwrap()`` and panic, every function raises :class:`KernelInputsError`
+with the reference's message text when the input contract is violated.
+
+All arithmetic happens in ``librwkv7_b200.so`` (hand-written sm_100a CUDA, see
+``csrc/``); torch only owns device memory and streams here.  There is no CPU
+fallback: importing works without a GPU, calling an operator does not.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librwkv7_b200.so")
+
+MAX_DIMS = 5
+F32, BF16, F16, I32, I64, U32 = 0, 1, 2, 3, 4, 5
+WKV7_AUTO, WKV7_SEQUENTIAL, WKV7_CHUNKED = 0, 1, 2
+
+_DTYPES = {
+    torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16,
+    torch.int32: I32, torch.int64: I64,
+}
+
+STATUS_NAMES = {
+    0: "Ok", 1: "AxisMismatch", 2: "ShapeMismatch", 3: "DTypeMismatch", 4: "DeviceMismatch",
+    5: "EmptyAxis", 6: "NotContiguous", 7: "BadChunk", 8: "Unsupported", 9: "NullPointer",
+    10: "WorkspaceTooSmall", 11: "CudaError", 12: "Timeout", 13: "BadIndex", 14: "BadArgument",
+}
+
+
+class KernelInputsError(RuntimeError):
+    """Raised where the reference panics (``kernels/check.rs:34-73``)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+        self.kind = STATUS_NAMES.get(status, "Unknown")
+
+
+class Tensor(ctypes.Structure):
+    """``rwkv7_tensor`` of ``include/rwkv7_b200.h``."""
+
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("dtype", ctypes.c_int32),
+        ("device", ctypes.c_int32),
+        ("ndim", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("shape", ctypes.c_int64 * MAX_DIMS),
+        ("stride", ctypes.c_int64 * MAX_DIMS),
+    ]
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the C-ABI library; fails loudly when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}`. "
+                "There is no fallback path.")
+        L = ctypes.CDLL(LIB_PATH)
+        L.rwkv7_status_string.restype = ctypes.c_char_p
+        L.rwkv7_last_error_message.restype = ctypes.c_char_p
+        L.rwkv7_wkv7_workspace_bytes.restype = ctypes.c_size_t
+        L.rwkv7_wkv7_workspace_bytes.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_int32]
+        L.rwkv7_kernel_launch_count.restype = ctypes.c_int64
+        L.rwkv7_lm_head_ce_workspace_bytes.restype = ctypes.c_size_t
+        L.rwkv7_lm_head_ce_workspace_bytes.argtypes = [ctypes.c_int64] * 3
+        _lib = L
+    return _lib
+
+
+def describe(t: Optional[torch.Tensor], device: Optional[int] = None) -> Optional[Tensor]:
+    """Builds the borrowed descriptor of a torch tensor (no copy)."""
+    if t is None:
+        return None
+    d = Tensor()
+    d.data = t.data_ptr() if t.numel() else None
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"unsupported torch dtype {t.dtype}")
+    d.dtype = _DTYPES[t.dtype]
+    d.device = t.device.index if t.device.type == "cuda" else (-1 if device is None else device)
+    d.ndim = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def _ref(d: Optional[Tensor]):
+    return None if d is None else ctypes.byref(d)
+
+
+def _stream(t: torch.Tensor) -> ctypes.c_void_p:
+    if t.device.type != "cuda":
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise KernelInputsError(status, lib().rwkv7_last_error_message().decode())
+
+
+def set_wkv7_path(path: int) -> None:
+    _check(lib().rwkv7_set_wkv7_path(ctypes.c_int(path)))
+
+
+def get_wkv7_path() -> int:
+    return int(lib().rwkv7_get_wkv7_path())
+
+
+def kernel_launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib().rwkv7_kernel_launch_count())
+
+
+def read_device_status(device: int = 0) -> int:
+    """Reads and clears the device status word; returns the status code."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    return int(lib().rwkv7_read_device_status(ctypes.c_int(device), stream))
+
+
+# ---------------------------------------------------------------------- WKV7 --
+
+
+@dataclass
+class Wkv7PretrainForwardInputs:
+    """``wkv7/io.rs:20-66``: six ``[batch, context_len, num_heads, head_size]`` tensors."""
+
+    receptance: torch.Tensor
+    weight_decay: torch.Tensor
+    replacement_key: torch.Tensor
+    value: torch.Tensor
+    removal_key_normalized: torch.Tensor
+    replacement: torch.Tensor
+    chunk_len: int = 16
+
+    def six(self):
+        return (self.receptance, self.weight_decay, self.replacement_key, self.value,
+                self.removal_key_normalized, self.replacement)
+
+    def check(self, reference_contract: bool = True) -> None:
+        """The reference's assertions that precede its shape checks
+        (``wkv7/io.rs:187,198-201``): ``chunk_len == 16`` and
+        ``context_len % chunk_len == 0``.  The C ABI itself accepts any ``T >= 1``."""
+        if not reference_contract:
+            return
+        if self.chunk_len != 16:
+            raise KernelInputsError(7, "wkv7 currently supports chunk_len=16")
+        if self.receptance.dim() == 4 and self.receptance.shape[1] % self.chunk_len != 0:
+            raise KernelInputsError(7, "context_len must be a multiple of chunk_len")
+
+
+@dataclass
+class Wkv7StatepassForwardOutput:
+    """``wkv7/io.rs:157-164``."""
+
+    output: torch.Tensor
+    next_state: torch.Tensor
+
+
+def _wkv7_workspace(r: torch.Tensor) -> tuple[Optional[torch.Tensor], int]:
+    if r.dim() != 4:
+        return None, 0
+    B, T, H, N = r.shape
+    n = int(lib().rwkv7_wkv7_workspace_bytes(B, T, H, N, _DTYPES.get(r.dtype, 0)))
+    if n == 0:
+        return None, 0
+    return torch.empty(n, dtype=torch.uint8, device=r.device), n
+
+
+def _wkv7_call(inputs: Wkv7PretrainForwardInputs, initial_state, want_state: bool,
+               next_state: Optional[torch.Tensor] = None, output: Optional[torch.Tensor] = None,
+               workspace: Optional[torch.Tensor] = None):
+    r = inputs.receptance
+    six = [describe(t) for t in inputs.six()]
+    y = torch.empty_like(r) if output is None else output
+    yd = describe(y)
+    if workspace is None:
+        workspace, ws_bytes = _wkv7_workspace(r)
+    else:
+        ws_bytes = workspace.numel() * workspace.element_size()
+    ws_ptr = ctypes.c_void_p(workspace.data_ptr() if workspace is not None else 0)
+    stream = _stream(r)
+    L = lib()
+    cl = ctypes.c_int64(inputs.chunk_len)
+    if initial_state is None:
+        st = L.rwkv7_fused_wkv7_pretrain(*[_ref(d) for d in six], cl, _ref(yd), ws_ptr,
+                                         ctypes.c_size_t(ws_bytes), stream)
+        _check(st)
+        return y, None
+    s0d = describe(initial_state)
+    if not want_state:
+        st = L.rwkv7_fused_wkv7_statetune(_ref(s0d), *[_ref(d) for d in six], cl, _ref(yd), ws_ptr,
+                                          ctypes.c_size_t(ws_bytes), stream)
+        _check(st)
+        return y, None
+    s_out = torch.empty_like(initial_state) if next_state is None else next_state
+    sod = describe(s_out)
+    st = L.rwkv7_fused_wkv7_statepass(_ref(s0d), *[_ref(d) for d in six], cl, _ref(yd), _ref(sod),
+                                      ws_ptr, ctypes.c_size_t(ws_bytes), stream)
+    _check(st)
+    return y, s_out
+
+
+def wkv7_pretrain_custom(inputs: Wkv7PretrainForwardInputs, *, reference_contract: bool = True,
+                         output=None, workspace=None) -> torch.Tensor:
+    """``wkv7_pretrain_custom`` (``wkv7/mod.rs:105-110``): zero initial state -> y."""
+    inputs.check(reference_contract)
+    return _wkv7_call(inputs, None, False, output=output, workspace=workspace)[0]
+
+
+def wkv7_statetune_custom(initial_state: torch.Tensor, sequence: Wkv7PretrainForwardInputs, *,
+                          reference_contract: bool = True, output=None, workspace=None) -> torch.Tensor:
+    """``wkv7_statetune_custom`` (``wkv7/mod.rs:113-120``): given state -> y."""
+    sequence.check(reference_contract)
+    return _wkv7_call(sequence, initial_state, False, output=output, workspace=workspace)[0]
+
+
+def wkv7_statepass_custom(initial_state: torch.Tensor, sequence: Wkv7PretrainForwardInputs, *,
+                          reference_contract: bool = True, next_state=None, output=None,
+                          workspace=None) -> Wkv7StatepassForwardOutput:
+    """``wkv7_statepass_custom`` (``wkv7/mod.rs:123-133``): given state -> (y, S_T).
+    With ``reference_contract=False`` any ``T >= 1`` is accepted (``T == 1`` is decode);
+    ``next_state`` may be the same tensor as ``initial_state`` (in-place update)."""
+    sequence.check(reference_contract)
+    y, s = _wkv7_call(sequence, initial_state, True, next_state=next_state, output=output,
+                      workspace=workspace)
+    return Wkv7StatepassForwardOutput(output=y, next_state=s)
+
+
+class Wkv7StatepassCall:
+    """A statepass call with its descriptors built once, for callers that repeat the
+    same call on fixed buffers (decode loops, benchmarks): ``call()`` is one FFI
+    call with no per-call allocation.  The tensors must stay alive and unmoved."""
+
+    def __init__(self, initial_state, sequence: Wkv7PretrainForwardInputs, output, next_state,
+                 workspace=None):
+        self._keep = (initial_state, sequence, output, next_state, workspace)
+        self._desc = [describe(initial_state)] + [describe(t) for t in sequence.six()]
+        self._y, self._s = describe(output), describe(next_state)
+        self._args = [_ref(d) for d in self._desc] + [ctypes.c_int64(sequence.chunk_len), _ref(self._y),
+                                                      _ref(self._s)]
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        self._args += [ctypes.c_void_p(workspace.data_ptr() if workspace is not None else 0),
+                       ctypes.c_size_t(ws_bytes)]
+        self._device = sequence.receptance.device
+        self._fn = lib().rwkv7_fused_wkv7_statepass
+
+    def __call__(self):
+        st = self._fn(*self._args, ctypes.c_void_p(torch.cuda.current_stream(self._device).cuda_stream))
+        if st:
+            _check(st)
+
+
+wkv7_pretrain = wkv7_pretrain_custom
+wkv7_statetune = wkv7_statetune_custom
+wkv7_statepass = wkv7_statepass_custom
+
+# ---------------------------------------------------------------------- mix6 --
+
+MIX6_BRANCHES = ("receptance_input", "weight_decay_input", "key_input", "value_input",
+                 "learning_rate_input", "gate_input")
+
+
+def _ptr_array(descs: Sequence[Optional[Tensor]]):
+    arr = (ctypes.POINTER(Tensor) * len(descs))()
+    for i, d in enumerate(descs):
+        arr[i] = ctypes.pointer(d) if d is not None else None
+    return arr
+
+
+def mix6_custom(embedded_context: torch.Tensor, receptance_scale, weight_decay_scale, key_scale,
+                value_scale, learning_rate_scale, gate_scale, *, stacked: bool = False):
+    """``mix6_custom`` (``mix6/mod.rs:76-108``).  Returns a dict of the six
+    ``[B,T,C]`` outputs, or one ``[6,B,T,C]`` tensor when ``stacked``."""
+    x = embedded_context
+    scales = [receptance_scale, weight_decay_scale, key_scale, value_scale, learning_rate_scale, gate_scale]
+    xd = describe(x)
+    sd = [describe(s) for s in scales]
+    L = lib()
+    if stacked:
+        out = torch.empty((6,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+        od = describe(out)
+        _check(L.rwkv7_fused_mix6_stacked(_ref(xd), _ptr_array(sd), _ref(od), _stream(x)))
+        return out
+    outs = [torch.empty_like(x) for _ in range(6)]
+    od = [describe(o) for o in outs]
+    _check(L.rwkv7_fused_mix6(_ref(xd), _ptr_array(sd), _ptr_array(od), _stream(x)))
+    return dict(zip(MIX6_BRANCHES, outs))
+
+
+mix6 = mix6_custom
+
+# ------------------------------------------------------------------- addcmul --
+
+
+def addcmul_custom(base: torch.Tensor, diff: torch.Tensor, scale: torch.Tensor, *,
+                   inplace: bool = False) -> torch.Tensor:
+    """``addcmul_custom`` (``addcmul/mod.rs:100-105``): ``base + diff * scale``.
+    ``inplace`` writes over ``base`` like the reference does for a uniquely owned buffer."""
+    out = base if inplace else torch.empty_like(base)
+    bd, dd, sd, od = describe(base), describe(diff), describe(scale), describe(out)
+    _check(lib().rwkv7_fused_addcmul(_ref(bd), _ref(dd), _ref(sd), _ref(od), _stream(base)))
+    return out
+
+
+def addcmul5_custom(base: torch.Tensor, diff: torch.Tensor, receptance_scale, weight_decay_scale,
+                    key_scale, value_scale, learning_rate_scale):
+    """``addcmul5_custom`` (``addcmul/mod.rs:138-157``): five outputs sharing base and diff."""
+    scales = [receptance_scale, weight_decay_scale, key_scale, value_scale, learning_rate_scale]
+    outs = [torch.empty_like(base) for _ in range(5)]
+    bd, dd = describe(base), describe(diff)
+    sd = [describe(s) for s in scales]
+    od = [describe(o) for o in outs]
+    _check(lib().rwkv7_fused_addcmul5(_ref(bd), _ref(dd), _ptr_array(sd), _ptr_array(od), _stream(base)))
+    return dict(zip(MIX6_BRANCHES[:5], outs))
+
+
+addcmul = addcmul_custom
+addcmul5 = addcmul5_custom
+
+# ---------------------------------------------------------- token_shift_diff --
+
+
+@dataclass
+class TokenShiftDiffForwardOutput:
+    """``token_shift_diff/io.rs:77-83``."""
+
+    token_shifted_diff: torch.Tensor
+    next_token_shift: torch.Tensor
+
+
+def token_shift_diff_custom(embedded_context: torch.Tensor, embedded_token_shift: torch.Tensor,
+                            batch_ids: torch.Tensor, *, inplace_state: bool = False
+                            ) -> TokenShiftDiffForwardOutput:
+    """``token_shift_diff_custom`` (``token_shift_diff/mod.rs:82-111``).  The state
+    buffer is updated in place by the kernel; unless ``inplace_state`` the caller's
+    tensor is cloned first so that the call is functional like the reference's."""
+    state = embedded_token_shift if inplace_state else embedded_token_shift.clone()
+    diff = torch.empty_like(embedded_context)
+    xd, sd, idd, dd = describe(embedded_context), describe(state), describe(batch_ids), describe(diff)
+    _check(lib().rwkv7_fused_token_shift_diff(_ref(xd), _ref(sd), _ref(idd), _ref(dd),
+                                              _stream(embedded_context)))
+    return TokenShiftDiffForwardOutput(token_shifted_diff=diff, next_token_shift=state)
+
+
+token_shift_diff = token_shift_diff_custom
+
+# ---------------------------------------------------------------- lm_head_ce --
+
+
+def lm_head_ce_partial(x: torch.Tensor, weight_shard: torch.Tensor, targets: torch.Tensor,
+                       vocab_offset: int = 0) -> torch.Tensor:
+    """Per-row ``(max, sumexp, target logit)`` of ``x @ weight_shard.T`` over one
+    vocabulary shard, ``[R,3]`` fp32; logits are never materialised."""
+    R = x.shape[0]
+    partials = torch.empty((R, 3), dtype=torch.float32, device=x.device)
+    n = int(lib().rwkv7_lm_head_ce_workspace_bytes(R, x.shape[1], weight_shard.shape[0]))
+    ws = torch.empty(max(n, 1), dtype=torch.uint8, device=x.device)
+    xd, wd, td, pd = describe(x), describe(weight_shard), describe(targets), describe(partials)
+    _check(lib().rwkv7_fused_lm_head_ce_partial(_ref(xd), _ref(wd), _ref(td), ctypes.c_int64(vocab_offset),
+                                                _ref(pd), ctypes.c_void_p(ws.data_ptr()),
+                                                ctypes.c_size_t(n), _stream(x)))
+    return partials
+
+
+def lm_head_ce_finalize(partials_all: torch.Tensor, targets: torch.Tensor):
+    """Combines ``[num_shards,R,3]`` partials into per-row ``(lse, loss)``."""
+    R = partials_all.shape[1]
+    lse = torch.empty(R, dtype=torch.float32, device=partials_all.device)
+    loss = torch.empty(R, dtype=torch.float32, device=partials_all.device)
+    pd, td, ld, sd = describe(partials_all), describe(targets), describe(lse), describe(loss)
+    _check(lib().rwkv7_lm_head_ce_finalize(_ref(pd), _ref(td), _ref(ld), _ref(sd), _stream(partials_all)))
+    return lse, loss
+
+
+def lm_head_ce(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor):
+    """Single-GPU fused LM-head cross entropy: per-row ``(lse, loss)``."""
+    p = lm_head_ce_partial(x, weight, targets, 0)
+    return lm_head_ce_finalize(p.unsqueeze(0), targets)

@@ -1,0 +1,519 @@
+// extern "C" entry points: input contracts in the reference's order, then
+// dispatch to the CUDA launchers.  There is no CPU fallback: every entry point
+// either enqueues sm_100a kernels or returns an error status.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+#include <vector>
+
+#include "check.h"
+#include "kernels.h"
+#include "rwkv7_b200.h"
+
+using namespace rwkv7;
+
+namespace {
+
+std::atomic<int> g_wkv7_path{RWKV7_WKV7_AUTO};
+
+constexpr int kMaxDevices = 64;
+std::mutex g_props_mu;
+int g_num_sms[kMaxDevices] = {};
+
+// Makes `device` current for the duration of a call and restores the caller's.
+class DeviceGuard {
+   public:
+    explicit DeviceGuard(int device) {
+        err_ = cudaGetDevice(&prev_);
+        if (err_ == cudaSuccess && prev_ != device) {
+            err_ = cudaSetDevice(device);
+            switched_ = err_ == cudaSuccess;
+        }
+    }
+    ~DeviceGuard() {
+        if (switched_) cudaSetDevice(prev_);
+    }
+    cudaError_t error() const { return err_; }
+
+   private:
+    int prev_ = 0;
+    bool switched_ = false;
+    cudaError_t err_ = cudaSuccess;
+};
+
+int cuda_fail(const char *what, int err) {
+    return fail(RWKV7_ERR_CUDA, "CudaError: %s: %s", what, cudaGetErrorString((cudaError_t)err));
+}
+
+int num_sms(int device, int *out) {
+    if (device < 0 || device >= kMaxDevices)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_props_mu);
+    if (g_num_sms[device] == 0) {
+        int v = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return cuda_fail("cudaDeviceGetAttribute", (int)e);
+        g_num_sms[device] = v;
+    }
+    *out = g_num_sms[device];
+    return RWKV7_OK;
+}
+
+bool float_dtype_supported(int32_t dt) { return dt == RWKV7_F32 || dt == RWKV7_BF16; }
+
+#define RWKV7_TRY(expr)                 \
+    do {                                \
+        if (int st_ = (expr)) return st_; \
+    } while (0)
+
+// check_wkv7_sequence_inputs (wkv7/io.rs:175-241) + the contiguity assertions of
+// the CubeBackend impl (wkv7/mod.rs:56-76).  `chunk_len == 16` and
+// `T % chunk_len == 0` (io.rs:187,198-201) are properties of the reference's
+// backward snapshots, not of the forward arithmetic, and are not required here.
+int check_wkv7_sequence(const TensorInfo six[6], int64_t chunk_len) {
+    for (int i = 0; i < 6; ++i) RWKV7_TRY(check_present(six[i], 4));
+    if (chunk_len <= 0)
+        return fail(RWKV7_ERR_BAD_CHUNK, "BadChunk: chunk_len must be positive, got %lld", (long long)chunk_len);
+    const TensorInfo &r = six[0];
+    RWKV7_TRY(check_axis_non_empty(r, 1));
+    RWKV7_TRY(check_axis_non_empty(r, 3));
+    RWKV7_TRY(check_axes_equal({{six[0], 0}, {six[1], 0}, {six[2], 0}, {six[3], 0}, {six[4], 0}, {six[5], 0}}));
+    const std::vector<int64_t> expected(r.t->shape, r.t->shape + 4);
+    for (int i = 1; i < 6; ++i) RWKV7_TRY(check_shape(six[i], expected));
+    RWKV7_TRY(check_same_dtype({six[0], six[1], six[2], six[3], six[4], six[5]}));
+    RWKV7_TRY(check_same_device({six[0], six[1], six[2], six[3], six[4], six[5]}));
+    for (int i = 0; i < 6; ++i) RWKV7_TRY(check_contiguous(six[i]));
+    if (!float_dtype_supported(r.t->dtype))
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: wkv7 computes F32 or BF16 inputs, got %s",
+                    dtype_name(r.t->dtype));
+    return RWKV7_OK;
+}
+
+// check_initial_state (wkv7/io.rs:243-258).  The reference keeps the state in the
+// sequence dtype; this ABI carries it in F32 for every sequence dtype.
+int check_wkv7_state(const TensorInfo &state, const TensorInfo &r) {
+    RWKV7_TRY(check_present(state, 4));
+    RWKV7_TRY(check_shape(state, {r.dim(0), r.dim(2), r.dim(3), r.dim(3)}));
+    if (state.t->dtype != RWKV7_F32)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH,
+                    "DTypeMismatch: kernel input dtype mismatch: %s=%s, expected F32 state", state.name,
+                    dtype_name(state.t->dtype));
+    RWKV7_TRY(check_same_device({state, r}));
+    RWKV7_TRY(check_contiguous(state));
+    return RWKV7_OK;
+}
+
+int wkv7_run(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t chunk_len,
+             rwkv7_tensor *y, rwkv7_tensor *s_out, bool want_state, void *workspace,
+             size_t workspace_bytes, rwkv7_stream stream, bool has_s0) {
+    clear_error();
+    static const char *names[6] = {"receptance", "weight_decay", "replacement_key",
+                                   "value", "removal_key_normalized", "replacement"};
+    TensorInfo six[6];
+    for (int i = 0; i < 6; ++i) six[i] = TensorInfo{names[i], six_t[i]};
+    // Reference order (io.rs:95-106,131-141): sequence inputs first, then the state.
+    RWKV7_TRY(check_wkv7_sequence(six, chunk_len));
+    const TensorInfo &r = six[0];
+    if (has_s0) RWKV7_TRY(check_wkv7_state(TensorInfo{"initial_state", s0}, r));
+    const TensorInfo out{"output", y};
+    RWKV7_TRY(check_present(out, 4));
+    RWKV7_TRY(check_shape(out, std::vector<int64_t>(r.t->shape, r.t->shape + 4)));
+    RWKV7_TRY(check_same_dtype({r, out}));
+    RWKV7_TRY(check_same_device({r, out}));
+    RWKV7_TRY(check_contiguous(out));
+    if (want_state) RWKV7_TRY(check_wkv7_state(TensorInfo{"next_state", s_out}, r));
+
+    Wkv7Args p{};
+    p.r = six_t[0]->data; p.w = six_t[1]->data; p.k = six_t[2]->data;
+    p.v = six_t[3]->data; p.a = six_t[4]->data; p.b = six_t[5]->data;
+    p.s0 = has_s0 ? static_cast<const float *>(s0->data) : nullptr;
+    p.y = y->data;
+    p.s_out = want_state ? static_cast<float *>(s_out->data) : nullptr;
+    p.B = r.dim(0); p.T = r.dim(1); p.H = r.dim(2); p.N = r.dim(3);
+    p.bf16 = r.t->dtype == RWKV7_BF16;
+    p.device = r.t->device;
+    if (p.B == 0 || p.H == 0) return RWKV7_OK;  // nothing to compute
+
+    DeviceGuard guard(p.device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(p.device, &p.num_sms));
+
+    const int path = g_wkv7_path.load();
+    bool chunked = false;
+    if (path == RWKV7_WKV7_CHUNKED) {
+        if (!wkv7_chunked_supported(p))
+            return fail(RWKV7_ERR_UNSUPPORTED,
+                        "Unsupported: the chunked WKV7 kernel needs N == 64 (got N=%lld)", (long long)p.N);
+        chunked = true;
+    } else if (path == RWKV7_WKV7_AUTO) {
+        chunked = wkv7_chunked_supported(p) && p.T >= 64;
+    }
+    if (chunked) {
+        const size_t need = wkv7_chunked_workspace_bytes(p.B, p.T, p.H, p.N);
+        if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+            return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL,
+                        "WorkspaceTooSmall: wkv7 needs %zu workspace bytes, got %zu", need,
+                        workspace == nullptr ? (size_t)0 : workspace_bytes);
+        if (int e = launch_wkv7_chunked(p, workspace, workspace_bytes, (cudaStream_t)stream))
+            return cuda_fail("wkv7 chunked launch", e);
+        return RWKV7_OK;
+    }
+    if (p.N > 128)
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: head size N=%lld exceeds 128", (long long)p.N);
+    if (int e = launch_wkv7_sequential(p, (cudaStream_t)stream)) return cuda_fail("wkv7 sequential launch", e);
+    return RWKV7_OK;
+}
+
+// Shared contract of the [1,1,C] scale tensors (mix6/io.rs:48-86, addcmul/io.rs:42-54).
+int check_scales(const TensorInfo &x, const rwkv7_tensor *const *scales, const char *const *names, int n) {
+    const int64_t C = x.dim(2);
+    std::vector<TensorInfo> all{x};
+    for (int s = 0; s < n; ++s) {
+        TensorInfo info{names[s], scales[s]};
+        RWKV7_TRY(check_present(info, 3));
+        RWKV7_TRY(check_shape(info, {1, 1, C}));
+        all.push_back(info);
+    }
+    RWKV7_TRY(check_same_dtype(all));
+    RWKV7_TRY(check_same_device(all));
+    for (auto &t : all) RWKV7_TRY(check_contiguous(t));
+    return RWKV7_OK;
+}
+
+int check_output_like(const TensorInfo &x, const TensorInfo &out) {
+    RWKV7_TRY(check_present(out, x.t->ndim));
+    RWKV7_TRY(check_shape(out, std::vector<int64_t>(x.t->shape, x.t->shape + x.t->ndim)));
+    RWKV7_TRY(check_same_dtype({x, out}));
+    RWKV7_TRY(check_same_device({x, out}));
+    RWKV7_TRY(check_contiguous(out));
+    return RWKV7_OK;
+}
+
+const char *kMixScaleNames[6] = {"receptance_scale", "weight_decay_scale", "key_scale",
+                                 "value_scale", "learning_rate_scale", "gate_scale"};
+const char *kMixOutNames[6] = {"receptance_input", "weight_decay_input", "key_input",
+                               "value_input", "learning_rate_input", "gate_input"};
+
+int mix6_common(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6], MixArgs *p) {
+    const TensorInfo x{"embedded_context", x_t};
+    RWKV7_TRY(check_present(x, 3));
+    if (scales == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: scales array is null");
+    // Mix6ForwardInputs::check (mix6/io.rs:48-86)
+    RWKV7_TRY(check_axis_non_empty(x, 2));
+    RWKV7_TRY(check_scales(x, scales, kMixScaleNames, 6));
+    if (!float_dtype_supported(x_t->dtype))
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: mix6 computes F32 or BF16, got %s", dtype_name(x_t->dtype));
+    p->x = x_t->data;
+    for (int s = 0; s < 6; ++s) p->mu[s] = scales[s]->data;
+    p->B = x.dim(0); p->T = x.dim(1); p->C = x.dim(2);
+    p->bf16 = x_t->dtype == RWKV7_BF16;
+    return RWKV7_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int rwkv7_abi_version(void) { return RWKV7_ABI_VERSION; }
+
+const char *rwkv7_status_string(int status) {
+    switch (status) {
+        case RWKV7_OK: return "Ok";
+        case RWKV7_ERR_AXIS_MISMATCH: return "AxisMismatch";
+        case RWKV7_ERR_SHAPE_MISMATCH: return "ShapeMismatch";
+        case RWKV7_ERR_DTYPE_MISMATCH: return "DTypeMismatch";
+        case RWKV7_ERR_DEVICE_MISMATCH: return "DeviceMismatch";
+        case RWKV7_ERR_EMPTY_AXIS: return "EmptyAxis";
+        case RWKV7_ERR_NOT_CONTIGUOUS: return "NotContiguous";
+        case RWKV7_ERR_BAD_CHUNK: return "BadChunk";
+        case RWKV7_ERR_UNSUPPORTED: return "Unsupported";
+        case RWKV7_ERR_NULL_POINTER: return "NullPointer";
+        case RWKV7_ERR_WORKSPACE_TOO_SMALL: return "WorkspaceTooSmall";
+        case RWKV7_ERR_CUDA: return "CudaError";
+        case RWKV7_ERR_TIMEOUT: return "Timeout";
+        case RWKV7_ERR_BAD_INDEX: return "BadIndex";
+        case RWKV7_ERR_BAD_ARGUMENT: return "BadArgument";
+        default: return "Unknown";
+    }
+}
+
+const char *rwkv7_last_error_message(void) { return last_error(); }
+
+int rwkv7_set_wkv7_path(int path) {
+    if (path < RWKV7_WKV7_AUTO || path > RWKV7_WKV7_CHUNKED)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: unknown wkv7 path %d", path);
+    g_wkv7_path.store(path);
+    return RWKV7_OK;
+}
+
+int rwkv7_get_wkv7_path(void) { return g_wkv7_path.load(); }
+
+int64_t rwkv7_kernel_launch_count(void) { return launch_count(); }
+
+int rwkv7_read_device_status(int device, rwkv7_stream stream) {
+    clear_error();
+    DeviceGuard guard(device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    int *word = nullptr;
+    if (int e = device_status_ptr(device, &word)) return cuda_fail("device status word", e);
+    int host = 0;
+    cudaError_t e = cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(word, 0, sizeof(int), (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail("reading the device status word", (int)e);
+    if (host == kDevTimeout) return fail(RWKV7_ERR_TIMEOUT, "Timeout: a bounded device-side wait expired");
+    if (host == kDevBadIndex) return fail(RWKV7_ERR_BAD_INDEX, "BadIndex: a device-side index was out of range");
+    return RWKV7_OK;
+}
+
+size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype) {
+    (void)dtype;
+    if (g_wkv7_path.load() == RWKV7_WKV7_SEQUENTIAL) return 0;
+    return wkv7_chunked_workspace_bytes(B, T, H, N);
+}
+
+int rwkv7_fused_wkv7_pretrain(const rwkv7_tensor *r, const rwkv7_tensor *w, const rwkv7_tensor *k,
+                              const rwkv7_tensor *v, const rwkv7_tensor *a, const rwkv7_tensor *b,
+                              int64_t chunk_len, rwkv7_tensor *output, void *workspace,
+                              size_t workspace_bytes, rwkv7_stream stream) {
+    const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
+    return wkv7_run(nullptr, six, chunk_len, output, nullptr, false, workspace, workspace_bytes, stream, false);
+}
+
+int rwkv7_fused_wkv7_statetune(const rwkv7_tensor *s0, const rwkv7_tensor *r, const rwkv7_tensor *w,
+                               const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                               const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
+                               void *workspace, size_t workspace_bytes, rwkv7_stream stream) {
+    const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
+    return wkv7_run(s0, six, chunk_len, output, nullptr, false, workspace, workspace_bytes, stream, true);
+}
+
+int rwkv7_fused_wkv7_statepass(const rwkv7_tensor *s0, const rwkv7_tensor *r, const rwkv7_tensor *w,
+                               const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                               const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
+                               rwkv7_tensor *next_state, void *workspace, size_t workspace_bytes,
+                               rwkv7_stream stream) {
+    const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
+    return wkv7_run(s0, six, chunk_len, output, next_state, true, workspace, workspace_bytes, stream, true);
+}
+
+int rwkv7_fused_mix6(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6],
+                     rwkv7_tensor *const outputs[6], rwkv7_stream stream) {
+    clear_error();
+    MixArgs p{};
+    RWKV7_TRY(mix6_common(x_t, scales, &p));
+    if (outputs == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: outputs array is null");
+    const TensorInfo x{"embedded_context", x_t};
+    for (int s = 0; s < 6; ++s) {
+        RWKV7_TRY(check_output_like(x, TensorInfo{kMixOutNames[s], outputs[s]}));
+        p.out[s] = outputs[s]->data;
+    }
+    DeviceGuard guard(x_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(x_t->device, &p.num_sms));
+    if (int e = launch_mix6(p, (cudaStream_t)stream)) return cuda_fail("mix6 launch", e);
+    return RWKV7_OK;
+}
+
+int rwkv7_fused_mix6_stacked(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6],
+                             rwkv7_tensor *stacked, rwkv7_stream stream) {
+    clear_error();
+    MixArgs p{};
+    RWKV7_TRY(mix6_common(x_t, scales, &p));
+    const TensorInfo x{"embedded_context", x_t};
+    const TensorInfo out{"stacked_output", stacked};
+    RWKV7_TRY(check_present(out, 4));
+    RWKV7_TRY(check_shape(out, {6, p.B, p.T, p.C}));
+    RWKV7_TRY(check_same_dtype({x, out}));
+    RWKV7_TRY(check_same_device({x, out}));
+    RWKV7_TRY(check_contiguous(out));
+    const size_t plane = (size_t)(p.B * p.T * p.C) * dtype_size(x_t->dtype);
+    for (int s = 0; s < 6; ++s) p.out[s] = static_cast<char *>(stacked->data) + plane * s;
+    DeviceGuard guard(x_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(x_t->device, &p.num_sms));
+    if (int e = launch_mix6(p, (cudaStream_t)stream)) return cuda_fail("mix6 launch", e);
+    return RWKV7_OK;
+}
+
+static int addcmul_run(const rwkv7_tensor *base_t, const rwkv7_tensor *diff_t,
+                       const rwkv7_tensor *const *scales, rwkv7_tensor *const *outputs, int n,
+                       const char *const *scale_names, const char *const *out_names,
+                       rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo base{"base", base_t}, diff{"diff", diff_t};
+    RWKV7_TRY(check_present(base, 3));
+    RWKV7_TRY(check_present(diff, 3));
+    if (scales == nullptr || outputs == nullptr)
+        return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: scales or outputs array is null");
+    // AddcmulForwardInputs::check / Addcmul5ForwardInputs::check (addcmul/io.rs:42-54,108-150)
+    RWKV7_TRY(check_axis_non_empty(base, 2));
+    RWKV7_TRY(check_same_shape({base, diff}));
+    const int64_t C = base.dim(2);
+    std::vector<TensorInfo> all{base, diff};
+    for (int s = 0; s < n; ++s) {
+        TensorInfo info{scale_names[s], scales[s]};
+        RWKV7_TRY(check_present(info, 3));
+        RWKV7_TRY(check_shape(info, {1, 1, C}));
+        all.push_back(info);
+    }
+    RWKV7_TRY(check_same_dtype(all));
+    RWKV7_TRY(check_same_device(all));
+    for (auto &t : all) RWKV7_TRY(check_contiguous(t));
+    if (!float_dtype_supported(base_t->dtype))
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: addcmul computes F32 or BF16, got %s", dtype_name(base_t->dtype));
+    AddcmulArgs p{};
+    p.base = base_t->data; p.diff = diff_t->data; p.nscale = n;
+    p.rows = base.dim(0) * base.dim(1); p.C = C; p.bf16 = base_t->dtype == RWKV7_BF16;
+    for (int s = 0; s < n; ++s) {
+        RWKV7_TRY(check_output_like(base, TensorInfo{out_names[s], outputs[s]}));
+        p.scale[s] = scales[s]->data;
+        p.out[s] = outputs[s]->data;
+    }
+    DeviceGuard guard(base_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(base_t->device, &p.num_sms));
+    if (int e = launch_addcmul(p, (cudaStream_t)stream)) return cuda_fail("addcmul launch", e);
+    return RWKV7_OK;
+}
+
+int rwkv7_fused_addcmul(const rwkv7_tensor *base, const rwkv7_tensor *diff, const rwkv7_tensor *scale,
+                        rwkv7_tensor *output, rwkv7_stream stream) {
+    static const char *sn[1] = {"scale"};
+    static const char *on[1] = {"output"};
+    const rwkv7_tensor *scales[1] = {scale};
+    rwkv7_tensor *outs[1] = {output};
+    return addcmul_run(base, diff, scales, outs, 1, sn, on, stream);
+}
+
+int rwkv7_fused_addcmul5(const rwkv7_tensor *base, const rwkv7_tensor *diff,
+                         const rwkv7_tensor *const scales[5], rwkv7_tensor *const outputs[5],
+                         rwkv7_stream stream) {
+    return addcmul_run(base, diff, scales, outputs, 5, kMixScaleNames, kMixOutNames, stream);
+}
+
+int rwkv7_fused_token_shift_diff(const rwkv7_tensor *x_t, rwkv7_tensor *state_t,
+                                 const rwkv7_tensor *ids_t, rwkv7_tensor *diff_t, rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo x{"embedded_context", x_t}, state{"embedded_token_shift", state_t},
+        ids{"batch_ids", ids_t};
+    RWKV7_TRY(check_present(x, 3));
+    RWKV7_TRY(check_present(state, 2));
+    RWKV7_TRY(check_present(ids, 1));
+    // TokenShiftDiffForwardInputs::check (token_shift_diff/io.rs:50-66)
+    RWKV7_TRY(check_axis_non_empty(x, 2));
+    RWKV7_TRY(check_shape(state, {state.dim(0), x.dim(2)}));
+    RWKV7_TRY(check_shape(ids, {x.dim(0)}));
+    RWKV7_TRY(check_same_dtype({x, state}));
+    RWKV7_TRY(check_same_device({x, state, ids}));
+    RWKV7_TRY(check_contiguous(x));
+    RWKV7_TRY(check_contiguous(state));
+    RWKV7_TRY(check_contiguous(ids));
+    if (!float_dtype_supported(x_t->dtype))
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: token_shift_diff computes F32 or BF16, got %s", dtype_name(x_t->dtype));
+    if (ids_t->dtype != RWKV7_I32 && ids_t->dtype != RWKV7_I64 && ids_t->dtype != RWKV7_U32)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH, "DTypeMismatch: batch_ids must be I32, I64 or U32, got %s", dtype_name(ids_t->dtype));
+    RWKV7_TRY(check_output_like(x, TensorInfo{"token_shifted_diff", diff_t}));
+    TokenShiftArgs p{};
+    p.x = x_t->data; p.state = state_t->data; p.ids = ids_t->data; p.ids_dtype = ids_t->dtype;
+    p.diff = diff_t->data;
+    p.B = x.dim(0); p.T = x.dim(1); p.C = x.dim(2); p.S = state.dim(0);
+    p.bf16 = x_t->dtype == RWKV7_BF16;
+    if (p.B == 0 || p.T == 0) return RWKV7_OK;  // token_shift_diff/mod.rs:88-97: T == 0 is a no-op
+    DeviceGuard guard(x_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(x_t->device, &p.num_sms));
+    if (int e = device_status_ptr(x_t->device, &p.status)) return cuda_fail("device status word", e);
+    if (int e = launch_token_shift_diff(p, (cudaStream_t)stream)) return cuda_fail("token_shift_diff launch", e);
+    return RWKV7_OK;
+}
+
+size_t rwkv7_lm_head_ce_workspace_bytes(int64_t R, int64_t C, int64_t V_shard) {
+    return lm_head_ce_workspace_bytes(R, C, V_shard);
+}
+
+int rwkv7_fused_lm_head_ce_partial(const rwkv7_tensor *x_t, const rwkv7_tensor *w_t,
+                                   const rwkv7_tensor *targets_t, int64_t vocab_offset,
+                                   rwkv7_tensor *partials_t, void *workspace, size_t workspace_bytes,
+                                   rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo x{"x", x_t}, w{"weight_shard", w_t}, tg{"targets", targets_t},
+        pt{"partials", partials_t};
+    RWKV7_TRY(check_present(x, 2));
+    RWKV7_TRY(check_present(w, 2));
+    RWKV7_TRY(check_present(tg, 1));
+    RWKV7_TRY(check_present(pt, 2));
+    RWKV7_TRY(check_axis_non_empty(x, 1));
+    RWKV7_TRY(check_axis_non_empty(w, 0));
+    RWKV7_TRY(check_axes_equal({{x, 1}, {w, 1}}));
+    RWKV7_TRY(check_shape(tg, {x.dim(0)}));
+    RWKV7_TRY(check_shape(pt, {x.dim(0), 3}));
+    RWKV7_TRY(check_same_dtype({x, w}));
+    RWKV7_TRY(check_same_device({x, w, tg, pt}));
+    RWKV7_TRY(check_contiguous(x));
+    RWKV7_TRY(check_contiguous(w));
+    RWKV7_TRY(check_contiguous(tg));
+    RWKV7_TRY(check_contiguous(pt));
+    if (x_t->dtype != RWKV7_BF16)
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: lm_head_ce computes BF16 inputs, got %s", dtype_name(x_t->dtype));
+    if (targets_t->dtype != RWKV7_I32 && targets_t->dtype != RWKV7_I64)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH, "DTypeMismatch: targets must be I32 or I64, got %s", dtype_name(targets_t->dtype));
+    if (partials_t->dtype != RWKV7_F32)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH, "DTypeMismatch: partials must be F32, got %s", dtype_name(partials_t->dtype));
+    LmHeadArgs p{};
+    p.x = x_t->data; p.w = w_t->data; p.targets = targets_t->data; p.targets_dtype = targets_t->dtype;
+    p.vocab_offset = vocab_offset; p.partials = static_cast<float *>(partials_t->data);
+    p.R = x.dim(0); p.C = x.dim(1); p.V = w.dim(0); p.device = x_t->device;
+    if (p.R == 0) return RWKV7_OK;
+    if (p.C % 64 != 0)
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: lm_head_ce needs C %% 64 == 0 (got C=%lld)", (long long)p.C);
+    const size_t need = lm_head_ce_workspace_bytes(p.R, p.C, p.V);
+    if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+        return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: lm_head_ce needs %zu workspace bytes, got %zu",
+                    need, workspace == nullptr ? (size_t)0 : workspace_bytes);
+    DeviceGuard guard(p.device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(p.device, &p.num_sms));
+    if (int e = device_status_ptr(p.device, &p.status)) return cuda_fail("device status word", e);
+    if (int e = launch_lm_head_ce_partial(p, workspace, workspace_bytes, (cudaStream_t)stream))
+        return cuda_fail("lm_head_ce launch", e);
+    return RWKV7_OK;
+}
+
+int rwkv7_lm_head_ce_finalize(const rwkv7_tensor *partials_all_t, const rwkv7_tensor *targets_t,
+                              rwkv7_tensor *lse_t, rwkv7_tensor *loss_t, rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo pa{"partials_all", partials_all_t}, tg{"targets", targets_t}, lse{"lse", lse_t},
+        loss{"loss", loss_t};
+    RWKV7_TRY(check_present(pa, 3));
+    RWKV7_TRY(check_present(tg, 1));
+    RWKV7_TRY(check_present(lse, 1));
+    RWKV7_TRY(check_present(loss, 1));
+    RWKV7_TRY(check_axis_non_empty(pa, 0));
+    const int64_t R = pa.dim(1);
+    RWKV7_TRY(check_shape(pa, {pa.dim(0), R, 3}));
+    RWKV7_TRY(check_shape(tg, {R}));
+    RWKV7_TRY(check_shape(lse, {R}));
+    RWKV7_TRY(check_shape(loss, {R}));
+    RWKV7_TRY(check_same_dtype({pa, lse, loss}));
+    RWKV7_TRY(check_same_device({pa, tg, lse, loss}));
+    RWKV7_TRY(check_contiguous(pa));
+    RWKV7_TRY(check_contiguous(tg));
+    RWKV7_TRY(check_contiguous(lse));
+    RWKV7_TRY(check_contiguous(loss));
+    if (partials_all_t->dtype != RWKV7_F32)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH, "DTypeMismatch: partials_all must be F32, got %s", dtype_name(partials_all_t->dtype));
+    if (targets_t->dtype != RWKV7_I32 && targets_t->dtype != RWKV7_I64)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH, "DTypeMismatch: targets must be I32 or I64, got %s", dtype_name(targets_t->dtype));
+    if (R == 0) return RWKV7_OK;
+    DeviceGuard guard(partials_all_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    if (int e = launch_lm_head_ce_finalize(static_cast<const float *>(partials_all_t->data), (int)pa.dim(0),
+                                           targets_t->data, targets_t->dtype, static_cast<float *>(lse_t->data),
+                                           static_cast<float *>(loss_t->data), R, (cudaStream_t)stream))
+        return cuda_fail("lm_head_ce finalize launch", e);
+    return RWKV7_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,95 @@
+// Internal launch interface between the C ABI (abi.cpp) and the CUDA kernels.
+// Plain pointers and sizes; every launcher enqueues on `stream` and returns the
+// cudaError_t of the launch as an int (0 = success).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include <cuda_runtime_api.h>
+
+namespace rwkv7 {
+
+// Device status word values (see rwkv7_read_device_status).
+enum DeviceStatus : int { kDevOk = 0, kDevTimeout = 1, kDevBadIndex = 2 };
+// Address of the per-device status word, resolved once per device.
+int device_status_ptr(int device, int **out);
+// Process-wide count of kernel launches (rwkv7_kernel_launch_count).
+void count_launch(int n = 1);
+int64_t launch_count();
+
+struct Wkv7Args {
+    const void *r, *w, *k, *v, *a, *b;  // [B,T,H,N], bf16 or f32
+    const float *s0;                    // [B,H,N,N] or null (zero state)
+    void *y;                            // [B,T,H,N]
+    float *s_out;                       // [B,H,N,N] or null
+    int64_t B, T, H, N;
+    bool bf16;
+    int device;
+    int num_sms;
+};
+
+// Token-by-token scan, fp32 state in registers (N == 64) or shared memory (any
+// N <= 128).  Also the decode (T == 1) sweep.
+int launch_wkv7_sequential(const Wkv7Args &p, cudaStream_t stream);
+
+// Chunked tensor-core prefill (N == 64): tcgen05 MMAs with TMEM accumulators.
+size_t wkv7_chunked_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+bool wkv7_chunked_supported(const Wkv7Args &p);
+int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes,
+                        cudaStream_t stream);
+
+struct MixArgs {
+    const void *x;        // [B,T,C]
+    const void *mu[6];    // [C] each
+    void *out[6];         // [B,T,C] each
+    int64_t B, T, C;
+    bool bf16;
+    int num_sms;
+};
+int launch_mix6(const MixArgs &p, cudaStream_t stream);
+
+struct AddcmulArgs {
+    const void *base, *diff;  // [rows,C]
+    const void *scale[5];     // [C] each
+    void *out[5];             // [rows,C] each
+    int nscale;               // 1 or 5
+    int64_t rows, C;
+    bool bf16;
+    int num_sms;
+};
+int launch_addcmul(const AddcmulArgs &p, cudaStream_t stream);
+
+struct TokenShiftArgs {
+    const void *x;     // [B,T,C]
+    void *state;       // [S,C], updated in place
+    const void *ids;   // [B]
+    int ids_dtype;     // RWKV7_I32 / RWKV7_I64 / RWKV7_U32
+    void *diff;        // [B,T,C]
+    int64_t B, T, C, S;
+    bool bf16;
+    int *status;       // device status word
+    int num_sms;
+};
+int launch_token_shift_diff(const TokenShiftArgs &p, cudaStream_t stream);
+
+struct LmHeadArgs {
+    const void *x;        // [R,C] bf16
+    const void *w;        // [V,C] bf16
+    const void *targets;  // [R]
+    int targets_dtype;
+    int64_t vocab_offset;
+    float *partials;      // [R,3]
+    int64_t R, C, V;
+    int device;
+    int num_sms;
+    int *status;
+};
+size_t lm_head_ce_workspace_bytes(int64_t R, int64_t C, int64_t V);
+int launch_lm_head_ce_partial(const LmHeadArgs &p, void *workspace, size_t workspace_bytes,
+                              cudaStream_t stream);
+int launch_lm_head_ce_finalize(const float *partials_all, int num_shards, const void *targets,
+                               int targets_dtype, float *lse, float *loss, int64_t R,
+                               cudaStream_t stream);
+
+}  // namespace rwkv7

@@ -1,0 +1,317 @@
+// Sequential WKV7 scan and decode sweep.
+//
+// Semantics: crates/rwkv-nn/src/kernels/train/time_mixer/wkv7/mod.rs:179-242 of
+// the reference (per token: sa = S a; S = S diag(d) + sa b^T + v k^T; y = S r,
+// d = exp(-exp(w))).  Unlike the reference kernel (kernel.rs:82-195), which
+// re-reads its state row from global memory every token, the fp32 state here
+// stays in registers for the whole call and is read from / written to HBM once.
+//
+// N == 64: a CTA owns ROWS value rows of one (b,h); 4 threads share a row, each
+// holding 16 key columns (interleaved in groups of 4 so that the per-token
+// vectors are read from shared memory with conflict-free 128-bit loads).  Token
+// vectors are staged 16 tokens at a time through a double-buffered shared tile,
+// converted to fp32 once (decay computed once per element).
+// Any other N <= 128: one thread per row, state in shared memory.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+
+#include "kernels.h"
+
+namespace rwkv7 {
+namespace {
+
+constexpr int kN = 64;
+constexpr int kTile = 16;  // tokens staged per shared tile
+
+enum { VR = 0, VD = 1, VK = 2, VV = 3, VA = 4, VB = 5 };
+
+struct SeqPtrs {
+    const void *in[6];  // r, w, k, v, a, b
+};
+
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+    static constexpr int kElems = 4;
+    static __device__ __forceinline__ void unpack(const uint4 &u, float *f) {
+        f[0] = __uint_as_float(u.x);
+        f[1] = __uint_as_float(u.y);
+        f[2] = __uint_as_float(u.z);
+        f[3] = __uint_as_float(u.w);
+    }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+    static constexpr int kElems = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &u, float *f) {
+        const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(ROWS * 4)
+wkv7_seq64_kernel(SeqPtrs ptrs, const float *__restrict__ s0, T *__restrict__ y,
+                  float *__restrict__ s_out, int Tlen, int H) {
+    constexpr int THREADS = ROWS * 4;
+    constexpr int SPLITS = kN / ROWS;
+    constexpr int EPV = Vec16<T>::kElems;
+    constexpr int VPR = kN / EPV;                 // 16-byte vectors per token row
+    constexpr int VECS = kTile * 6 * VPR;         // vectors per tile
+    constexpr int NV = (VECS + THREADS - 1) / THREADS;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *vec = reinterpret_cast<float *>(smem_raw);             // [2][kTile][6][kN]
+    float *ytile = vec + 2 * kTile * 6 * kN;                      // [2][kTile][ROWS]
+
+    const int bh = blockIdx.x / SPLITS;
+    const int split = blockIdx.x % SPLITS;
+    const int bi = bh / H, h = bh % H;
+    const int row0 = split * ROWS;
+    const int tid = threadIdx.x;
+    const int i = tid >> 2, q = tid & 3;
+
+    float S[16];
+    if (s0 != nullptr) {
+        const float4 *src =
+            reinterpret_cast<const float4 *>(s0 + ((size_t)bh * kN + row0 + i) * kN);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const float4 x = src[kk * 4 + q];
+            S[kk * 4 + 0] = x.x; S[kk * 4 + 1] = x.y; S[kk * 4 + 2] = x.z; S[kk * 4 + 3] = x.w;
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) S[e] = 0.f;
+    }
+
+    const size_t seq_base = ((size_t)bi * Tlen * H + h) * kN;  // element offset of (b, t=0, h, 0)
+    const size_t tok_stride = (size_t)H * kN;
+    const int ntiles = (Tlen + kTile - 1) / kTile;
+
+    uint4 stage[NV];
+    auto issue_loads = [&](int tile) {
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int idx = tid + n * THREADS;
+            stage[n] = make_uint4(0, 0, 0, 0);
+            if (idx < VECS) {
+                const int c = idx % VPR;
+                const int tensor = (idx / VPR) % 6;
+                const int tok = idx / (VPR * 6);
+                const int t = tile * kTile + tok;
+                if (t < Tlen) {
+                    const T *p = reinterpret_cast<const T *>(ptrs.in[tensor]) + seq_base +
+                                 (size_t)t * tok_stride + c * EPV;
+                    stage[n] = __ldg(reinterpret_cast<const uint4 *>(p));
+                }
+            }
+        }
+    };
+    auto commit_stage = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+            const int idx = tid + n * THREADS;
+            if (idx < VECS) {
+                const int c = idx % VPR;
+                const int tensor = (idx / VPR) % 6;
+                const int tok = idx / (VPR * 6);
+                float f[EPV];
+                Vec16<T>::unpack(stage[n], f);
+                if (tensor == VD) {
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) f[e] = expf(-expf(f[e]));
+                }
+                float4 *dst = reinterpret_cast<float4 *>(
+                    vec + (((size_t)buf * kTile + tok) * 6 + tensor) * kN + c * EPV);
+#pragma unroll
+                for (int e = 0; e < EPV / 4; ++e)
+                    dst[e] = make_float4(f[4 * e], f[4 * e + 1], f[4 * e + 2], f[4 * e + 3]);
+            }
+        }
+    };
+
+    issue_loads(0);
+    commit_stage(0);
+    __syncthreads();
+
+    for (int tile = 0; tile < ntiles; ++tile) {
+        const int buf = tile & 1;
+        if (tile + 1 < ntiles) issue_loads(tile + 1);
+        const int ntok = min(kTile, Tlen - tile * kTile);
+        const float *tv = vec + (size_t)buf * kTile * 6 * kN;
+        float *yt = ytile + (size_t)buf * kTile * ROWS;
+
+        for (int tt = 0; tt < ntok; ++tt) {
+            const float *base = tv + (size_t)tt * 6 * kN;
+            const float4 *a4 = reinterpret_cast<const float4 *>(base + VA * kN);
+            float sa0 = 0.f, sa1 = 0.f, sa2 = 0.f, sa3 = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const float4 x = a4[kk * 4 + q];
+                sa0 = fmaf(S[kk * 4 + 0], x.x, sa0);
+                sa1 = fmaf(S[kk * 4 + 1], x.y, sa1);
+                sa2 = fmaf(S[kk * 4 + 2], x.z, sa2);
+                sa3 = fmaf(S[kk * 4 + 3], x.w, sa3);
+            }
+            float sa = (sa0 + sa1) + (sa2 + sa3);
+            sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+            sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+            const float vi = base[VV * kN + row0 + i];
+            const float4 *d4 = reinterpret_cast<const float4 *>(base + VD * kN);
+            const float4 *b4 = reinterpret_cast<const float4 *>(base + VB * kN);
+            const float4 *k4 = reinterpret_cast<const float4 *>(base + VK * kN);
+            const float4 *r4 = reinterpret_cast<const float4 *>(base + VR * kN);
+            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const float4 d = d4[kk * 4 + q], bb = b4[kk * 4 + q], kx = k4[kk * 4 + q],
+                             rr = r4[kk * 4 + q];
+                float s;
+                s = fmaf(S[kk * 4 + 0], d.x, fmaf(sa, bb.x, vi * kx.x)); S[kk * 4 + 0] = s; y0 = fmaf(s, rr.x, y0);
+                s = fmaf(S[kk * 4 + 1], d.y, fmaf(sa, bb.y, vi * kx.y)); S[kk * 4 + 1] = s; y1 = fmaf(s, rr.y, y1);
+                s = fmaf(S[kk * 4 + 2], d.z, fmaf(sa, bb.z, vi * kx.z)); S[kk * 4 + 2] = s; y2 = fmaf(s, rr.z, y2);
+                s = fmaf(S[kk * 4 + 3], d.w, fmaf(sa, bb.w, vi * kx.w)); S[kk * 4 + 3] = s; y3 = fmaf(s, rr.w, y3);
+            }
+            float yy = (y0 + y1) + (y2 + y3);
+            yy += __shfl_xor_sync(0xffffffffu, yy, 1);
+            yy += __shfl_xor_sync(0xffffffffu, yy, 2);
+            if (q == 0) yt[tt * ROWS + i] = yy;
+        }
+
+        if (tile + 1 < ntiles) commit_stage(buf ^ 1);
+        __syncthreads();
+        for (int idx = tid; idx < ntok * ROWS; idx += THREADS) {
+            const int tt = idx / ROWS, rr = idx % ROWS;
+            const size_t o = seq_base + (size_t)(tile * kTile + tt) * tok_stride + row0 + rr;
+            y[o] = from_f32<T>(yt[tt * ROWS + rr]);
+        }
+    }
+
+    if (s_out != nullptr) {
+        float4 *dst = reinterpret_cast<float4 *>(s_out + ((size_t)bh * kN + row0 + i) * kN);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+            dst[kk * 4 + q] = make_float4(S[kk * 4 + 0], S[kk * 4 + 1], S[kk * 4 + 2], S[kk * 4 + 3]);
+    }
+}
+
+// Any head size N <= 128: thread i owns state row i, kept in shared memory with
+// a padded row pitch; the six token vectors are staged per token.
+template <typename T>
+__global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *__restrict__ s0,
+                                        T *__restrict__ y, float *__restrict__ s_out, int Tlen,
+                                        int H, int N) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int pitch = N + 1;
+    float *S = reinterpret_cast<float *>(smem_raw);  // [N][N+1]
+    float *vec = S + (size_t)N * pitch;              // [6][N]
+    const int bh = blockIdx.x;
+    const int bi = bh / H, h = bh % H;
+    const int tid = threadIdx.x;
+
+    for (int idx = tid; idx < N * N; idx += blockDim.x) {
+        const int i = idx / N, j = idx % N;
+        S[i * pitch + j] = s0 ? s0[(size_t)bh * N * N + idx] : 0.f;
+    }
+    const size_t seq_base = ((size_t)bi * Tlen * H + h) * N;
+    const size_t tok_stride = (size_t)H * N;
+    __syncthreads();
+    for (int t = 0; t < Tlen; ++t) {
+        const size_t o = seq_base + (size_t)t * tok_stride;
+        for (int idx = tid; idx < 6 * N; idx += blockDim.x) {
+            const int tensor = idx / N, j = idx % N;
+            float x = static_cast<float>(reinterpret_cast<const T *>(ptrs.in[tensor])[o + j]);
+            if (tensor == VD) x = expf(-expf(x));
+            vec[idx] = x;
+        }
+        __syncthreads();
+        if (tid < N) {
+            float *Si = S + tid * pitch;
+            float sa = 0.f;
+            for (int j = 0; j < N; ++j) sa = fmaf(Si[j], vec[VA * N + j], sa);
+            const float vi = vec[VV * N + tid];
+            float acc = 0.f;
+            for (int j = 0; j < N; ++j) {
+                const float s = fmaf(Si[j], vec[VD * N + j], fmaf(sa, vec[VB * N + j], vi * vec[VK * N + j]));
+                Si[j] = s;
+                acc = fmaf(s, vec[VR * N + j], acc);
+            }
+            y[o + tid] = from_f32<T>(acc);
+        }
+        __syncthreads();
+    }
+    if (s_out != nullptr)
+        for (int idx = tid; idx < N * N; idx += blockDim.x) {
+            const int i = idx / N, j = idx % N;
+            s_out[(size_t)bh * N * N + idx] = S[i * pitch + j];
+        }
+}
+
+template <typename T, int ROWS>
+int launch_seq64(const Wkv7Args &p, cudaStream_t stream) {
+    SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
+    const size_t smem = sizeof(float) * (2 * kTile * 6 * kN + 2 * kTile * ROWS);
+    auto kern = wkv7_seq64_kernel<T, ROWS>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const unsigned grid = (unsigned)(p.B * p.H * (kN / ROWS));
+    kern<<<grid, ROWS * 4, smem, stream>>>(ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out,
+                                           (int)p.T, (int)p.H);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int launch_seq(const Wkv7Args &p, cudaStream_t stream) {
+    if (p.N == kN) {
+        // Split the 64 value rows of a (b,h) over several CTAs when there are too
+        // few (b,h) chains to fill the SMs; rows of S never interact.
+        const int64_t chains = p.B * p.H;
+        int rows = 64;
+        if (chains < 2 * (int64_t)p.num_sms) rows = 32;
+        if (chains * 2 < 2 * (int64_t)p.num_sms) rows = 16;
+        if (const char *env = std::getenv("RWKV7_SEQ_ROWS")) {
+            const int v = std::atoi(env);
+            if (v == 16 || v == 32 || v == 64) rows = v;
+        }
+        if (rows == 64) return launch_seq64<T, 64>(p, stream);
+        if (rows == 32) return launch_seq64<T, 32>(p, stream);
+        return launch_seq64<T, 16>(p, stream);
+    }
+    SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
+    const int N = (int)p.N;
+    const size_t smem = sizeof(float) * ((size_t)N * (N + 1) + 6 * N);
+    auto kern = wkv7_seq_generic_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int threads = ((N + 31) / 32) * 32;
+    kern<<<(unsigned)(p.B * p.H), threads, smem, stream>>>(ptrs, p.s0, reinterpret_cast<T *>(p.y),
+                                                          p.s_out, (int)p.T, (int)p.H, N);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_wkv7_sequential(const Wkv7Args &p, cudaStream_t stream) {
+    return p.bf16 ? launch_seq<__nv_bfloat16>(p, stream) : launch_seq<float>(p, stream);
+}
+
+}  // namespace rwkv7

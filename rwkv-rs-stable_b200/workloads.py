@@ -1,0 +1,79 @@
+"""Seeded synthetic inputs with the shapes and value distributions of the
+benchmark configurations (no dataset is involved anywhere on this path).
+
+WKV7 sequence inputs follow the ranges the reference's ``WeightPrepare`` produces
+(``crates/rwkv-nn/src/modules/time_mixer/weight_prepare.rs:252-287``):
+``r, k, v ~ N(0,1)``; ``w ~ U(-6,-0.5)`` (the op applies ``exp(-exp(w))``);
+``kk`` = L2-normalised ``N(0,1)`` per head; ``a = -kk``; ``b = kk * sigmoid(N(0,1))``.
+Values are generated in fp32 and rounded ONCE to the requested dtype, so the
+oracle and the kernels consume identical numbers.
+"""
+from __future__ import annotations
+
+import torch
+
+SEED_BASE = 0x5257_4B56  # "RWKV"
+
+# (B, T, H, N) of the benchmark configurations that are a single WKV7 call.
+WKV7_CONFIGS = {
+    "cfg0_cpu_f32": dict(B=1, T=64, H=4, N=64, dtype=torch.float32),
+    "cfg1_prefill_bf16": dict(B=8, T=4096, H=12, N=64, dtype=torch.bfloat16),
+    "cfg2_layer_bf16": dict(B=16, T=8192, H=32, N=64, dtype=torch.bfloat16),
+    "cfg3_decode_layer_bf16": dict(B=1024, T=1, H=40, N=64, dtype=torch.bfloat16),
+    "cfg4_layer_bf16": dict(B=4, T=65536, H=64, N=64, dtype=torch.bfloat16),
+}
+
+
+def _gen(device, seed: int) -> torch.Generator:
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED_BASE * 1000 + seed)
+    return g
+
+
+def wkv7_inputs(B: int, T: int, H: int, N: int, *, seed: int = 0, dtype=torch.float32,
+                device="cpu", state: str | None = None):
+    """Returns ``dict(r, w, k, v, a, b[, s0])``; ``state`` is None (zero state,
+    not materialised), ``"zeros"`` or ``"normal"`` (``N(0, 0.1)`` fp32)."""
+    g = _gen(device, seed)
+    shape = (B, T, H, N)
+
+    def normal():
+        return torch.randn(shape, generator=g, device=device, dtype=torch.float32)
+
+    r, k, v = normal(), normal(), normal()
+    w = torch.rand(shape, generator=g, device=device, dtype=torch.float32) * 5.5 - 6.0
+    kk = normal()
+    kk = kk / kk.norm(dim=-1, keepdim=True).clamp_min(1e-12)
+    a = -kk
+    b = kk * torch.sigmoid(normal())
+    out = {n: t.to(dtype).contiguous() for n, t in dict(r=r, w=w, k=k, v=v, a=a, b=b).items()}
+    if state == "zeros":
+        out["s0"] = torch.zeros((B, H, N, N), device=device, dtype=torch.float32)
+    elif state == "normal":
+        out["s0"] = torch.randn((B, H, N, N), generator=g, device=device, dtype=torch.float32) * 0.1
+    return out
+
+
+def uniform_inputs(shape, *, seed: int = 0, dtype=torch.float32, device="cpu", n: int = 6):
+    """``n`` tensors of U[0,1): the distribution of the reference's own unit tests
+    (``Tensor::random(.., Distribution::Default)``, ``wkv7/mod.rs:386-398``)."""
+    g = _gen(device, 7919 + seed)
+    return [torch.rand(shape, generator=g, device=device, dtype=torch.float32).to(dtype) for _ in range(n)]
+
+
+def mix_inputs(B: int, T: int, C: int, *, seed: int = 0, dtype=torch.float32, device="cpu", nscale: int = 6):
+    """``x ~ N(0,1)`` of shape ``[B,T,C]`` and ``nscale`` scales ``U[0,1)`` of shape ``[1,1,C]``."""
+    g = _gen(device, 104729 + seed)
+    x = torch.randn((B, T, C), generator=g, device=device, dtype=torch.float32).to(dtype)
+    mus = [torch.rand((1, 1, C), generator=g, device=device, dtype=torch.float32).to(dtype)
+           for _ in range(nscale)]
+    return x, mus
+
+
+def lm_head_inputs(R: int, C: int, V: int, *, seed: int = 0, device="cpu"):
+    """Hidden rows ``N(0,1)`` bf16, weights ``N(0,0.02)`` bf16, uniform targets in ``[0,V)``."""
+    g = _gen(device, 1299709 + seed)
+    x = torch.randn((R, C), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    w = (torch.randn((V, C), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    tg = torch.randint(0, V, (R,), generator=g, device=device, dtype=torch.int64)
+    return x, w, tg

@@ -1,0 +1,188 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the
+header declares, and rejects bad inputs with the reference's error kinds before
+touching CUDA.  Mirrors the reference's panic tests (wkv7/mod.rs:329-336,
+mix6/mod.rs:248-257, token_shift_diff/mod.rs:330-347)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    header = open(os.path.join(ROOT, "include", "rwkv7_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    names = set(re.findall(r"\b(rwkv7_[a-z0-9_]+)\s*\(", header))
+    assert len(names) >= 18
+    L = pkg.lib()
+    for n in sorted(names):
+        assert hasattr(L, n), f"librwkv7_b200.so does not export {n}"
+    assert L.rwkv7_abi_version() == 1
+    assert L.rwkv7_status_string(2) == b"ShapeMismatch"
+
+
+def test_tensor_struct_layout(pkg):
+    # data(8) dtype device ndim reserved (4x4) shape[5] stride[5] (2x40)
+    assert ctypes.sizeof(pkg.Tensor) == 8 + 16 + 40 + 40
+
+
+def _seq(pkg, shape, dtype=torch.float32, chunk_len=16):
+    t = [torch.zeros(shape, dtype=dtype) for _ in range(6)]
+    return pkg.Wkv7PretrainForwardInputs(*t, chunk_len=chunk_len)
+
+
+def test_wkv7_panics_on_wrong_context_len(pkg):
+    """wkv7/mod.rs:329-336: T = 15 is rejected by the reference contract."""
+    with pytest.raises(pkg.KernelInputsError, match="multiple of chunk_len"):
+        pkg.wkv7_pretrain_custom(_seq(pkg, (1, 15, 1, 4)))
+    with pytest.raises(pkg.KernelInputsError, match="chunk_len=16"):
+        pkg.wkv7_pretrain_custom(_seq(pkg, (1, 16, 1, 4), chunk_len=32))
+
+
+def test_wkv7_contract_errors(pkg):
+    E = pkg.KernelInputsError
+    seq = _seq(pkg, (2, 16, 2, 8))
+    seq.value = torch.zeros(2, 16, 2, 4)
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(seq)
+    assert e.value.kind == "ShapeMismatch" and "value" in str(e.value)
+    assert "expected=[2, 16, 2, 8], actual=[2, 16, 2, 4]" in str(e.value)
+
+    seq = _seq(pkg, (2, 16, 2, 8))
+    seq.replacement = torch.zeros(3, 16, 2, 8)
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(seq)
+    assert e.value.kind == "AxisMismatch"
+    assert "receptance[0]=2 != replacement[0]=3" in str(e.value)
+
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(_seq(pkg, (2, 0, 2, 8)), reference_contract=False)
+    assert e.value.kind == "EmptyAxis" and "receptance[1]" in str(e.value)
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(_seq(pkg, (2, 16, 2, 0)))
+    assert e.value.kind == "EmptyAxis" and "receptance[3]" in str(e.value)
+
+    seq = _seq(pkg, (2, 16, 2, 8))
+    seq.weight_decay = torch.zeros(2, 16, 2, 8, dtype=torch.bfloat16)
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(seq)
+    assert e.value.kind == "DTypeMismatch" and "weight_decay=BF16" in str(e.value)
+
+    seq = _seq(pkg, (2, 16, 2, 8))
+    seq.receptance = torch.zeros(2, 16, 8, 2).transpose(2, 3)
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(seq)
+    assert e.value.kind == "NotContiguous" and "receptance" in str(e.value)
+
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(_seq(pkg, (1, 16, 1, 4), chunk_len=0), reference_contract=False)
+    assert e.value.kind == "BadChunk"
+
+    # initial_state must be [B,H,N,N] (check_initial_state, wkv7/io.rs:243-258)
+    with pytest.raises(E) as e:
+        pkg.wkv7_statepass_custom(torch.zeros(2, 2, 8, 4), _seq(pkg, (2, 16, 2, 8)))
+    assert e.value.kind == "ShapeMismatch" and "initial_state" in str(e.value)
+    with pytest.raises(E) as e:
+        pkg.wkv7_statetune_custom(torch.zeros(2, 2, 8, 8, dtype=torch.bfloat16), _seq(pkg, (2, 16, 2, 8)))
+    assert e.value.kind == "DTypeMismatch"
+
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(_seq(pkg, (1, 16, 1, 8), dtype=torch.float16))
+    assert e.value.kind == "Unsupported"
+
+
+def test_wkv7_device_mismatch_is_reported(pkg):
+    seq = _seq(pkg, (1, 16, 1, 4))
+    six = [pkg.describe(t, device=0) for t in seq.six()]
+    six[3].device = 1
+    y = pkg.describe(torch.zeros(1, 16, 1, 4), device=0)
+    st = pkg.lib().rwkv7_fused_wkv7_pretrain(*[ctypes.byref(d) for d in six], ctypes.c_int64(16),
+                                             ctypes.byref(y), None, ctypes.c_size_t(0), None)
+    assert st == 4
+    assert b"DeviceMismatch" in pkg.lib().rwkv7_last_error_message()
+
+
+def test_null_descriptor(pkg):
+    seq = _seq(pkg, (1, 16, 1, 4))
+    six = [pkg.describe(t, device=0) for t in seq.six()]
+    y = pkg.describe(torch.zeros(1, 16, 1, 4), device=0)
+    args = [ctypes.byref(d) for d in six]
+    args[2] = None
+    st = pkg.lib().rwkv7_fused_wkv7_pretrain(*args, ctypes.c_int64(16), ctypes.byref(y), None,
+                                             ctypes.c_size_t(0), None)
+    assert st == 9 and b"replacement_key" in pkg.lib().rwkv7_last_error_message()
+
+
+def test_mix6_panics_on_wrong_scale_shape(pkg):
+    """mix6/mod.rs:248-257: gate_scale [1,1,7] against C = 8."""
+    x = torch.zeros(2, 4, 8)
+    mus = [torch.zeros(1, 1, 8) for _ in range(5)] + [torch.zeros(1, 1, 7)]
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.mix6_custom(x, *mus)
+    assert e.value.kind == "ShapeMismatch" and "gate_scale" in str(e.value)
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.mix6_custom(torch.zeros(2, 4, 0), *[torch.zeros(1, 1, 0) for _ in range(6)])
+    assert e.value.kind == "EmptyAxis"
+
+
+def test_addcmul_contract_errors(pkg):
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.addcmul_custom(torch.zeros(2, 8, 32), torch.zeros(2, 8, 16), torch.zeros(1, 1, 32))
+    assert e.value.kind == "ShapeMismatch" and "diff" in str(e.value)
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.addcmul_custom(torch.zeros(2, 8, 32), torch.zeros(2, 8, 32), torch.zeros(32))
+    assert e.value.kind == "ShapeMismatch" and "scale" in str(e.value)
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.addcmul5_custom(torch.zeros(2, 8, 32), torch.zeros(2, 8, 32),
+                            *[torch.zeros(1, 1, 32) for _ in range(4)], torch.zeros(1, 1, 31))
+    assert e.value.kind == "ShapeMismatch" and "learning_rate_scale" in str(e.value)
+
+
+def test_token_shift_diff_shape_mismatch_panics(pkg):
+    """token_shift_diff/mod.rs:330-347: state [3,7] against C = 8."""
+    with pytest.raises(pkg.KernelInputsError, match="ShapeMismatch") as e:
+        pkg.token_shift_diff_custom(torch.zeros(2, 4, 8), torch.zeros(3, 7), torch.tensor([0, 1], dtype=torch.int32))
+    assert "embedded_token_shift" in str(e.value)
+    with pytest.raises(pkg.KernelInputsError, match="ShapeMismatch") as e:
+        pkg.token_shift_diff_custom(torch.zeros(2, 4, 8), torch.zeros(3, 8), torch.tensor([0], dtype=torch.int32))
+    assert "batch_ids" in str(e.value)
+
+
+def test_token_shift_diff_empty_context_is_noop(pkg):
+    """T == 0 returns without any CUDA call (token_shift_diff/mod.rs:88-97)."""
+    state = torch.rand(4, 8)
+    out = pkg.token_shift_diff_custom(torch.zeros(2, 0, 8), state, torch.tensor([3, 1], dtype=torch.int32))
+    assert out.token_shifted_diff.shape == (2, 0, 8)
+    assert torch.equal(out.next_token_shift, state)
+
+
+def test_lm_head_contract_errors(pkg):
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    w = torch.zeros(16, 32, dtype=torch.bfloat16)
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.lm_head_ce_partial(x, w, torch.zeros(4, dtype=torch.int64))
+    assert e.value.kind == "AxisMismatch"
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.lm_head_ce_partial(x.float(), torch.zeros(16, 64), torch.zeros(4, dtype=torch.int64))
+    assert e.value.kind == "Unsupported"
+
+
+def test_no_cpu_fallback(pkg):
+    """Valid inputs without a CUDA device must fail loudly, not compute on the host."""
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.wkv7_pretrain_custom(_seq(pkg, (1, 16, 1, 4)))
+    assert e.value.kind in ("CudaError", "BadArgument")
+
+
+def test_wkv7_path_switch(pkg):
+    assert pkg.get_wkv7_path() == pkg.WKV7_AUTO
+    pkg.set_wkv7_path(pkg.WKV7_SEQUENTIAL)
+    assert pkg.get_wkv7_path() == pkg.WKV7_SEQUENTIAL
+    pkg.set_wkv7_path(pkg.WKV7_AUTO)
+    with pytest.raises(pkg.KernelInputsError):
+        pkg.set_wkv7_path(9)
