@@ -68,7 +68,7 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
 template <typename T, int ROWS>
 __global__ void __launch_bounds__(ROWS * 4)
 wkv7_seq64_kernel(SeqPtrs ptrs, const float *__restrict__ s0, T *__restrict__ y,
-                  float *__restrict__ s_out, int Tlen, int H) {
+                  float *__restrict__ s_out, int Tlen, int H, const int *__restrict__ flags) {
     constexpr int THREADS = ROWS * 4;
     constexpr int SPLITS = kN / ROWS;
     constexpr int EPV = Vec16<T>::kElems;
@@ -81,6 +81,8 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *__restrict__ s0, T *__restrict__ y,
     float *ytile = vec + 2 * kTile * 6 * kN;                      // [2][kTile][ROWS]
 
     const int bh = blockIdx.x / SPLITS;
+    // Fallback mode: only the chains another kernel flagged are (re)computed.
+    if (flags != nullptr && flags[bh] == 0) return;
     const int split = blockIdx.x % SPLITS;
     const int bi = bh / H, h = bh % H;
     const int row0 = split * ROWS;
@@ -265,7 +267,7 @@ __global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *__restrict__ 
 }
 
 template <typename T, int ROWS>
-int launch_seq64(const Wkv7Args &p, cudaStream_t stream) {
+int launch_seq64(const Wkv7Args &p, cudaStream_t stream, const int *flags = nullptr) {
     SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
     const size_t smem = sizeof(float) * (2 * kTile * 6 * kN + 2 * kTile * ROWS);
     auto kern = wkv7_seq64_kernel<T, ROWS>;
@@ -273,7 +275,7 @@ int launch_seq64(const Wkv7Args &p, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     const unsigned grid = (unsigned)(p.B * p.H * (kN / ROWS));
     kern<<<grid, ROWS * 4, smem, stream>>>(ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out,
-                                           (int)p.T, (int)p.H);
+                                           (int)p.T, (int)p.H, flags);
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -309,6 +311,11 @@ int launch_seq(const Wkv7Args &p, cudaStream_t stream) {
 }
 
 }  // namespace
+
+// N == 64 only: recomputes the chains with flags[b*H+h] != 0, 16 value rows per CTA.
+int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStream_t stream) {
+    return p.bf16 ? launch_seq64<__nv_bfloat16, 16>(p, stream, flags) : launch_seq64<float, 16>(p, stream, flags);
+}
 
 int launch_wkv7_sequential(const Wkv7Args &p, cudaStream_t stream) {
     return p.bf16 ? launch_seq<__nv_bfloat16>(p, stream) : launch_seq<float>(p, stream);
