@@ -25,7 +25,8 @@ from typing import Optional, Sequence
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librwkv7_b200.so")
+# RWKV7_B200_LIB selects another build of the same library (e.g. an instrumented one).
+LIB_PATH = os.environ.get("RWKV7_B200_LIB") or os.path.join(_HERE, "librwkv7_b200.so")
 
 MAX_DIMS = 5
 F32, BF16, F16, I32, I64, U32 = 0, 1, 2, 3, 4, 5

@@ -26,6 +26,9 @@
 // All MMAs are M = 128.  Where only 64 rows are meaningful the other 64 rows of
 // the A operand alias neighbouring shared memory and the matching accumulator
 // lanes are never read.
+//
+// One CTA of 16 warps per (b,h).  Warp w reads TMEM lanes 32*(w%4).. and, among
+// the four warps that share a lane quarter, column group w/4.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -46,11 +49,11 @@ using namespace sm100;
 
 constexpr int kN = 64;   // head size
 constexpr int kL = 64;   // chunk length
-constexpr int kThreads = 128;
+constexpr int kThreads = 512;
 constexpr float kMaxLogDecay = 80.f;
 
 // Shared-memory map (bytes from a 1024-aligned base).
-constexpr uint32_t kRawBytes = 6 * kL * kN * 2;        // six bf16 tiles
+constexpr uint32_t kRawBytes = 6 * kL * kN * 2;        // six bf16 tiles; scratch after phase A
 constexpr uint32_t kOffRaw = 0;
 constexpr uint32_t kOffAR = kOffRaw + kRawBytes;        // [At;Rt]        128 x 64 fp32
 constexpr uint32_t kOffBK = kOffAR + 32768;             // [Bh;Kh]        128 x 64, later [T;A_rb]
@@ -58,14 +61,40 @@ constexpr uint32_t kOffZT = kOffBK + 32768;             // [Bh^T;Kh^T]    128 x 
 constexpr uint32_t kOffS = kOffZT + 32768;              // S [i][j]       64 x 64
 constexpr uint32_t kOffVT = kOffS + 16384;              // V^T [i][s]     64 x 64
 constexpr uint32_t kOffAKRK = kOffVT + 16384;           // [A_ak;A_rk]    128 x 64
-constexpr uint32_t kOffXU = kOffAKRK + 32768;           // A_ab, then X^T, then U^T   64 x 64
+constexpr uint32_t kOffXU = kOffAKRK + 32768;           // group sums, then X^T, then U^T   64 x 64
 constexpr uint32_t kOffMisc = kOffXU + 16384;
 constexpr uint32_t kMiscBytes = 1024;
 constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 
+// fp32 scratch matrices of the triangular inverse, row pitch 68 floats, inside the
+// raw-tile region (free between phase A and the next TMA request).
+constexpr int kPitch = 68;
+constexpr uint32_t kOffAm = kOffRaw;                          // A_ab   [64][68]
+constexpr uint32_t kOffTm = kOffAm + 64 * kPitch * 4;         // T      [64][68]
+constexpr uint32_t kOffPm = kOffTm + 64 * kPitch * 4;         // P      [32][68]
+static_assert(kOffPm + 32 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
+
 // TMEM columns.
 constexpr uint32_t kColG = 0, kColXY = 128, kColU = 192, kColZ = 256, kTmemCols = 512;
+
+// Optional per-phase cycle counters (development builds only): thread 0 of CTA 0
+// adds the cycles spent since the previous mark to the slot of the phase that
+// just ended.
+#ifdef RWKV7_PHASE_CLOCKS
+__device__ long long g_phase_clocks[16];
+#define PHASE(k)                                                        \
+    do {                                                                \
+        if (blockIdx.x == 0 && threadIdx.x == 0) {                      \
+            const long long now_ = clock64();                           \
+            g_phase_clocks[phase_prev_] += now_ - phase_t_;             \
+            phase_t_ = now_;                                            \
+            phase_prev_ = (k);                                          \
+        }                                                               \
+    } while (0)
+#else
+#define PHASE(k) do {} while (0)
+#endif
 
 struct TmaMaps {
     CUtensorMap m[6];  // r, w, k, v, a, b as [B*T, H*N] bf16, box 64 x 64
@@ -81,15 +110,56 @@ __device__ __forceinline__ float bf16_at(const unsigned char *raw, int tensor, i
 __device__ __forceinline__ void st_tile(unsigned char *tile, int rows, int row, int col, float v) {
     *reinterpret_cast<float *>(tile + tile_off_f32(rows, row, col)) = v;
 }
+__device__ __forceinline__ void st_tile4(unsigned char *tile, int rows, int row, int col, float4 v) {
+    *reinterpret_cast<float4 *>(tile + tile_off_f32(rows, row, col)) = v;
+}
 
 // Issues the 8 K-steps of one 128 x N x 64 tf32 product, both operands K-major.
-__device__ __forceinline__ void mma_k64(uint32_t d_tmem, uint32_t a_addr, int a_rows, uint32_t b_addr, int b_rows,
-                                        int N, bool accumulate) {
-    const uint32_t idesc = make_idesc(kFmtTF32, 128, N, false, false);
+// a0 / b0 are the descriptors of K-step 0; later steps only move the start address.
+template <int A_ROWS, int B_ROWS, int N>
+__device__ __forceinline__ void mma_k64(uint32_t d_tmem, uint64_t a0, uint64_t b0, bool accumulate) {
+    constexpr uint32_t idesc = make_idesc(kFmtTF32, 128, N, false, false);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-        umma_tf32(d_tmem, desc_kmajor(a_addr, a_rows, ks), desc_kmajor(b_addr, b_rows, ks), idesc,
-                  accumulate || ks > 0);
+    for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t ao = (uint64_t)(((ks >> 2) * A_ROWS * 128 + (ks & 3) * 32) >> 4);
+        const uint64_t bo = (uint64_t)(((ks >> 2) * B_ROWS * 128 + (ks & 3) * 32) >> 4);
+        umma_tf32(d_tmem, a0 + ao, b0 + bo, idesc, accumulate || ks > 0);
+    }
+}
+
+// 2x2 output tile: rows P0, P1 against columns Q[.][0], Q[.][1] (Q 8-byte aligned).
+template <int K>
+__device__ __forceinline__ void dot_2x2(const float *P0, const float *P1, const float *Q, float (&o)[4]) {
+    float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;
+#pragma unroll
+    for (int k4 = 0; k4 < K / 4; ++k4) {
+        const float4 p0 = *reinterpret_cast<const float4 *>(P0 + 4 * k4);
+        const float4 p1 = *reinterpret_cast<const float4 *>(P1 + 4 * k4);
+        const float x0[4] = {p0.x, p0.y, p0.z, p0.w}, x1[4] = {p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 q = *reinterpret_cast<const float2 *>(Q + (4 * k4 + e) * kPitch);
+            a00 = fmaf(x0[e], q.x, a00);
+            a01 = fmaf(x0[e], q.y, a01);
+            a10 = fmaf(x1[e], q.x, a10);
+            a11 = fmaf(x1[e], q.y, a11);
+        }
+    }
+    o[0] = a00; o[1] = a01; o[2] = a10; o[3] = a11;
+}
+
+template <int K>
+__device__ __forceinline__ float dot_rows(const float *P_row, const float *Q_col) {
+    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int k4 = 0; k4 < K / 4; ++k4) {
+        const float4 p = *reinterpret_cast<const float4 *>(P_row + 4 * k4);
+        acc0 = fmaf(p.x, Q_col[(4 * k4 + 0) * kPitch], acc0);
+        acc1 = fmaf(p.y, Q_col[(4 * k4 + 1) * kPitch], acc1);
+        acc0 = fmaf(p.z, Q_col[(4 * k4 + 2) * kPitch], acc0);
+        acc1 = fmaf(p.w, Q_col[(4 * k4 + 3) * kPitch], acc1);
+    }
+    return acc0 + acc1;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -100,14 +170,19 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char *raw = smem + kOffRaw, *tAR = smem + kOffAR, *tBK = smem + kOffBK, *tZT = smem + kOffZT,
                   *tS = smem + kOffS, *tVT = smem + kOffVT, *tAKRK = smem + kOffAKRK, *tXU = smem + kOffXU;
+    float *Am = reinterpret_cast<float *>(smem + kOffAm);
+    float *Tm = reinterpret_cast<float *>(smem + kOffTm);
+    float *Pm = reinterpret_cast<float *>(smem + kOffPm);
+    float *grp_tot = reinterpret_cast<float *>(tXU);  // [8][64], phase A only
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc + 16);
     float *exp_cl = reinterpret_cast<float *>(smem + kOffMisc + 64);   // [64] exp(c_L)
-    float *tot0 = exp_cl + 64;                                         // [64] sum of l over the first half
-    int *unsafe = reinterpret_cast<int *>(tot0 + 64);
+    int *unsafe = reinterpret_cast<int *>(exp_cl + 64);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = warp & 3;   // TMEM lane quarter this warp may read
+    const int cgrp = warp >> 2;     // column group among the four warps of a quarter
     const int bh = blockIdx.x;
     const int bi = bh / H, h = bh % H;
     const int nchunks = (Tlen + kL - 1) / kL;
@@ -125,7 +200,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
 
     auto issue_tma = [&](int chunk) {
         mbar_expect_tx(bar_tma, kRawBytes);
@@ -135,13 +210,28 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
     };
     if (tid == 0) issue_tma(0);
 
-    // fp32 state: thread j (< 64) holds Z[j][i] = S[i][j] for all i.
-    float Z[kN];
-    if (tid < kN) {
+    // fp32 state: the thread at TMEM lane j (< 64), column group g holds
+    // Z[j][16g .. 16g+15] = S[16g + e][j].
+    const int zj = quarter * 32 + lane;  // meaningful for quarter < 2
+    float Z[16];
+    if (quarter < 2) {
 #pragma unroll
-        for (int i = 0; i < kN; ++i) Z[i] = s0 ? s0[((size_t)bh * kN + i) * kN + tid] : 0.f;
+        for (int e = 0; e < 16; ++e) {
+            const int i = cgrp * 16 + e;
+            Z[e] = s0 ? s0[((size_t)bh * kN + i) * kN + zj] : 0.f;
+            st_tile(tS, 64, i, zj, round_tf32(Z[e]));
+        }
     }
 
+#ifdef RWKV7_PHASE_CLOCKS
+    long long phase_t_ = clock64();
+    int phase_prev_ = 15;
+#endif
+    // K-step-0 descriptors of every operand tile (constant for the whole kernel).
+    const uint64_t dAR = desc_kmajor(smem_u32(tAR), 128, 0), dBK = desc_kmajor(smem_u32(tBK), 128, 0),
+                   dZT = desc_kmajor(smem_u32(tZT), 128, 0), dZTk = desc_kmajor(smem_u32(tZT) + 64 * 128, 128, 0),
+                   dS = desc_kmajor(smem_u32(tS), 64, 0), dVT = desc_kmajor(smem_u32(tVT), 64, 0),
+                   dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0), dXU = desc_kmajor(smem_u32(tXU), 64, 0);
     uint32_t mma_phase = 0;
     bool failed = false;
     int tma_issued = 1, tma_consumed = 0;  // tile batches requested / received
@@ -149,74 +239,77 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
     for (int chunk = 0; chunk < nchunks; ++chunk) {
         const int valid = min(kL, Tlen - chunk * kL);
         // ---------------- wait for this chunk's six input tiles
+        PHASE(0);
         {
             const bool ok = mbar_wait(bar_tma, (uint32_t)(chunk & 1));
             if (__syncthreads_or(!ok)) { failed = true; break; }
             ++tma_consumed;
         }
         // ---------------- phase A: decay prefix sums and scaled operands
+        PHASE(1);
         {
-            const int j = tid & 63, half = tid >> 6;
-            const int t0 = half * 32;
-            float l[32];
+            const int j = tid & 63, tg = tid >> 6;  // channel, group of 8 tokens
+            const int t0 = tg * 8;
+            float c[8];
             float sum = 0.f;
 #pragma unroll
-            for (int u = 0; u < 32; ++u) {
-                const int t = t0 + u;
-                const float lw = (t < valid) ? -__expf(bf16_at(raw, TW, t, j)) : 0.f;
+            for (int u = 0; u < 8; ++u) {
+                const float lw = (t0 + u < valid) ? -__expf(bf16_at(raw, TW, t0 + u, j)) : 0.f;
                 sum += lw;
-                l[u] = sum;  // inclusive prefix inside this half
+                c[u] = sum;  // inclusive prefix inside this group
             }
-            if (half == 0) tot0[j] = sum;
+            grp_tot[tg * 64 + j] = sum;
             __syncthreads();
-            const float base = half ? tot0[j] : 0.f;
-            const float c_last = base + sum;
-            if (half == 1) {
-                exp_cl[j] = __expf(c_last);
-                if (c_last < -kMaxLogDecay) *unsafe = 1;
+            float base = 0.f, total = 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const float x = grp_tot[g * 64 + j];
+                total += x;
+                if (g < tg) base += x;
+            }
+            if (tg == 7) {
+                exp_cl[j] = __expf(total);
+                if (total < -kMaxLogDecay) *unsafe = 1;
             }
             float e_prev = __expf(base);  // exp(c_{t0-1})
+            float bhv[8], khv[8], vv[8];
 #pragma unroll
-            for (int u = 0; u < 32; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int t = t0 + u;
                 const bool live = t < valid;
-                const float e = __expf(base + l[u]);   // exp(c_t)
+                const float e = __expf(base + c[u]);   // exp(c_t)
                 const float einv = __frcp_rn(e);        // exp(-c_t)
                 const float a = live ? bf16_at(raw, TA, t, j) : 0.f;
                 const float r = live ? bf16_at(raw, TR, t, j) : 0.f;
                 const float b = live ? bf16_at(raw, TB, t, j) : 0.f;
                 const float k = live ? bf16_at(raw, TK, t, j) : 0.f;
-                const float v = live ? bf16_at(raw, TV, t, j) : 0.f;
-                const float bh_ = round_tf32(b * einv), kh_ = round_tf32(k * einv);
+                vv[u] = live ? bf16_at(raw, TV, t, j) : 0.f;  // bf16 values are tf32-exact
+                bhv[u] = round_tf32(b * einv);
+                khv[u] = round_tf32(k * einv);
                 st_tile(tAR, 128, t, j, round_tf32(a * e_prev));
                 st_tile(tAR, 128, 64 + t, j, round_tf32(r * e));
-                st_tile(tBK, 128, t, j, bh_);
-                st_tile(tBK, 128, 64 + t, j, kh_);
-                st_tile(tZT, 128, j, t, bh_);        // Bh^T [j][t]
-                st_tile(tZT, 128, 64 + j, t, kh_);   // Kh^T [j][t]
-                st_tile(tVT, 64, j, t, v);           // V^T [i][s]  (bf16 values are tf32-exact)
+                st_tile(tBK, 128, t, j, bhv[u]);
+                st_tile(tBK, 128, 64 + t, j, khv[u]);
                 e_prev = e;
             }
-        }
-        __syncthreads();  // every read of the raw tiles is done
-        if (*unsafe) { failed = true; break; }
-        if (chunk + 1 < nchunks) {
-            if (tid == 0) issue_tma(chunk + 1);
-            ++tma_issued;
-        }
-        // state -> S operand tile [i][j], tf32-rounded
-        if (tid < kN) {
+            // transposed copies: Bh^T, Kh^T [j][t] and V^T [i][s], 8 consecutive tokens per thread
 #pragma unroll
-            for (int i = 0; i < kN; ++i) st_tile(tS, 64, i, tid, round_tf32(Z[i]));
+            for (int q4 = 0; q4 < 2; ++q4) {
+                st_tile4(tZT, 128, j, t0 + 4 * q4, make_float4(bhv[4 * q4], bhv[4 * q4 + 1], bhv[4 * q4 + 2], bhv[4 * q4 + 3]));
+                st_tile4(tZT, 128, 64 + j, t0 + 4 * q4, make_float4(khv[4 * q4], khv[4 * q4 + 1], khv[4 * q4 + 2], khv[4 * q4 + 3]));
+                st_tile4(tVT, 64, j, t0 + 4 * q4, make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]));
+            }
         }
         fence_proxy_async();
-        __syncthreads();
+        __syncthreads();  // operands visible to the tensor core; raw tiles and group sums are dead
+        if (*unsafe) { failed = true; break; }
         // ---------------- M1: G = [At;Rt] [Bh;Kh]^T ; state-independent part of Z
+        PHASE(3);
         if (tid == 0) {
             tc_fence_after();
-            mma_k64(tmem + kColG, smem_u32(tAR), 128, smem_u32(tBK), 128, 128, false);
+            mma_k64<128, 128, 128>(tmem + kColG, dAR, dBK, false);
             // Z = Kh^T V : A = rows 64..127 of the [Bh^T;Kh^T] stack
-            mma_k64(tmem + kColZ, smem_u32(tZT) + 64 * 128, 128, smem_u32(tVT), 64, 64, false);
+            mma_k64<128, 64, 64>(tmem + kColZ, dZTk, dVT, false);
             umma_commit(bar_mma);
         }
         {
@@ -225,77 +318,127 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
             if (__syncthreads_or(!ok)) { failed = true; break; }
         }
         tc_fence_after();
-        // ---------------- hop 1: G -> masked A_ab (fp32), A_ak, A_rb, A_rk (tf32)
+        // ---------------- hop 1: G -> masked A_ab (fp32 scratch), A_ak, A_rb, A_rk (tf32 tiles)
+        PHASE(4);
         {
-            const bool upper = tid >= 64;         // Rt rows: inclusive lower triangle
-            const int t = tid & 63;
-            const int lim = upper ? t : t - 1;    // keep s <= lim
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + kColG + q * 32, v);
-                tmem_ld_wait();
-                const int s0c = (q & 1) * 32;     // column offset inside the 64-wide quadrant
-                // q = 0,1: against Bh (A_ab / A_rb) ; q = 2,3: against Kh (A_ak / A_rk)
-                unsigned char *dst;
-                int rows, row;
-                bool exact = false;
-                if (q < 2) {
-                    if (!upper) { dst = tXU; rows = 64; row = t; exact = true; }       // A_ab plain fp32
-                    else        { dst = tBK; rows = 128; row = 64 + t; }               // A_rb under T
-                } else {
-                    dst = tAKRK; rows = 128; row = upper ? 64 + t : t;                 // A_ak / A_rk
-                }
+            const bool upper = quarter >= 2;          // Rt rows: inclusive lower triangle
+            const int t = (quarter & 1) * 32 + lane;
+            const int lim = upper ? t : t - 1;        // keep s <= lim
+            const int s_base = (cgrp & 1) * 32;       // column offset inside the 64-wide quadrant
+            uint32_t v[32];
+            tmem_ld32(tmem + lane_base + kColG + cgrp * 32, v);
+            tmem_ld_wait();
+            if (cgrp < 2 && !upper) {
+                // A_ab: exact fp32 into the inverse's scratch matrix
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     float4 o;
                     float *of = &o.x;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int s = s0c + e4 * 4 + e;
-                        float x = __uint_as_float(v[e4 * 4 + e]);
-                        x = (s <= lim) ? x : 0.f;
-                        of[e] = exact ? x : round_tf32(x);
+                        const int s = s_base + e4 * 4 + e;
+                        of[e] = (s <= lim) ? __uint_as_float(v[e4 * 4 + e]) : 0.f;
                     }
-                    *reinterpret_cast<float4 *>(dst + tile_off_f32(rows, row, s0c + e4 * 4)) = o;
+                    *reinterpret_cast<float4 *>(Am + t * kPitch + s_base + e4 * 4) = o;
+                }
+            } else {
+                unsigned char *dst = (cgrp < 2) ? tBK : tAKRK;   // A_rb under T, or [A_ak;A_rk]
+                const int row = upper ? 64 + t : t;
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    float4 o;
+                    float *of = &o.x;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int s = s_base + e4 * 4 + e;
+                        of[e] = (s <= lim) ? round_tf32(__uint_as_float(v[e4 * 4 + e])) : 0.f;
+                    }
+                    st_tile4(dst, 128, row, s_base + e4 * 4, o);
                 }
             }
         }
         tc_fence_before();
         __syncthreads();
-        // ---------------- T = (I - A_ab)^-1 by forward substitution, two threads per column
-        {
-            // Thread (c, p) keeps T[s][c] for s % 4 in {2p, 2p+1} and sums its half of
-            // every dot product; A_ab is strictly lower triangular, so entries with
-            // s >= t are zero in shared memory and need no predicate.
-            const int c = tid >> 1, p = tid & 1;
-            float Tc[32];  // T[4*q + 2*p + e][c] at index 2*q + e
+        // ---------------- T = (I - A_ab)^-1, blocked: 16x16 diagonal blocks by forward
+        // substitution, then the off-diagonal blocks T_ba = T_bb A_ba T_aa at block
+        // sizes 16 and 32.  All in fp32 on the scratch matrices.
+        PHASE(5);
+        if (tid < 64) {
+            const int b = tid >> 4, cc = tid & 15;
+            const float *Ab = Am + (16 * b) * kPitch + 16 * b;
+            float x[16];
 #pragma unroll
-            for (int q = 0; q < 32; ++q) Tc[q] = 0.f;
-#pragma unroll
-            for (int t = 0; t < kL; ++t) {
+            for (int t = 0; t < 16; ++t) {
                 float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
                 for (int s4 = 0; s4 < (t + 3) / 4; ++s4) {
-                    const float2 a2 =
-                        *reinterpret_cast<const float2 *>(tXU + tile_off_f32(64, t, s4 * 4) + p * 8);
-                    acc0 = fmaf(a2.x, Tc[2 * s4], acc0);
-                    acc1 = fmaf(a2.y, Tc[2 * s4 + 1], acc1);
+                    const float4 a4 = *reinterpret_cast<const float4 *>(Ab + t * kPitch + 4 * s4);
+                    if (4 * s4 + 0 < t) acc0 = fmaf(a4.x, x[4 * s4 + 0], acc0);
+                    if (4 * s4 + 1 < t) acc1 = fmaf(a4.y, x[4 * s4 + 1], acc1);
+                    if (4 * s4 + 2 < t) acc0 = fmaf(a4.z, x[4 * s4 + 2], acc0);
+                    if (4 * s4 + 3 < t) acc1 = fmaf(a4.w, x[4 * s4 + 3], acc1);
                 }
-                float acc = acc0 + acc1;
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                const float val = (t == c) ? 1.f : ((t > c) ? acc : 0.f);
-                if (((t & 3) >> 1) == p) Tc[2 * (t >> 2) + (t & 1)] = val;
-                if (p == 0) st_tile(tBK, 128, t, c, round_tf32(val));
+                x[t] = (t == cc) ? 1.f : ((t > cc) ? acc0 + acc1 : 0.f);
+                Tm[(16 * b + t) * kPitch + 16 * b + cc] = x[t];
             }
         }
-        fence_proxy_async();
         __syncthreads();
+        PHASE(13);
+        {   // block size 16: P = A_ba T_aa for (a,b) = (0,1) and (2,3)
+            const int sb = tid >> 8, r = (tid >> 4) & 15, cc = tid & 15;
+            const int a0 = 32 * sb, b0 = a0 + 16;
+            Pm[(16 * sb + r) * kPitch + cc] = dot_rows<16>(Am + (b0 + r) * kPitch + a0, Tm + a0 * kPitch + a0 + cc);
+            Tm[(a0 + r) * kPitch + b0 + cc] = 0.f;  // block above the diagonal, read by the 32-wide products
+        }
+        __syncthreads();
+        {   // T_ba = T_bb P
+            const int sb = tid >> 8, r = (tid >> 4) & 15, cc = tid & 15;
+            const int a0 = 32 * sb, b0 = a0 + 16;
+            Tm[(b0 + r) * kPitch + a0 + cc] = dot_rows<16>(Tm + (b0 + r) * kPitch + b0, Pm + (16 * sb) * kPitch + cc);
+        }
+        __syncthreads();
+        PHASE(14);
+        if (tid < 256) {   // block size 32: P = A_BA T_AA, a 2x2 output tile per thread
+            const int r = 2 * (tid >> 4), cc = 2 * (tid & 15);
+            float o[4];
+            dot_2x2<32>(Am + (32 + r) * kPitch, Am + (33 + r) * kPitch, Tm + cc, o);
+            *reinterpret_cast<float2 *>(Pm + r * kPitch + cc) = make_float2(o[0], o[1]);
+            *reinterpret_cast<float2 *>(Pm + (r + 1) * kPitch + cc) = make_float2(o[2], o[3]);
+        } else {           // meanwhile: the finished blocks T_AA, T_BB -> tf32 operand tile rows 0..63
+#pragma unroll
+            for (int rep = 0; rep < 3; ++rep) {
+                const int idx = (tid - 256) + 256 * rep;
+                const int t = idx < 512 ? (idx >> 4) : 32 + ((idx - 512) >> 3);
+                const int cb = idx < 512 ? 4 * (idx & 15) : 32 + 4 * ((idx - 512) & 7);
+                const float4 x = *reinterpret_cast<const float4 *>(Tm + t * kPitch + cb);
+                float4 o;
+                o.x = (cb + 0 <= t) ? round_tf32(x.x) : 0.f;
+                o.y = (cb + 1 <= t) ? round_tf32(x.y) : 0.f;
+                o.z = (cb + 2 <= t) ? round_tf32(x.z) : 0.f;
+                o.w = (cb + 3 <= t) ? round_tf32(x.w) : 0.f;
+                st_tile4(tBK, 128, t, cb, o);
+            }
+        }
+        __syncthreads();
+        if (tid < 256) {   // T_BA = T_BB P, written straight into the operand tile
+            const int r = 2 * (tid >> 4), cc = 2 * (tid & 15);
+            float o[4];
+            dot_2x2<32>(Tm + (32 + r) * kPitch + 32, Tm + (33 + r) * kPitch + 32, Pm + cc, o);
+            *reinterpret_cast<float2 *>(tBK + tile_off_f32(128, 32 + r, cc)) = make_float2(round_tf32(o[0]), round_tf32(o[1]));
+            *reinterpret_cast<float2 *>(tBK + tile_off_f32(128, 33 + r, cc)) = make_float2(round_tf32(o[2]), round_tf32(o[3]));
+        }
+        fence_proxy_async();
+        __syncthreads();  // scratch matrices are dead: the raw-tile region may be refilled
+        if (chunk + 1 < nchunks) {
+            if (tid == 32) issue_tma(chunk + 1);   // not the thread that issues the MMAs
+            ++tma_issued;
+        }
         // ---------------- M2: XY = [A_ak;A_rk] V + [At;Rt] Z0
+        PHASE(6);
         if (tid == 0) {
             tc_fence_after();
-            mma_k64(tmem + kColXY, smem_u32(tAKRK), 128, smem_u32(tVT), 64, 64, false);
-            mma_k64(tmem + kColXY, smem_u32(tAR), 128, smem_u32(tS), 64, 64, true);
+            mma_k64<128, 64, 64>(tmem + kColXY, dAKRK, dVT, false);
+            mma_k64<128, 64, 64>(tmem + kColXY, dAR, dS, true);
             umma_commit(bar_mma);
         }
         {
@@ -305,23 +448,22 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
         }
         tc_fence_after();
         // ---------------- hop 2: X (lanes 0..63) -> X^T [i][t]
-        if (tid < 64) {
+        PHASE(7);
+        if (quarter < 2) {
+            uint32_t v[16];
+            tmem_ld16(tmem + lane_base + kColXY + cgrp * 16, v);
+            tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + kColXY + q * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) st_tile(tXU, 64, q * 32 + e, tid, round_tf32(__uint_as_float(v[e])));
-            }
+            for (int e = 0; e < 16; ++e) st_tile(tXU, 64, cgrp * 16 + e, zj, round_tf32(__uint_as_float(v[e])));
         }
         tc_fence_before();
         fence_proxy_async();
         __syncthreads();
         // ---------------- M3: U = T X
+        PHASE(8);
         if (tid == 0) {
             tc_fence_after();
-            mma_k64(tmem + kColU, smem_u32(tBK), 128, smem_u32(tXU), 64, 64, false);
+            mma_k64<128, 64, 64>(tmem + kColU, dBK, dXU, false);
             umma_commit(bar_mma);
         }
         {
@@ -331,24 +473,23 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
         }
         tc_fence_after();
         // ---------------- hop 3: U (lanes 0..63) -> U^T [i][t]   (M3 has finished reading X^T)
-        if (tid < 64) {
+        PHASE(9);
+        if (quarter < 2) {
+            uint32_t v[16];
+            tmem_ld16(tmem + lane_base + kColU + cgrp * 16, v);
+            tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + kColU + q * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) st_tile(tXU, 64, q * 32 + e, tid, round_tf32(__uint_as_float(v[e])));
-            }
+            for (int e = 0; e < 16; ++e) st_tile(tXU, 64, cgrp * 16 + e, zj, round_tf32(__uint_as_float(v[e])));
         }
         tc_fence_before();
         fence_proxy_async();
         __syncthreads();
         // ---------------- M4: XY[64..127] += A_rb U ; Z += Bh^T U
+        PHASE(10);
         if (tid == 0) {
             tc_fence_after();
-            mma_k64(tmem + kColXY, smem_u32(tBK), 128, smem_u32(tXU), 64, 64, true);
-            mma_k64(tmem + kColZ, smem_u32(tZT), 128, smem_u32(tXU), 64, 64, true);
+            mma_k64<128, 64, 64>(tmem + kColXY, dBK, dXU, true);
+            mma_k64<128, 64, 64>(tmem + kColZ, dZT, dXU, true);
             umma_commit(bar_mma);
         }
         {
@@ -358,37 +499,35 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
         }
         tc_fence_after();
         // ---------------- hop 4: state update (lanes 0..63) and y (lanes 64..127)
-        if (tid < 64) {
-            const float g = exp_cl[tid];
+        PHASE(11);
+        if (quarter < 2) {
+            const float g = exp_cl[zj];
+            uint32_t v[16];
+            tmem_ld16(tmem + lane_base + kColZ + cgrp * 16, v);
+            tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + kColZ + q * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) Z[q * 32 + e] = g * (Z[q * 32 + e] + __uint_as_float(v[e]));
+            for (int e = 0; e < 16; ++e) {
+                Z[e] = g * (Z[e] + __uint_as_float(v[e]));
+                st_tile(tS, 64, cgrp * 16 + e, zj, round_tf32(Z[e]));   // operand of the next chunk
             }
         } else {
-            const int t = tid - 64;
-            __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + t) * H + h) * kN;
+            const int t = (quarter - 2) * 32 + lane;
+            uint32_t v[16];
+            tmem_ld16(tmem + lane_base + kColXY + cgrp * 16, v);
+            tmem_ld_wait();
+            if (t < valid) {
+                __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + t) * H + h) * kN + cgrp * 16;
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + kColXY + q * 32, v);
-                tmem_ld_wait();
-                if (t < valid) {
+                for (int e8 = 0; e8 < 2; ++e8) {
+                    uint4 o;
+                    unsigned *ow = &o.x;
 #pragma unroll
-                    for (int e8 = 0; e8 < 4; ++e8) {
-                        uint4 o;
-                        unsigned *ow = &o.x;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[e8 * 8 + 2 * e]),
-                                                                            __uint_as_float(v[e8 * 8 + 2 * e + 1]));
-                            ow[e] = *reinterpret_cast<const unsigned *>(&h2);
-                        }
-                        *reinterpret_cast<uint4 *>(dst + q * 32 + e8 * 8) = o;
+                    for (int e = 0; e < 4; ++e) {
+                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[e8 * 8 + 2 * e]),
+                                                                        __uint_as_float(v[e8 * 8 + 2 * e + 1]));
+                        ow[e] = *reinterpret_cast<const unsigned *>(&h2);
                     }
+                    *reinterpret_cast<uint4 *>(dst + e8 * 8) = o;
                 }
             }
         }
@@ -397,14 +536,15 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restric
     }
 
     // ---------------- epilogue
+    PHASE(12);
     // A tile batch still in flight must land before the CTA gives up its shared memory.
     if (failed && tma_issued > tma_consumed) mbar_wait(bar_tma, (uint32_t)(tma_consumed & 1));
     const bool bad_decay = *unsafe != 0;
     if (failed && !bad_decay && tid == 0) atomicExch(status, (int)kDevTimeout);
     if (tid == 0) flags[bh] = bad_decay ? 1 : 0;
-    if (!failed && s_out != nullptr && tid < kN) {
+    if (!failed && s_out != nullptr && quarter < 2) {
 #pragma unroll
-        for (int i = 0; i < kN; ++i) s_out[((size_t)bh * kN + i) * kN + tid] = Z[i];
+        for (int e = 0; e < 16; ++e) s_out[((size_t)bh * kN + cgrp * 16 + e) * kN + zj] = Z[e];
     }
     tc_fence_before();
     __syncthreads();
@@ -432,6 +572,17 @@ EncodeTiledFn encode_fn() {
 }
 
 }  // namespace
+
+#ifdef RWKV7_PHASE_CLOCKS
+extern "C" int rwkv7_debug_phase_clocks(long long *out16, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out16, g_phase_clocks, sizeof(long long) * 16);
+    if (e == cudaSuccess && reset) {
+        long long zero[16] = {};
+        e = cudaMemcpyToSymbol(g_phase_clocks, zero, sizeof(zero));
+    }
+    return (int)e;
+}
+#endif
 
 size_t wkv7_chunked_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     (void)T;

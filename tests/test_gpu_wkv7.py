@@ -182,8 +182,9 @@ def test_state_carry_and_inplace(pkg, oracle, workloads, cuda):
         ys.append(out.output)
     torch.cuda.synchronize()
     y_cat = torch.cat(ys, 1).float().cpu().numpy()
-    # identical fp32 arithmetic per token, so the pieces agree to fp32 round-off
-    np.testing.assert_allclose(y_cat, y_all, rtol=0, atol=2 ** -8 * np.abs(y_all).max())
+    # the pieces take different kernels (sequential for T < 64, chunked otherwise):
+    # both are within 1e-3 of the exact result, and bf16 storage may flip one ulp
+    parity.assert_close_bf16_store(y_cat, y_all, 2e-3, "y pieces")
     parity.assert_close_f32(state.cpu().numpy(), s_all, 1e-3, "carried state")
 
 
