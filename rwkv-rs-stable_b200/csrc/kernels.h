@@ -32,6 +32,8 @@ struct Wkv7Args {
 // Token-by-token scan, fp32 state in registers (N == 64) or shared memory (any
 // N <= 128).  Also the decode (T == 1) sweep.
 int launch_wkv7_sequential(const Wkv7Args &p, cudaStream_t stream);
+// Decode sweep (N == 64, a few tokens): one pass over the fp32 state per call.
+int launch_wkv7_decode(const Wkv7Args &p, cudaStream_t stream);
 
 // Chunked tensor-core prefill (N == 64): tcgen05 MMAs with TMEM accumulators.
 size_t wkv7_chunked_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);

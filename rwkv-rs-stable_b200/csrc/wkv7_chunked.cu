@@ -163,8 +163,8 @@ __device__ __forceinline__ float dot_rows(const float *P_row, const float *Q_col
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *__restrict__ s0,
-                    __nv_bfloat16 *__restrict__ y, float *__restrict__ s_out, int *__restrict__ flags,
+wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
+                    __nv_bfloat16 *__restrict__ y, float *s_out, int *__restrict__ flags,
                     int Tlen, int H, int *status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));

@@ -67,8 +67,8 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
 
 template <typename T, int ROWS>
 __global__ void __launch_bounds__(ROWS * 4)
-wkv7_seq64_kernel(SeqPtrs ptrs, const float *__restrict__ s0, T *__restrict__ y,
-                  float *__restrict__ s_out, int Tlen, int H, const int *__restrict__ flags) {
+wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
+                  float *s_out, int Tlen, int H, const int *__restrict__ flags) {
     constexpr int THREADS = ROWS * 4;
     constexpr int SPLITS = kN / ROWS;
     constexpr int EPV = Vec16<T>::kElems;
@@ -217,8 +217,8 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *__restrict__ s0, T *__restrict__ y,
 // Any head size N <= 128: thread i owns state row i, kept in shared memory with
 // a padded row pitch; the six token vectors are staged per token.
 template <typename T>
-__global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *__restrict__ s0,
-                                        T *__restrict__ y, float *__restrict__ s_out, int Tlen,
+__global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *s0,
+                                        T *__restrict__ y, float *s_out, int Tlen,
                                         int H, int N) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int pitch = N + 1;
@@ -318,6 +318,8 @@ int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStre
 }
 
 int launch_wkv7_sequential(const Wkv7Args &p, cudaStream_t stream) {
+    // A handful of tokens per chain is the decode case: the state sweep dominates.
+    if (p.N == kN && p.T <= 4) return launch_wkv7_decode(p, stream);
     return p.bf16 ? launch_seq<__nv_bfloat16>(p, stream) : launch_seq<float>(p, stream);
 }
 
