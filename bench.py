@@ -172,7 +172,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--small", action="store_true",
-                    help="profiling case: B=2 instead of 8 (inputs still exceed L2 only partly)")
+                    help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -193,7 +193,7 @@ def main():
 
     cfg = dict(CFG1)
     if args.small:
-        cfg["B"] = 2
+        cfg["B"] = 4
     B, T, H, N = cfg["B"], cfg["T"], cfg["H"], cfg["N"]
     # each rank owns its own batch x head shard: a different seed, the same shape
     host = workloads.wkv7_inputs(B, T, H, N, seed=100 + rank, dtype=torch.bfloat16, device=dev)
