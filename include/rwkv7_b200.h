@@ -159,6 +159,38 @@ int rwkv7_fused_wkv7_statepass(const rwkv7_tensor *initial_state, const rwkv7_te
                                rwkv7_tensor *output, rwkv7_tensor *next_state, void *workspace,
                                size_t workspace_bytes, rwkv7_stream stream);
 
+/* This entry point has no counterpart in the reference.  It is
+ * rwkv7_fused_wkv7_statepass for callers that cannot allocate device memory at
+ * the moment they call in and therefore have no workspace to pass: for example a
+ * serving process whose own memory pool has already claimed the whole GPU, so that
+ * a cudaMalloc at call time would fail, or a host runtime in which a device
+ * allocation is not allowed on the calling thread because it would stall every
+ * stream of the device.  The per-chain fallback flags of the chunked kernel live
+ * in a fixed array inside the library image instead (256 KiB, held by every GPU
+ * that loads the library until the process exits), so the call itself performs no
+ * cudaMalloc / cudaFree and uses no allocating library routine.
+ *
+ * Limits and rules:
+ *  - B*H must not exceed 65536 chains; larger shapes return RWKV7_ERR_UNSUPPORTED.
+ *  - The first call on each device resolves the array's device address
+ *    (cudaGetSymbolAddress, with that device made current for the call); make
+ *    that first call before starting any stream capture on the device.
+ *  - All calls on a device share the one array and it keeps the previous call's
+ *    contents.  Nothing in it has to start at zero (every call overwrites the
+ *    flags of its own chains before reading them), but two calls whose GPU work
+ *    overlaps (different streams, or different host threads) race on it:
+ *    serialise calls to this entry point per device.
+ * Inputs, outputs and results are those of rwkv7_fused_wkv7_statepass. */
+int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *initial_state,
+                                       const rwkv7_tensor *receptance,
+                                       const rwkv7_tensor *weight_decay,
+                                       const rwkv7_tensor *replacement_key,
+                                       const rwkv7_tensor *value,
+                                       const rwkv7_tensor *removal_key_normalized,
+                                       const rwkv7_tensor *replacement, int64_t chunk_len,
+                                       rwkv7_tensor *output, rwkv7_tensor *next_state,
+                                       rwkv7_stream stream);
+
 /* ------------------------------------------------------------------ mix6 -- */
 /* Replaces Mix6Backend::fused_mix6 (mix6/mod.rs:25-28, impl :42-73; kernel
  * mix6/kernel.rs:25-57): prev = x[b,t-1,:] (0 at t == 0);

@@ -274,6 +274,24 @@ class Wkv7StatepassCall:
             _check(st)
 
 
+def wkv7_statepass_noalloc(initial_state: torch.Tensor, sequence: Wkv7PretrainForwardInputs,
+                           output: torch.Tensor, next_state: torch.Tensor) -> Wkv7StatepassForwardOutput:
+    """``rwkv7_fused_wkv7_statepass_noalloc``: the statepass for callers that must
+    not allocate device memory while calling (a server whose memory pool already
+    owns the GPU, a thread on which a device allocation would stall the device).
+    The caller passes every buffer, ``output`` and ``next_state`` included, and no
+    workspace: the library's own fixed 256 KiB flag array is used instead, which
+    limits ``B*H`` to 65536 chains.  Calls on one device must not overlap on the
+    GPU, since they share that array.  Nothing is allocated here either: the
+    descriptors are plain ctypes structures on the host."""
+    desc = [describe(initial_state)] + [describe(t) for t in sequence.six()]
+    yd, sd = describe(output), describe(next_state)
+    st = lib().rwkv7_fused_wkv7_statepass_noalloc(*[_ref(d) for d in desc], ctypes.c_int64(sequence.chunk_len),
+                                                  _ref(yd), _ref(sd), _stream(sequence.receptance))
+    _check(st)
+    return Wkv7StatepassForwardOutput(output=output, next_state=next_state)
+
+
 wkv7_pretrain = wkv7_pretrain_custom
 wkv7_statetune = wkv7_statetune_custom
 wkv7_statepass = wkv7_statepass_custom

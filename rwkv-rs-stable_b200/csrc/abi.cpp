@@ -298,6 +298,29 @@ int rwkv7_fused_wkv7_statepass(const rwkv7_tensor *s0, const rwkv7_tensor *r, co
     return wkv7_run(s0, six, chunk_len, output, next_state, true, workspace, workspace_bytes, stream, true);
 }
 
+int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *s0, const rwkv7_tensor *r, const rwkv7_tensor *w,
+                                       const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                                       const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
+                                       rwkv7_tensor *next_state, rwkv7_stream stream) {
+    clear_error();
+    if (r == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: tensor descriptor receptance is null");
+    if (r->ndim == 4) {
+        const int64_t chains = r->shape[0] * r->shape[2];
+        if (chains > wkv7_static_scratch_max_chains())
+            return fail(RWKV7_ERR_UNSUPPORTED,
+                        "Unsupported: B*H = %lld chains exceed the %lld-chain capacity of the allocation-free "
+                        "entry point; use rwkv7_fused_wkv7_statepass with a workspace",
+                        (long long)chains, (long long)wkv7_static_scratch_max_chains());
+    }
+    DeviceGuard guard(r->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    if (int e = wkv7_static_scratch(r->device, &scratch, &scratch_bytes)) return cuda_fail("static scratch address", e);
+    const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
+    return wkv7_run(s0, six, chunk_len, output, next_state, true, scratch, scratch_bytes, stream, true);
+}
+
 int rwkv7_fused_mix6(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6],
                      rwkv7_tensor *const outputs[6], rwkv7_stream stream) {
     clear_error();

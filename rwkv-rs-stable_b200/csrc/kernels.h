@@ -41,6 +41,12 @@ bool wkv7_chunked_supported(const Wkv7Args &p);
 int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream);
 
+// Fixed flag array inside the library image, usable in place of a workspace by
+// callers that must not allocate: device address (resolved on first use per
+// device, which must be current) and capacity.
+int wkv7_static_scratch(int device, void **ptr, size_t *bytes);
+int64_t wkv7_static_scratch_max_chains();
+
 struct MixArgs {
     const void *x;        // [B,T,C]
     const void *mu[6];    // [C] each

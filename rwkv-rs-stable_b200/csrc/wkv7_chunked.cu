@@ -584,6 +584,42 @@ extern "C" int rwkv7_debug_phase_clocks(long long *out16, int reset) {
 }
 #endif
 
+// ---- scratch that lives in the library image ----------------------------------------
+//
+// The fallback flags of the chunked kernel (one int per (b,h) chain) can also be
+// taken from this fixed array instead of a caller-provided workspace, for callers
+// that may not allocate device memory when they call in.  Every GPU that loads
+// the library holds the array (256 KiB) until the process exits.  In host code the
+// array's name is only a stand-in: the device address is resolved per device with
+// cudaGetSymbolAddress while that device is current.
+constexpr int64_t kStaticScratchChains = 65536;
+static __device__ __align__(256) int g_static_chain_flags[kStaticScratchChains];
+
+int64_t wkv7_static_scratch_max_chains() { return kStaticScratchChains; }
+
+// Resolves (once per device) and returns the device address of the static flag
+// array.  `device` must be the current device of the calling thread.
+int wkv7_static_scratch(int device, void **ptr, size_t *bytes) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int *cached[kMaxDevices] = {};
+    if (device < 0 || device >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[device] == nullptr) {
+        int current = -1;
+        cudaError_t e = cudaGetDevice(&current);
+        if (e != cudaSuccess) return (int)e;
+        if (current != device) return (int)cudaErrorInvalidDevice;
+        int *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_static_chain_flags);
+        if (e != cudaSuccess) return (int)e;
+        cached[device] = p;
+    }
+    *ptr = cached[device];
+    *bytes = sizeof(int) * (size_t)kStaticScratchChains;
+    return 0;
+}
+
 size_t wkv7_chunked_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     (void)T;
     if (N != kN) return 0;
