@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "sequential", "chunked"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-streaming", action="store_true")
+    ap.add_argument("--no-lm-head", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
     args = ap.parse_args()
@@ -297,6 +299,71 @@ def main():
                   "algorithmic_bytes": dbytes}
         del d, dseq, dy, dcall
 
+    # ---- token-shift mixing kernels at the configuration-2 layer shape (HBM-bound) --------
+    streaming = None
+    if not args.no_streaming and rank == 0:
+        peak_gbs, _ = measured_peaks()
+        Bs, Ts, Cs = 16, 8192, 2048
+        x, mus = workloads.mix_inputs(Bs, Ts, Cs, seed=5, dtype=torch.bfloat16, device=dev)
+        diff = torch.randn_like(x)
+        state = torch.zeros(Bs + 1, Cs, dtype=torch.bfloat16, device=dev)
+        ids = torch.arange(Bs, dtype=torch.int32, device=dev)
+        elems = Bs * Ts * Cs
+
+        def timeit(fn, nbytes, reps=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / reps
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            return {"ms": ms, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak_gbs, "algorithmic_bytes": nbytes}
+
+        # outputs are allocated inside the wrappers (caching allocator, no cudaMalloc after warm-up)
+        streaming = {
+            "shape": f"B={Bs} T={Ts} C={Cs} bf16 (configuration 2, one layer)",
+            "mix6": timeit(lambda: pkg.mix6_custom(x, *mus), 7 * 2 * elems),
+            "addcmul": timeit(lambda: pkg.addcmul_custom(x, diff, mus[0]), 3 * 2 * elems),
+            "addcmul5": timeit(lambda: pkg.addcmul5_custom(x, diff, *mus[:5]), 7 * 2 * elems),
+            "token_shift_diff": timeit(lambda: pkg.token_shift_diff_custom(x, state, ids, inplace_state=True),
+                                       2 * 2 * elems),
+        }
+        del x, diff, mus
+
+    # ---- fused LM-head cross entropy at the configuration-2 shape (tensor-core-bound) -----
+    lm_head = None
+    if not args.no_lm_head and rank == 0:
+        Rl, Cl, Vl = 16 * 8192, 2048, 65536
+        xl, wl, tl = workloads.lm_head_inputs(Rl, Cl, Vl, seed=2, device=dev)
+        for _ in range(2):
+            pkg.lm_head_ce(xl, wl, tl)
+        torch.cuda.synchronize()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_lm = 3
+        l0.record()
+        for _ in range(n_lm):
+            lse, loss = pkg.lm_head_ce(xl, wl, tl)
+        l1.record()
+        torch.cuda.synchronize()
+        lms = l0.elapsed_time(l1) / n_lm
+        flops = 2.0 * Rl * Cl * Vl
+        tf_peak = 1653.6
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tf_peak = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            pass
+        lm_head = {"workload": f"R={Rl} C={Cl} V={Vl} bf16, logits never materialised (configuration 2)",
+                   "ms": lms, "tflops": flops / (lms * 1e-3) / 1e12, "peak_tflops": tf_peak,
+                   "frac_of_bf16_peak": flops / (lms * 1e-3) / 1e12 / tf_peak,
+                   "mean_loss": float(loss.mean().item())}
+        del xl, wl, tl
+
     if world > 1:
         dist.barrier()
     if rank != 0:
@@ -325,6 +392,8 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "decode": decode,
+        "streaming": streaming,
+        "lm_head_ce": lm_head,
     }
     if not args.no_cpu_baseline:
         oracle = entry.load_oracle()

@@ -126,7 +126,13 @@ addcmul_kernel(const T *base, const T *__restrict__ diff, AddcmulPtrs ptrs, int6
 #pragma unroll 4
         for (int64_t row = row_begin; row < row_end; ++row) {
             Pack<T, EPV> bs, df;
-            bs.load(base + row * C + c);  // `out[0]` may alias `base`: read before write, same thread
+            if constexpr (NS == 1) {
+                bs.load(base + row * C + c);  // `out[0]` may alias `base`: read before write, same thread
+            } else {
+                // the five outputs never alias the inputs: let loads of later rows pass earlier stores
+                const T *__restrict__ base_noalias = base;
+                bs.load(base_noalias + row * C + c);
+            }
             df.load(diff + row * C + c);
 #pragma unroll
             for (int s = 0; s < NS; ++s) {
