@@ -123,7 +123,8 @@ addcmul_kernel(const T *base, const T *__restrict__ diff, AddcmulPtrs ptrs, int6
         Pack<T, EPV> sc[NS];
 #pragma unroll
         for (int s = 0; s < NS; ++s) sc[s].load(reinterpret_cast<const T *>(ptrs.scale[s]) + c);
-#pragma unroll 4
+        // five scale vectors already fill 40 registers: a shorter unroll keeps three CTAs per SM
+#pragma unroll(NS == 1 ? 4 : 2)
         for (int64_t row = row_begin; row < row_end; ++row) {
             Pack<T, EPV> bs, df;
             if constexpr (NS == 1) {
