@@ -264,6 +264,7 @@ int rwkv7_read_device_status(int device, rwkv7_stream stream) {
     if (e != cudaSuccess) return cuda_fail("reading the device status word", (int)e);
     if (host == kDevTimeout) return fail(RWKV7_ERR_TIMEOUT, "Timeout: a bounded device-side wait expired");
     if (host == kDevBadIndex) return fail(RWKV7_ERR_BAD_INDEX, "BadIndex: a device-side index was out of range");
+    if (host == kDevInternal) return fail(RWKV7_ERR_CUDA, "CudaError: a kernel's own precondition check failed (shared memory alignment)");
     return RWKV7_OK;
 }
 

@@ -11,7 +11,7 @@
 namespace rwkv7 {
 
 // Device status word values (see rwkv7_read_device_status).
-enum DeviceStatus : int { kDevOk = 0, kDevTimeout = 1, kDevBadIndex = 2 };
+enum DeviceStatus : int { kDevOk = 0, kDevTimeout = 1, kDevBadIndex = 2, kDevInternal = 3 };
 // Address of the per-device status word, resolved once per device.
 int device_status_ptr(int device, int **out);
 // Process-wide count of kernel launches (rwkv7_kernel_launch_count).

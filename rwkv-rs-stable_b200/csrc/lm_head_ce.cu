@@ -52,8 +52,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 lm_head_ce_kernel(const __grid_constant__ LmMaps maps, const void *__restrict__ targets, int targets_dtype,
                   int64_t vocab_offset, float *__restrict__ out /* [splits][R][3] */, int64_t R, int C, int V,
                   int row_blocks, int tiles_per_split, int *status) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) unsigned char smem[];   // swizzled TMA tiles need 1024-byte alignment
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
+        return;
+    }
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
     uint64_t *empty = full + kStages;
     uint64_t *tmem_full = empty + kStages;

@@ -166,8 +166,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     __nv_bfloat16 *__restrict__ y, float *s_out, int *__restrict__ flags,
                     int Tlen, int H, int *status) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Every pointer is derived from the array itself so that the accesses stay in
+    // the shared address space; the 1024-byte alignment the swizzled tiles need is
+    // what the runtime provides and is verified before anything else happens.
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
+        return;
+    }
     unsigned char *raw = smem + kOffRaw, *tAR = smem + kOffAR, *tBK = smem + kOffBK, *tZT = smem + kOffZT,
                   *tS = smem + kOffS, *tVT = smem + kOffVT, *tAKRK = smem + kOffAKRK, *tXU = smem + kOffXU;
     float *Am = reinterpret_cast<float *>(smem + kOffAm);
@@ -177,8 +183,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc + 16);
-    float *exp_cl = reinterpret_cast<float *>(smem + kOffMisc + 64);   // [64] exp(c_L)
-    int *unsafe = reinterpret_cast<int *>(exp_cl + 64);
+    float *exp_cl = reinterpret_cast<float *>(smem + kOffMisc + 64);   // [2][64] exp(c_L), by chunk parity
+    int *unsafe = reinterpret_cast<int *>(exp_cl + 128);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quarter = warp & 3;   // TMEM lane quarter this warp may read
@@ -240,22 +246,37 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         const int valid = min(kL, Tlen - chunk * kL);
         // ---------------- wait for this chunk's six input tiles
         PHASE(0);
-        {
-            const bool ok = mbar_wait(bar_tma, (uint32_t)(chunk & 1));
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-            ++tma_consumed;
-        }
+        // A wait that expires sets a sticky flag; every thread sees it after the next
+        // CTA barrier and leaves the loop there, so no extra barrier is spent on it.
+        if (!mbar_wait(bar_tma, (uint32_t)(chunk & 1))) atomicOr(unsafe, 2);
+        ++tma_consumed;
         // ---------------- phase A: decay prefix sums and scaled operands
         PHASE(1);
+        if (valid < kL) {
+            // Last, partial chunk: turn the rows past the end into no-op tokens
+            // (w = -inf gives a log-decay of -0, every other vector is zero).
+            for (int idx = tid; idx < (kL - valid) * kN; idx += kThreads) {
+                const int t = valid + idx / kN, jj = idx % kN;
+#pragma unroll
+                for (int x = 0; x < 6; ++x)
+                    *reinterpret_cast<unsigned short *>(raw + x * (kL * kN * 2) + (t * kN + jj) * 2) =
+                        (x == TW) ? (unsigned short)0xFF80 : (unsigned short)0;
+            }
+            __syncthreads();
+        }
         {
             const int j = tid & 63, tg = tid >> 6;  // channel, group of 8 tokens
             const int t0 = tg * 8;
+            const unsigned char *rp = raw + (t0 * kN + j) * 2;
+            auto ld = [&](int tensor, int u) {
+                return __uint_as_float(
+                    (unsigned)*reinterpret_cast<const unsigned short *>(rp + tensor * (kL * kN * 2) + u * (kN * 2)) << 16);
+            };
             float c[8];
             float sum = 0.f;
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const float lw = (t0 + u < valid) ? -__expf(bf16_at(raw, TW, t0 + u, j)) : 0.f;
-                sum += lw;
+                sum -= __expf(ld(TW, u));
                 c[u] = sum;  // inclusive prefix inside this group
             }
             grp_tot[tg * 64 + j] = sum;
@@ -268,28 +289,28 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 if (g < tg) base += x;
             }
             if (tg == 7) {
-                exp_cl[j] = __expf(total);
-                if (total < -kMaxLogDecay) *unsafe = 1;
+                exp_cl[(chunk & 1) * 64 + j] = __expf(total);
+                if (total < -kMaxLogDecay) atomicOr(unsafe, 1);
             }
+            // Row t0 + u of a 128-row tile: t0 is a multiple of 8, so the swizzle term is u.
+            const uint32_t cb = (uint32_t)(j & 31) * 4u;
+            unsigned char *pAR = tAR + (j >> 5) * (128 * 128) + t0 * 128;
+            unsigned char *pBK = tBK + (j >> 5) * (128 * 128) + t0 * 128;
             float e_prev = __expf(base);  // exp(c_{t0-1})
             float bhv[8], khv[8], vv[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const int t = t0 + u;
-                const bool live = t < valid;
                 const float e = __expf(base + c[u]);   // exp(c_t)
-                const float einv = __frcp_rn(e);        // exp(-c_t)
-                const float a = live ? bf16_at(raw, TA, t, j) : 0.f;
-                const float r = live ? bf16_at(raw, TR, t, j) : 0.f;
-                const float b = live ? bf16_at(raw, TB, t, j) : 0.f;
-                const float k = live ? bf16_at(raw, TK, t, j) : 0.f;
-                vv[u] = live ? bf16_at(raw, TV, t, j) : 0.f;  // bf16 values are tf32-exact
-                bhv[u] = round_tf32(b * einv);
-                khv[u] = round_tf32(k * einv);
-                st_tile(tAR, 128, t, j, round_tf32(a * e_prev));
-                st_tile(tAR, 128, 64 + t, j, round_tf32(r * e));
-                st_tile(tBK, 128, t, j, bhv[u]);
-                st_tile(tBK, 128, 64 + t, j, khv[u]);
+                float einv;                             // exp(-c_t)
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(einv) : "f"(e));
+                vv[u] = ld(TV, u);                      // bf16 values are tf32-exact
+                bhv[u] = round_tf32(ld(TB, u) * einv);
+                khv[u] = round_tf32(ld(TK, u) * einv);
+                const uint32_t o = (uint32_t)u * 128u + (cb ^ ((uint32_t)u << 4));
+                *reinterpret_cast<float *>(pAR + o) = round_tf32(ld(TA, u) * e_prev);
+                *reinterpret_cast<float *>(pAR + 64 * 128 + o) = round_tf32(ld(TR, u) * e);
+                *reinterpret_cast<float *>(pBK + o) = bhv[u];
+                *reinterpret_cast<float *>(pBK + 64 * 128 + o) = khv[u];
                 e_prev = e;
             }
             // transposed copies: Bh^T, Kh^T [j][t] and V^T [i][s], 8 consecutive tokens per thread
@@ -303,20 +324,15 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         fence_proxy_async();
         __syncthreads();  // operands visible to the tensor core; raw tiles and group sums are dead
         if (*unsafe) { failed = true; break; }
-        // ---------------- M1: G = [At;Rt] [Bh;Kh]^T ; state-independent part of Z
+        // ---------------- M1: G = [At;Rt] [Bh;Kh]^T
         PHASE(3);
         if (tid == 0) {
             tc_fence_after();
             mma_k64<128, 128, 128>(tmem + kColG, dAR, dBK, false);
-            // Z = Kh^T V : A = rows 64..127 of the [Bh^T;Kh^T] stack
-            mma_k64<128, 64, 64>(tmem + kColZ, dZTk, dVT, false);
             umma_commit(bar_mma);
         }
-        {
-            const bool ok = mbar_wait(bar_mma, mma_phase);
-            mma_phase ^= 1;
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
+        mma_phase ^= 1;
         tc_fence_after();
         // ---------------- hop 1: G -> masked A_ab (fp32 scratch), A_ak, A_rb, A_rk (tf32 tiles)
         PHASE(4);
@@ -359,6 +375,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         }
         tc_fence_before();
         __syncthreads();
+        if (*unsafe) { failed = true; break; }
         // ---------------- T = (I - A_ab)^-1, blocked: 16x16 diagonal blocks by forward
         // substitution, then the off-diagonal blocks T_ba = T_bb A_ba T_aa at block
         // sizes 16 and 32.  All in fp32 on the scratch matrices.
@@ -439,13 +456,13 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             tc_fence_after();
             mma_k64<128, 64, 64>(tmem + kColXY, dAKRK, dVT, false);
             mma_k64<128, 64, 64>(tmem + kColXY, dAR, dS, true);
+            // Z = Kh^T V (state independent): A = rows 64..127 of the [Bh^T;Kh^T] stack.  Issued
+            // here, after the previous chunk's state update has read the Z columns.
+            mma_k64<128, 64, 64>(tmem + kColZ, dZTk, dVT, false);
             umma_commit(bar_mma);
         }
-        {
-            const bool ok = mbar_wait(bar_mma, mma_phase);
-            mma_phase ^= 1;
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
+        mma_phase ^= 1;
         tc_fence_after();
         // ---------------- hop 2: X (lanes 0..63) -> X^T [i][t]
         PHASE(7);
@@ -459,6 +476,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         tc_fence_before();
         fence_proxy_async();
         __syncthreads();
+        if (*unsafe) { failed = true; break; }
         // ---------------- M3: U = T X
         PHASE(8);
         if (tid == 0) {
@@ -466,11 +484,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             mma_k64<128, 64, 64>(tmem + kColU, dBK, dXU, false);
             umma_commit(bar_mma);
         }
-        {
-            const bool ok = mbar_wait(bar_mma, mma_phase);
-            mma_phase ^= 1;
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
+        mma_phase ^= 1;
         tc_fence_after();
         // ---------------- hop 3: U (lanes 0..63) -> U^T [i][t]   (M3 has finished reading X^T)
         PHASE(9);
@@ -484,6 +499,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         tc_fence_before();
         fence_proxy_async();
         __syncthreads();
+        if (*unsafe) { failed = true; break; }
         // ---------------- M4: XY[64..127] += A_rb U ; Z += Bh^T U
         PHASE(10);
         if (tid == 0) {
@@ -492,16 +508,13 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             mma_k64<128, 64, 64>(tmem + kColZ, dZT, dXU, true);
             umma_commit(bar_mma);
         }
-        {
-            const bool ok = mbar_wait(bar_mma, mma_phase);
-            mma_phase ^= 1;
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
+        mma_phase ^= 1;
         tc_fence_after();
         // ---------------- hop 4: state update (lanes 0..63) and y (lanes 64..127)
         PHASE(11);
         if (quarter < 2) {
-            const float g = exp_cl[zj];
+            const float g = exp_cl[(chunk & 1) * 64 + zj];
             uint32_t v[16];
             tmem_ld16(tmem + lane_base + kColZ + cgrp * 16, v);
             tmem_ld_wait();
@@ -531,15 +544,19 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 }
             }
         }
+        // No CTA barrier here: the next chunk's phase A touches neither TMEM nor any
+        // buffer this hop reads (exp(c_L) is kept per chunk parity), and its own
+        // barriers come before the next MMA that overwrites the accumulators read above.
         tc_fence_before();
-        __syncthreads();
     }
+    __syncthreads();
+    if (*unsafe) failed = true;   // also catches a flag raised during the last chunk
 
     // ---------------- epilogue
     PHASE(12);
     // A tile batch still in flight must land before the CTA gives up its shared memory.
     if (failed && tma_issued > tma_consumed) mbar_wait(bar_tma, (uint32_t)(tma_consumed & 1));
-    const bool bad_decay = *unsafe != 0;
+    const bool bad_decay = (*unsafe & 1) != 0;
     if (failed && !bad_decay && tid == 0) atomicExch(status, (int)kDevTimeout);
     if (tid == 0) flags[bh] = bad_decay ? 1 : 0;
     if (!failed && s_out != nullptr && quarter < 2) {
