@@ -1,0 +1,175 @@
+// rwkv7_b200.hpp — C++ host-side mirror of the reference's operator interface,
+// header-only, over the C ABI of rwkv7_b200.h.
+//
+// Names and argument meaning follow the reference's public wrappers and I/O
+// structs: Wkv7PretrainForwardInputs / wkv7_pretrain_custom / wkv7_statetune_custom /
+// wkv7_statepass_custom (crates/rwkv-nn/src/kernels/train/time_mixer/wkv7/io.rs:20-173,
+// mod.rs:105-150), mix6_custom (.../mix6/mod.rs:76-108), addcmul_custom /
+// addcmul5_custom (crates/rwkv-nn/src/kernels/template/addcmul/mod.rs:100-157),
+// token_shift_diff_custom (.../token_shift_diff/mod.rs:82-111).  Where the reference
+// panics (`inputs.check().unwrap()`, `assert!`), these functions throw
+// KernelInputsError carrying the same message text.  Unlike the reference there
+// is no allocator behind this layer: the caller passes the output tensors.
+#ifndef RWKV7_B200_HPP_
+#define RWKV7_B200_HPP_
+
+#include <array>
+#include <cstdint>
+#include <initializer_list>
+#include <stdexcept>
+#include <string>
+
+#include "rwkv7_b200.h"
+
+namespace rwkv7b200 {
+
+// The reference's KernelInputsError (kernels/check.rs:34-73) plus the ABI's own codes.
+class KernelInputsError : public std::runtime_error {
+   public:
+    KernelInputsError(int status, const std::string &message) : std::runtime_error(message), status_(status) {}
+    int status() const { return status_; }
+    const char *kind() const { return rwkv7_status_string(status_); }
+
+   private:
+    int status_;
+};
+
+inline void check_status(int status) {
+    if (status != RWKV7_OK) throw KernelInputsError(status, rwkv7_last_error_message());
+}
+
+// Borrowed, contiguous row-major view of device memory.
+struct TensorView {
+    rwkv7_tensor t{};
+    TensorView() = default;
+    TensorView(void *data, rwkv7_dtype dtype, int device, std::initializer_list<int64_t> shape) {
+        t.data = data;
+        t.dtype = dtype;
+        t.device = device;
+        t.ndim = (int32_t)shape.size();
+        int i = 0;
+        for (int64_t d : shape) t.shape[i++] = d;
+        int64_t stride = 1;
+        for (int k = t.ndim - 1; k >= 0; --k) {
+            t.stride[k] = stride;
+            stride *= t.shape[k];
+        }
+    }
+    const rwkv7_tensor *c() const { return &t; }
+    rwkv7_tensor *m() { return &t; }
+};
+
+// wkv7/io.rs:20-66
+struct Wkv7PretrainForwardInputs {
+    TensorView receptance, weight_decay, replacement_key, value, removal_key_normalized, replacement;
+    int64_t chunk_len = 16;
+
+    // The two assertions that precede the reference's shape checks (wkv7/io.rs:187,198-201).
+    // The C ABI itself accepts any T >= 1; pass reference_contract = false for decode steps.
+    void check(bool reference_contract = true) const {
+        if (!reference_contract) return;
+        if (chunk_len != 16) throw KernelInputsError(RWKV7_ERR_BAD_CHUNK, "wkv7 currently supports chunk_len=16");
+        if (receptance.t.ndim == 4 && receptance.t.shape[1] % chunk_len != 0)
+            throw KernelInputsError(RWKV7_ERR_BAD_CHUNK, "context_len must be a multiple of chunk_len");
+    }
+};
+
+// wkv7/io.rs:122-164
+struct Wkv7StatepassForwardInputs {
+    TensorView initial_state;
+    Wkv7PretrainForwardInputs sequence;
+};
+struct Wkv7StatepassForwardOutput {
+    TensorView output, next_state;
+};
+
+struct Workspace {
+    void *data = nullptr;
+    size_t bytes = 0;
+};
+
+inline size_t wkv7_workspace_bytes(const Wkv7PretrainForwardInputs &in) {
+    const rwkv7_tensor &r = in.receptance.t;
+    return r.ndim == 4 ? rwkv7_wkv7_workspace_bytes(r.shape[0], r.shape[1], r.shape[2], r.shape[3], r.dtype) : 0;
+}
+
+// wkv7_pretrain_custom (wkv7/mod.rs:105-110)
+inline void wkv7_pretrain_custom(const Wkv7PretrainForwardInputs &in, TensorView &output, Workspace ws = {},
+                                 rwkv7_stream stream = nullptr, bool reference_contract = true) {
+    in.check(reference_contract);
+    check_status(rwkv7_fused_wkv7_pretrain(in.receptance.c(), in.weight_decay.c(), in.replacement_key.c(),
+                                           in.value.c(), in.removal_key_normalized.c(), in.replacement.c(),
+                                           in.chunk_len, output.m(), ws.data, ws.bytes, stream));
+}
+
+// wkv7_statetune_custom (wkv7/mod.rs:113-120)
+inline void wkv7_statetune_custom(const Wkv7StatepassForwardInputs &in, TensorView &output, Workspace ws = {},
+                                  rwkv7_stream stream = nullptr, bool reference_contract = true) {
+    in.sequence.check(reference_contract);
+    const auto &s = in.sequence;
+    check_status(rwkv7_fused_wkv7_statetune(in.initial_state.c(), s.receptance.c(), s.weight_decay.c(),
+                                            s.replacement_key.c(), s.value.c(), s.removal_key_normalized.c(),
+                                            s.replacement.c(), s.chunk_len, output.m(), ws.data, ws.bytes, stream));
+}
+
+// wkv7_statepass_custom (wkv7/mod.rs:123-133); out.next_state may view the same memory as in.initial_state.
+inline void wkv7_statepass_custom(const Wkv7StatepassForwardInputs &in, Wkv7StatepassForwardOutput &out,
+                                  Workspace ws = {}, rwkv7_stream stream = nullptr, bool reference_contract = true) {
+    in.sequence.check(reference_contract);
+    const auto &s = in.sequence;
+    check_status(rwkv7_fused_wkv7_statepass(in.initial_state.c(), s.receptance.c(), s.weight_decay.c(),
+                                            s.replacement_key.c(), s.value.c(), s.removal_key_normalized.c(),
+                                            s.replacement.c(), s.chunk_len, out.output.m(), out.next_state.m(),
+                                            ws.data, ws.bytes, stream));
+}
+
+// mix6/io.rs:20-46, 110-124: scales and outputs in the order receptance, weight_decay, key, value,
+// learning_rate, gate.
+struct Mix6ForwardInputs {
+    TensorView embedded_context;
+    std::array<TensorView, 6> scales;
+};
+struct Mix6ForwardOutput {
+    std::array<TensorView, 6> inputs;
+};
+
+// mix6_custom (mix6/mod.rs:76-108)
+inline void mix6_custom(const Mix6ForwardInputs &in, Mix6ForwardOutput &out, rwkv7_stream stream = nullptr) {
+    const rwkv7_tensor *sc[6];
+    rwkv7_tensor *o[6];
+    for (int i = 0; i < 6; ++i) {
+        sc[i] = in.scales[i].c();
+        o[i] = out.inputs[i].m();
+    }
+    check_status(rwkv7_fused_mix6(in.embedded_context.c(), sc, o, stream));
+}
+
+// addcmul_custom (addcmul/mod.rs:100-105); `output` may view the same memory as `base`.
+inline void addcmul_custom(const TensorView &base, const TensorView &diff, const TensorView &scale,
+                           TensorView &output, rwkv7_stream stream = nullptr) {
+    check_status(rwkv7_fused_addcmul(base.c(), diff.c(), scale.c(), output.m(), stream));
+}
+
+// addcmul5_custom (addcmul/mod.rs:138-157)
+inline void addcmul5_custom(const TensorView &base, const TensorView &diff, const std::array<TensorView, 5> &scales,
+                            std::array<TensorView, 5> &outputs, rwkv7_stream stream = nullptr) {
+    const rwkv7_tensor *sc[5];
+    rwkv7_tensor *o[5];
+    for (int i = 0; i < 5; ++i) {
+        sc[i] = scales[i].c();
+        o[i] = outputs[i].m();
+    }
+    check_status(rwkv7_fused_addcmul5(base.c(), diff.c(), sc, o, stream));
+}
+
+// token_shift_diff_custom (token_shift_diff/mod.rs:82-111): `embedded_token_shift` is updated in place.
+inline void token_shift_diff_custom(const TensorView &embedded_context, TensorView &embedded_token_shift,
+                                    const TensorView &batch_ids, TensorView &token_shifted_diff,
+                                    rwkv7_stream stream = nullptr) {
+    check_status(rwkv7_fused_token_shift_diff(embedded_context.c(), embedded_token_shift.m(), batch_ids.c(),
+                                              token_shifted_diff.m(), stream));
+}
+
+}  // namespace rwkv7b200
+
+#endif  // RWKV7_B200_HPP_
