@@ -118,13 +118,21 @@ def cpu_baseline(oracle, workloads, torch, budget_s: float = 12.0):
     chains = rounds * threads
     inp = workloads.wkv7_inputs(1, CFG1["T"], chains, 64, seed=1, dtype=torch.bfloat16)
     f = [inp[n].float().numpy() for n in "rwkvab"]
+    # The sample usually is the whole workload (well under the budget on a many-core
+    # host): repeat it a few times and keep the mean.
+    reps = 0
     t0 = time.perf_counter()
-    oracle.wkv7(*f, None, precision="f32")
-    dt = time.perf_counter() - t0
+    while True:
+        oracle.wkv7(*f, None, precision="f32")
+        reps += 1
+        dt_all = time.perf_counter() - t0
+        if reps >= 5 or dt_all > budget_s:
+            break
+    dt = dt_all / reps
     token_heads_per_s = chains * CFG1["T"] / dt
     return {"value": token_heads_per_s / CFG1["H"], "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"{chains} of {CFG1['B'] * CFG1['H']} (b,h) chains x T={CFG1['T']} "
-                      f"(fp32 oracle, OpenMP), {dt:.2f} s; tokens/s = token-heads/s / H"}
+                      f"(fp32 oracle, OpenMP), mean of {reps} runs of {dt:.2f} s; tokens/s = token-heads/s / H"}
 
 
 def run_reference(args):
