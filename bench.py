@@ -41,6 +41,20 @@ STATE_BYTES = 64 * 64 * 4
 DECODE_BYTES_PER_BH = 2 * STATE_BYTES + 7 * 64 * 2
 
 
+def bench_config(B, T, H, N, path="auto"):
+    """The `config` object of the JSON line (shared by both arms)."""
+    return {"workload": f"cfg1 WKV7 chunked prefill B={B} T={T} H={H} N={N} per GPU, S0=0, bf16 in/out, fp32 state",
+            "B": B, "T": T, "H": H, "N": N, "path": path,
+            "l2": "inputs (302 MB per step) exceed the 126 MB L2; no flush needed",
+            "sharding": "batch x head shard per rank, no collective on the data path"}
+
+
+# DRAM bytes of one prefill launch from the ncu capture of the B=4 case (151.9 MB read +
+# 15.2 MB written; y still partly in L2 at kernel end), scaled x2 to B=8: traffic is
+# proportional to the number of chains.  See profiles/wkv7_chunked_prefill_cfg1.md.
+NCU_TRAFFIC_BYTES_CFG1 = 2 * (151.9e6 + 15.2e6)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -164,7 +178,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg1 WKV7 prefill B=8 T=4096 H=12 N=64 (CPU sample)", **CFG1},
+        "config": bench_config(**CFG1),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -390,12 +404,11 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate, bf16 I/O", "data": "synthetic",
-        "config": {"workload": f"cfg1 WKV7 chunked prefill B={B} T={T} H={H} N={N} per GPU, S0=0, bf16 in/out, "
-                               "fp32 state", "B": B, "T": T, "H": H, "N": N, "path": args.path,
-                   "l2": "inputs (302 MB per step) exceed the 126 MB L2; no flush needed",
-                   "sharding": "batch x head shard per rank, no collective on the data path"},
+        "config": bench_config(B, T, H, N, args.path),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
+                     "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_CFG1 * (B / 8.0) if args.path != "sequential" else None,
+                     "peak_source": peak_kind,
                      "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kernel_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
