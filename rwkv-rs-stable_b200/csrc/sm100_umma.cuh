@@ -217,11 +217,13 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// fp32 -> tf32 with round-to-nearest (the tensor core would otherwise truncate).
+// fp32 -> tf32 with round-to-nearest, ties away from zero (what cvt.rna.tf32.f32
+// computes for finite values).  The tensor core ignores the low 13 mantissa bits,
+// so adding half a tf32 ulp to the magnitude is all the rounding needs; as one
+// integer add it runs at full rate, whereas the cvt instruction shares the
+// quarter-rate transcendental pipe with exp and rcp.  Only finite operands reach it.
 __device__ __forceinline__ float round_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float(__float_as_uint(x) + 0x1000u);
 }
 
 }  // namespace sm100
