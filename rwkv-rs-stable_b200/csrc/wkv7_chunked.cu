@@ -76,7 +76,7 @@ constexpr uint32_t kOffPm = kOffTm + 64 * kPitch * 4;         // P      [32][68]
 static_assert(kOffPm + 32 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
 
 // TMEM columns.
-constexpr uint32_t kColG = 0, kColXY = 128, kColU = 192, kColZ = 256, kTmemCols = 512;
+constexpr uint32_t kColG = 0, kColXT = 128, kColUT = 192, kColYT = 256, kColDS = 320, kTmemCols = 512;
 
 // Optional per-phase cycle counters (development builds only): thread 0 of CTA 0
 // adds the cycles spent since the previous mark to the slot of the phase that
@@ -124,6 +124,18 @@ __device__ __forceinline__ void mma_k64(uint32_t d_tmem, uint64_t a0, uint64_t b
         const uint64_t ao = (uint64_t)(((ks >> 2) * A_ROWS * 128 + (ks & 3) * 32) >> 4);
         const uint64_t bo = (uint64_t)(((ks >> 2) * B_ROWS * 128 + (ks & 3) * 32) >> 4);
         umma_tf32(d_tmem, a0 + ao, b0 + bo, idesc, accumulate || ks > 0);
+    }
+}
+
+// Same with the A operand read from TMEM (a previous accumulator: 128 lanes x 64
+// fp32 columns, 8 columns per K-step; the tensor core truncates it to tf32).
+template <int B_ROWS, int N>
+__device__ __forceinline__ void mma_k64_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b0, bool accumulate) {
+    constexpr uint32_t idesc = make_idesc(kFmtTF32, 128, N, false, false);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t bo = (uint64_t)(((ks >> 2) * B_ROWS * 128 + (ks & 3) * 32) >> 4);
+        umma_tf32_ts(d_tmem, a_tmem + ks * 8, b0 + bo, idesc, accumulate || ks > 0);
     }
 }
 
@@ -216,16 +228,17 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     };
     if (tid == 0) issue_tma(0);
 
-    // fp32 state: the thread at TMEM lane j (< 64), column group g holds
-    // Z[j][16g .. 16g+15] = S[16g + e][j].
-    const int zj = quarter * 32 + lane;  // meaningful for quarter < 2
+    // fp32 state: the thread at TMEM lane i (< 64), column group g holds S[i][16g .. 16g+15].
+    const int zj = quarter * 32 + lane;  // value row i, meaningful for quarter < 2
     float Z[16];
     if (quarter < 2) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const int i = cgrp * 16 + e;
-            Z[e] = s0 ? s0[((size_t)bh * kN + i) * kN + zj] : 0.f;
-            st_tile(tS, 64, i, zj, round_tf32(Z[e]));
+        for (int q4 = 0; q4 < 4; ++q4) {
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s0) x = *reinterpret_cast<const float4 *>(s0 + ((size_t)bh * kN + zj) * kN + cgrp * 16 + 4 * q4);
+            Z[4 * q4] = x.x; Z[4 * q4 + 1] = x.y; Z[4 * q4 + 2] = x.z; Z[4 * q4 + 3] = x.w;
+            st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,
+                     make_float4(round_tf32(x.x), round_tf32(x.y), round_tf32(x.z), round_tf32(x.w)));
         }
     }
 
@@ -235,9 +248,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
 #endif
     // K-step-0 descriptors of every operand tile (constant for the whole kernel).
     const uint64_t dAR = desc_kmajor(smem_u32(tAR), 128, 0), dBK = desc_kmajor(smem_u32(tBK), 128, 0),
-                   dZT = desc_kmajor(smem_u32(tZT), 128, 0), dZTk = desc_kmajor(smem_u32(tZT) + 64 * 128, 128, 0),
+                   dZT = desc_kmajor(smem_u32(tZT), 128, 0),
                    dS = desc_kmajor(smem_u32(tS), 64, 0), dVT = desc_kmajor(smem_u32(tVT), 64, 0),
-                   dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0), dXU = desc_kmajor(smem_u32(tXU), 64, 0);
+                   dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0);
     uint32_t mma_phase = 0;
     bool failed = false;
     int tma_issued = 1, tma_consumed = 0;  // tile batches requested / received
@@ -450,99 +463,52 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             if (tid == 32) issue_tma(chunk + 1);   // not the thread that issues the MMAs
             ++tma_issued;
         }
-        // ---------------- M2: XY = [A_ak;A_rk] V + [At;Rt] Z0
+        // ---------------- state path: eight MMA groups chained through TMEM, one commit.
+        // Value-major products (M = value index i, 64 valid lanes): X^T and U^T stay in
+        // TMEM and feed the next group as its A operand; the B operands are the K-major
+        // tiles staged above.  Order: the groups that do not depend on X^T / U^T first.
         PHASE(6);
         if (tid == 0) {
             tc_fence_after();
-            mma_k64<128, 64, 64>(tmem + kColXY, dAKRK, dVT, false);
-            mma_k64<128, 64, 64>(tmem + kColXY, dAR, dS, true);
-            // Z = Kh^T V (state independent): A = rows 64..127 of the [Bh^T;Kh^T] stack.  Issued
-            // here, after the previous chunk's state update has read the Z columns.
-            mma_k64<128, 64, 64>(tmem + kColZ, dZTk, dVT, false);
+            constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
+            mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
+            mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, true);    // Y^T += V^T A_rk^T
+            mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
+            mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
+            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
+            mma_k64_ts<128, 64>(tmem + kColUT, tmem + kColXT, dBK, false);     // U^T  = X^T T^T
+            mma_k64_ts<128, 64>(tmem + kColYT, tmem + kColUT, dBK + kLower, true);   // Y^T += U^T A_rb^T
+            mma_k64_ts<128, 64>(tmem + kColDS, tmem + kColUT, dZT, true);      // dS  += U^T Bh
             umma_commit(bar_mma);
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
         mma_phase ^= 1;
         tc_fence_after();
-        // ---------------- hop 2: X (lanes 0..63) -> X^T [i][t]
-        PHASE(7);
-        if (quarter < 2) {
-            uint32_t v[16];
-            tmem_ld16(tmem + lane_base + kColXY + cgrp * 16, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) st_tile(tXU, 64, cgrp * 16 + e, zj, round_tf32(__uint_as_float(v[e])));
-        }
-        tc_fence_before();
-        fence_proxy_async();
-        __syncthreads();
-        if (*unsafe) { failed = true; break; }
-        // ---------------- M3: U = T X
-        PHASE(8);
-        if (tid == 0) {
-            tc_fence_after();
-            mma_k64<128, 64, 64>(tmem + kColU, dBK, dXU, false);
-            umma_commit(bar_mma);
-        }
-        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
-        mma_phase ^= 1;
-        tc_fence_after();
-        // ---------------- hop 3: U (lanes 0..63) -> U^T [i][t]   (M3 has finished reading X^T)
-        PHASE(9);
-        if (quarter < 2) {
-            uint32_t v[16];
-            tmem_ld16(tmem + lane_base + kColU + cgrp * 16, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 16; ++e) st_tile(tXU, 64, cgrp * 16 + e, zj, round_tf32(__uint_as_float(v[e])));
-        }
-        tc_fence_before();
-        fence_proxy_async();
-        __syncthreads();
-        if (*unsafe) { failed = true; break; }
-        // ---------------- M4: XY[64..127] += A_rb U ; Z += Bh^T U
-        PHASE(10);
-        if (tid == 0) {
-            tc_fence_after();
-            mma_k64<128, 64, 64>(tmem + kColXY, dBK, dXU, true);
-            mma_k64<128, 64, 64>(tmem + kColZ, dZT, dXU, true);
-            umma_commit(bar_mma);
-        }
-        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
-        mma_phase ^= 1;
-        tc_fence_after();
-        // ---------------- hop 4: state update (lanes 0..63) and y (lanes 64..127)
+        // ---------------- hop: state update and y, by the 8 warps that own lanes 0..63
         PHASE(11);
         if (quarter < 2) {
-            const float g = exp_cl[(chunk & 1) * 64 + zj];
             uint32_t v[16];
-            tmem_ld16(tmem + lane_base + kColZ + cgrp * 16, v);
+            tmem_ld16(tmem + lane_base + kColDS + cgrp * 16, v);
+            uint32_t yv[16];
+            tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
             tmem_ld_wait();
+            const float4 *g4 = reinterpret_cast<const float4 *>(exp_cl + (chunk & 1) * 64 + cgrp * 16);
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                Z[e] = g * (Z[e] + __uint_as_float(v[e]));
-                st_tile(tS, 64, cgrp * 16 + e, zj, round_tf32(Z[e]));   // operand of the next chunk
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 g = g4[q4];
+                Z[4 * q4 + 0] = g.x * (Z[4 * q4 + 0] + __uint_as_float(v[4 * q4 + 0]));
+                Z[4 * q4 + 1] = g.y * (Z[4 * q4 + 1] + __uint_as_float(v[4 * q4 + 1]));
+                Z[4 * q4 + 2] = g.z * (Z[4 * q4 + 2] + __uint_as_float(v[4 * q4 + 2]));
+                Z[4 * q4 + 3] = g.w * (Z[4 * q4 + 3] + __uint_as_float(v[4 * q4 + 3]));
+                st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,   // operand of the next chunk
+                         make_float4(round_tf32(Z[4 * q4]), round_tf32(Z[4 * q4 + 1]), round_tf32(Z[4 * q4 + 2]),
+                                     round_tf32(Z[4 * q4 + 3])));
             }
-        } else {
-            const int t = (quarter - 2) * 32 + lane;
-            uint32_t v[16];
-            tmem_ld16(tmem + lane_base + kColXY + cgrp * 16, v);
-            tmem_ld_wait();
-            if (t < valid) {
-                __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + t) * H + h) * kN + cgrp * 16;
+            // y[t][i]: this thread holds value channel i = zj for tokens 16*cgrp .. +15
+            __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + cgrp * 16) * H + h) * kN + zj;
 #pragma unroll
-                for (int e8 = 0; e8 < 2; ++e8) {
-                    uint4 o;
-                    unsigned *ow = &o.x;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[e8 * 8 + 2 * e]),
-                                                                        __uint_as_float(v[e8 * 8 + 2 * e + 1]));
-                        ow[e] = *reinterpret_cast<const unsigned *>(&h2);
-                    }
-                    *reinterpret_cast<uint4 *>(dst + e8 * 8) = o;
-                }
-            }
+            for (int e = 0; e < 16; ++e)
+                if (cgrp * 16 + e < valid) dst[(size_t)e * H * kN] = __float2bfloat16_rn(__uint_as_float(yv[e]));
         }
         // No CTA barrier here: the next chunk's phase A touches neither TMEM nor any
         // buffer this hop reads (exp(c_L) is kept per chunk parity), and its own
@@ -561,7 +527,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     if (tid == 0) flags[bh] = bad_decay ? 1 : 0;
     if (!failed && s_out != nullptr && quarter < 2) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) s_out[((size_t)bh * kN + cgrp * 16 + e) * kN + zj] = Z[e];
+        for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<float4 *>(s_out + ((size_t)bh * kN + zj) * kN + cgrp * 16 + 4 * q4) =
+                make_float4(Z[4 * q4], Z[4 * q4 + 1], Z[4 * q4 + 2], Z[4 * q4 + 3]);
     }
     tc_fence_before();
     __syncthreads();
