@@ -67,13 +67,22 @@ constexpr uint32_t kMiscBytes = 1024;
 constexpr uint32_t kSmemBytes = kOffMisc + kMiscBytes + 1024;  // + alignment slack
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 
-// fp32 scratch matrices of the triangular inverse, row pitch 68 floats, inside the
+// fp32 scratch of the triangular solve: the diagonal 16 x 16 blocks of A_ab, inside the
 // raw-tile region (free between phase A and the next TMA request).
-constexpr int kPitch = 68;
-constexpr uint32_t kOffAm = kOffRaw;                          // A_ab   [64][68]
-constexpr uint32_t kOffTm = kOffAm + 64 * kPitch * 4;         // T      [64][68]
-constexpr uint32_t kOffPm = kOffTm + 64 * kPitch * 4;         // P      [32][68]
-static_assert(kOffPm + 32 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
+#ifndef RWKV7_SOLVE_BLOCK
+#define RWKV7_SOLVE_BLOCK 16
+#endif
+#ifndef RWKV7_TRUNC_DEBIAS
+#define RWKV7_TRUNC_DEBIAS 3.4e-4f
+#endif
+constexpr int kBlk = RWKV7_SOLVE_BLOCK;   // token block of the triangular solve (16 or 32)
+// An MMA whose A operand is read from TMEM truncates that operand to tf32, losing on
+// average about 0.7 * 2^-11 of its magnitude.  The shared-memory operand of such an MMA
+// is scaled up by the same factor before it is rounded, which removes the bias.
+constexpr float kDebias = 1.f + RWKV7_TRUNC_DEBIAS;
+constexpr int kPitch = 20;   // floats per scratch row (conflict-free 16-byte stores)
+constexpr uint32_t kOffAm = kOffRaw;                          // diagonal blocks of A_ab [64][20]
+static_assert(kOffAm + 64 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
 
 // TMEM columns.
 constexpr uint32_t kColG = 0, kColXT = 128, kColUT = 192, kColYT = 256, kColDS = 320, kTmemCols = 512;
@@ -139,39 +148,20 @@ __device__ __forceinline__ void mma_k64_ts(uint32_t d_tmem, uint32_t a_tmem, uin
     }
 }
 
-// 2x2 output tile: rows P0, P1 against columns Q[.][0], Q[.][1] (Q 8-byte aligned).
-template <int K>
-__device__ __forceinline__ void dot_2x2(const float *P0, const float *P1, const float *Q, float (&o)[4]) {
-    float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;
+// D[128 x N] (+)= A[tmem, 8 columns per K-step] * B^T, B = rows row0.. and columns col0..
+// of a 128-row K-major tile whose K-step-0 descriptor is `tile0`.
+template <int N>
+__device__ __forceinline__ void mma_ts_block(uint32_t d_tmem, uint32_t a_tmem, uint64_t tile0, int row0, int col0,
+                                             int ksteps, bool accumulate) {
+    constexpr uint32_t idesc = make_idesc(kFmtTF32, 128, N, false, false);
 #pragma unroll
-    for (int k4 = 0; k4 < K / 4; ++k4) {
-        const float4 p0 = *reinterpret_cast<const float4 *>(P0 + 4 * k4);
-        const float4 p1 = *reinterpret_cast<const float4 *>(P1 + 4 * k4);
-        const float x0[4] = {p0.x, p0.y, p0.z, p0.w}, x1[4] = {p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 q = *reinterpret_cast<const float2 *>(Q + (4 * k4 + e) * kPitch);
-            a00 = fmaf(x0[e], q.x, a00);
-            a01 = fmaf(x0[e], q.y, a01);
-            a10 = fmaf(x1[e], q.x, a10);
-            a11 = fmaf(x1[e], q.y, a11);
+    for (int ks = 0; ks < 8; ++ks) {
+        if (ks < ksteps) {
+            const int col = col0 + 8 * ks;
+            const uint64_t bo = (uint64_t)(((col >> 5) * 128 * 128 + row0 * 128 + (col & 31) * 4) >> 4);
+            umma_tf32_ts(d_tmem, a_tmem + ks * 8, tile0 + bo, idesc, accumulate || ks > 0);
         }
     }
-    o[0] = a00; o[1] = a01; o[2] = a10; o[3] = a11;
-}
-
-template <int K>
-__device__ __forceinline__ float dot_rows(const float *P_row, const float *Q_col) {
-    float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-    for (int k4 = 0; k4 < K / 4; ++k4) {
-        const float4 p = *reinterpret_cast<const float4 *>(P_row + 4 * k4);
-        acc0 = fmaf(p.x, Q_col[(4 * k4 + 0) * kPitch], acc0);
-        acc1 = fmaf(p.y, Q_col[(4 * k4 + 1) * kPitch], acc1);
-        acc0 = fmaf(p.z, Q_col[(4 * k4 + 2) * kPitch], acc0);
-        acc1 = fmaf(p.w, Q_col[(4 * k4 + 3) * kPitch], acc1);
-    }
-    return acc0 + acc1;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -189,11 +179,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     unsigned char *raw = smem + kOffRaw, *tAR = smem + kOffAR, *tBK = smem + kOffBK, *tZT = smem + kOffZT,
                   *tS = smem + kOffS, *tVT = smem + kOffVT, *tAKRK = smem + kOffAKRK, *tXU = smem + kOffXU;
     float *Am = reinterpret_cast<float *>(smem + kOffAm);
-    float *Tm = reinterpret_cast<float *>(smem + kOffTm);
-    float *Pm = reinterpret_cast<float *>(smem + kOffPm);
     float *grp_tot = reinterpret_cast<float *>(tXU);  // [8][64], phase A only
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
+    uint64_t *bar_dep = bar_tma + 3;   // used by the MMA-issuing thread alone, between dependent MMAs
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc + 16);
     float *exp_cl = reinterpret_cast<float *>(smem + kOffMisc + 64);   // [2][64] exp(c_L), by chunk parity
     int *unsafe = reinterpret_cast<int *>(exp_cl + 128);
@@ -208,6 +197,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     if (tid == 0) {
         mbar_init(bar_tma, 1);
         mbar_init(bar_mma, 1);
+        mbar_init(bar_dep, 1);
         mbar_fence_init();
         *unsafe = 0;
 #pragma unroll
@@ -251,7 +241,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                    dZT = desc_kmajor(smem_u32(tZT), 128, 0),
                    dS = desc_kmajor(smem_u32(tS), 64, 0), dVT = desc_kmajor(smem_u32(tVT), 64, 0),
                    dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0);
-    uint32_t mma_phase = 0;
+    uint32_t mma_phase = 0, dep_phase = 0;
     bool failed = false;
     int tma_issued = 1, tma_consumed = 0;  // tile batches requested / received
 
@@ -317,12 +307,13 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 float einv;                             // exp(-c_t)
                 asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(einv) : "f"(e));
                 vv[u] = ld(TV, u);                      // bf16 values are tf32-exact
-                bhv[u] = round_tf32(ld(TB, u) * einv);
+                const float bh = ld(TB, u) * einv;
+                bhv[u] = round_tf32(bh * kDebias);   // transposed copy: operand of dS += U^T Bh
                 khv[u] = round_tf32(ld(TK, u) * einv);
                 const uint32_t o = (uint32_t)u * 128u + (cb ^ ((uint32_t)u << 4));
                 *reinterpret_cast<float *>(pAR + o) = round_tf32(ld(TA, u) * e_prev);
                 *reinterpret_cast<float *>(pAR + 64 * 128 + o) = round_tf32(ld(TR, u) * e);
-                *reinterpret_cast<float *>(pBK + o) = bhv[u];
+                *reinterpret_cast<float *>(pBK + o) = round_tf32(bh);
                 *reinterpret_cast<float *>(pBK + 64 * 128 + o) = khv[u];
                 e_prev = e;
             }
@@ -358,7 +349,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             tmem_ld32(tmem + lane_base + kColG + cgrp * 32, v);
             tmem_ld_wait();
             if (cgrp < 2 && !upper) {
-                // A_ab: exact fp32 into the inverse's scratch matrix
+                // A_ab: tf32 into rows 0..63 of the [T;A_rb] tile (its blocks below the block
+                // diagonal are operands of the solve as they are), and the diagonal 16x16
+                // block of this row in exact fp32 into the scratch of the block inverses.
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     float4 o;
@@ -366,12 +359,23 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int s = s_base + e4 * 4 + e;
-                        of[e] = (s <= lim) ? __uint_as_float(v[e4 * 4 + e]) : 0.f;
+                        v[e4 * 4 + e] = (s <= lim) ? v[e4 * 4 + e] : 0u;
+                        of[e] = round_tf32(__uint_as_float(v[e4 * 4 + e]) * kDebias);
                     }
-                    *reinterpret_cast<float4 *>(Am + t * kPitch + s_base + e4 * 4) = o;
+                    st_tile4(tBK, 128, t, s_base + e4 * 4, o);
+                }
+                const int rb = t >> 4;
+                if ((rb >> 1) == (cgrp & 1)) {
+                    const bool hi = rb & 1;
+#pragma unroll
+                    for (int e4 = 0; e4 < 4; ++e4)
+                        *reinterpret_cast<uint4 *>(Am + t * kPitch + e4 * 4) =
+                            make_uint4(hi ? v[16 + e4 * 4] : v[e4 * 4], hi ? v[17 + e4 * 4] : v[e4 * 4 + 1],
+                                       hi ? v[18 + e4 * 4] : v[e4 * 4 + 2], hi ? v[19 + e4 * 4] : v[e4 * 4 + 3]);
                 }
             } else {
                 unsigned char *dst = (cgrp < 2) ? tBK : tAKRK;   // A_rb under T, or [A_ak;A_rk]
+                const float scale = (cgrp < 2) ? kDebias : 1.f;   // A_rb meets U^T read from TMEM
                 const int row = upper ? 64 + t : t;
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
@@ -380,7 +384,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int s = s_base + e4 * 4 + e;
-                        of[e] = (s <= lim) ? round_tf32(__uint_as_float(v[e4 * 4 + e])) : 0.f;
+                        of[e] = (s <= lim) ? round_tf32(__uint_as_float(v[e4 * 4 + e]) * scale) : 0.f;
                     }
                     st_tile4(dst, 128, row, s_base + e4 * 4, o);
                 }
@@ -389,13 +393,14 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         tc_fence_before();
         __syncthreads();
         if (*unsafe) { failed = true; break; }
-        // ---------------- T = (I - A_ab)^-1, blocked: 16x16 diagonal blocks by forward
-        // substitution, then the off-diagonal blocks T_ba = T_bb A_ba T_aa at block
-        // sizes 16 and 32.  All in fp32 on the scratch matrices.
+        // ---------------- U = (I - A_ab)^-1 X is solved block-wise with 16-token blocks:
+        // only the diagonal blocks T_bb = (I - A_bb)^-1 are formed here (forward substitution
+        // in fp32, one column per thread); the coupling between blocks is part of the MMA
+        // chain below.
         PHASE(5);
         if (tid < 64) {
             const int b = tid >> 4, cc = tid & 15;
-            const float *Ab = Am + (16 * b) * kPitch + 16 * b;
+            const float *Ab = Am + (16 * b) * kPitch;
             float x[16];
 #pragma unroll
             for (int t = 0; t < 16; ++t) {
@@ -409,53 +414,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     if (4 * s4 + 3 < t) acc1 = fmaf(a4.w, x[4 * s4 + 3], acc1);
                 }
                 x[t] = (t == cc) ? 1.f : ((t > cc) ? acc0 + acc1 : 0.f);
-                Tm[(16 * b + t) * kPitch + 16 * b + cc] = x[t];
+                *reinterpret_cast<float *>(tBK + tile_off_f32(128, 16 * b + t, 16 * b + cc)) = round_tf32(x[t] * kDebias);
             }
-        }
-        __syncthreads();
-        PHASE(13);
-        {   // block size 16: P = A_ba T_aa for (a,b) = (0,1) and (2,3)
-            const int sb = tid >> 8, r = (tid >> 4) & 15, cc = tid & 15;
-            const int a0 = 32 * sb, b0 = a0 + 16;
-            Pm[(16 * sb + r) * kPitch + cc] = dot_rows<16>(Am + (b0 + r) * kPitch + a0, Tm + a0 * kPitch + a0 + cc);
-            Tm[(a0 + r) * kPitch + b0 + cc] = 0.f;  // block above the diagonal, read by the 32-wide products
-        }
-        __syncthreads();
-        {   // T_ba = T_bb P
-            const int sb = tid >> 8, r = (tid >> 4) & 15, cc = tid & 15;
-            const int a0 = 32 * sb, b0 = a0 + 16;
-            Tm[(b0 + r) * kPitch + a0 + cc] = dot_rows<16>(Tm + (b0 + r) * kPitch + b0, Pm + (16 * sb) * kPitch + cc);
-        }
-        __syncthreads();
-        PHASE(14);
-        if (tid < 256) {   // block size 32: P = A_BA T_AA, a 2x2 output tile per thread
-            const int r = 2 * (tid >> 4), cc = 2 * (tid & 15);
-            float o[4];
-            dot_2x2<32>(Am + (32 + r) * kPitch, Am + (33 + r) * kPitch, Tm + cc, o);
-            *reinterpret_cast<float2 *>(Pm + r * kPitch + cc) = make_float2(o[0], o[1]);
-            *reinterpret_cast<float2 *>(Pm + (r + 1) * kPitch + cc) = make_float2(o[2], o[3]);
-        } else {           // meanwhile: the finished blocks T_AA, T_BB -> tf32 operand tile rows 0..63
-#pragma unroll
-            for (int rep = 0; rep < 3; ++rep) {
-                const int idx = (tid - 256) + 256 * rep;
-                const int t = idx < 512 ? (idx >> 4) : 32 + ((idx - 512) >> 3);
-                const int cb = idx < 512 ? 4 * (idx & 15) : 32 + 4 * ((idx - 512) & 7);
-                const float4 x = *reinterpret_cast<const float4 *>(Tm + t * kPitch + cb);
-                float4 o;
-                o.x = (cb + 0 <= t) ? round_tf32(x.x) : 0.f;
-                o.y = (cb + 1 <= t) ? round_tf32(x.y) : 0.f;
-                o.z = (cb + 2 <= t) ? round_tf32(x.z) : 0.f;
-                o.w = (cb + 3 <= t) ? round_tf32(x.w) : 0.f;
-                st_tile4(tBK, 128, t, cb, o);
-            }
-        }
-        __syncthreads();
-        if (tid < 256) {   // T_BA = T_BB P, written straight into the operand tile
-            const int r = 2 * (tid >> 4), cc = 2 * (tid & 15);
-            float o[4];
-            dot_2x2<32>(Tm + (32 + r) * kPitch + 32, Tm + (33 + r) * kPitch + 32, Pm + cc, o);
-            *reinterpret_cast<float2 *>(tBK + tile_off_f32(128, 32 + r, cc)) = make_float2(round_tf32(o[0]), round_tf32(o[1]));
-            *reinterpret_cast<float2 *>(tBK + tile_off_f32(128, 33 + r, cc)) = make_float2(round_tf32(o[2]), round_tf32(o[3]));
         }
         fence_proxy_async();
         __syncthreads();  // scratch matrices are dead: the raw-tile region may be refilled
@@ -471,16 +431,44 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         if (tid == 0) {
             tc_fence_after();
             constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
+            // An MMA that reads a TMEM operand written by an earlier MMA is ordered after it
+            // only through a commit and a wait: MMAs with different accumulators are not
+            // guaranteed to execute in issue order.
+            auto dep_sync = [&]() {
+                umma_commit(bar_dep);
+                if (!mbar_wait_spin(bar_dep, dep_phase)) atomicOr(unsafe, 2);
+                dep_phase ^= 1;
+                tc_fence_after();
+            };
+            mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
+            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
+            umma_commit(bar_dep);
+            // independent of X^T: they run while the commit above travels
             mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
             mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, true);    // Y^T += V^T A_rk^T
             mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
-            mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
-            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
-            mma_k64_ts<128, 64>(tmem + kColUT, tmem + kColXT, dBK, false);     // U^T  = X^T T^T
+            if (!mbar_wait_spin(bar_dep, dep_phase)) atomicOr(unsafe, 2);
+            dep_phase ^= 1;
+            tc_fence_after();
+            // U^T = X^T (I - A_ab)^-T by block forward substitution over the token blocks b:
+            // X_b^T += U_{<b}^T A_{b,<b}^T, then U_b^T = X_b^T T_bb^T.
+#pragma unroll
+            for (int b = 0; b < kL / kBlk; ++b) {
+                if (b > 0) {
+                    mma_ts_block<kBlk>(tmem + kColXT + b * kBlk, tmem + kColUT, dBK, b * kBlk, 0, b * kBlk / 8, true);
+                    dep_sync();
+                }
+                mma_ts_block<kBlk>(tmem + kColUT + b * kBlk, tmem + kColXT + b * kBlk, dBK, b * kBlk, b * kBlk,
+                                   kBlk / 8, false);
+                dep_sync();
+            }
             mma_k64_ts<128, 64>(tmem + kColYT, tmem + kColUT, dBK + kLower, true);   // Y^T += U^T A_rb^T
             mma_k64_ts<128, 64>(tmem + kColDS, tmem + kColUT, dZT, true);      // dS  += U^T Bh
             umma_commit(bar_mma);
         }
+        // The other lanes of the issuing warp must not poll the barrier below while lane 0 is
+        // still issuing: a suspended poll would stall lane 0's own waits between dependent MMAs.
+        __syncwarp();
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
         mma_phase ^= 1;
         tc_fence_after();
