@@ -241,6 +241,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                    dZT = desc_kmajor(smem_u32(tZT), 128, 0),
                    dS = desc_kmajor(smem_u32(tS), 64, 0), dVT = desc_kmajor(smem_u32(tVT), 64, 0),
                    dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0);
+    constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
     uint32_t mma_phase = 0, dep_phase = 0;
     bool failed = false;
     int tma_issued = 1, tma_consumed = 0;  // tile batches requested / received
@@ -334,6 +335,11 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             tc_fence_after();
             mma_k64<128, 128, 128>(tmem + kColG, dAR, dBK, false);
             umma_commit(bar_mma);
+            // State path, part 1: value-major products (M = value index i, 64 valid lanes) that
+            // need only this chunk's scaled operands.  They run while G is read back below.
+            mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
+            mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
+            mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
         mma_phase ^= 1;
@@ -390,16 +396,25 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 }
             }
         }
+        fence_proxy_async();
         tc_fence_before();
         __syncthreads();
         if (*unsafe) { failed = true; break; }
+        // ---------------- state path, part 2: the products with the masked A_ak, A_rk just
+        // staged; they run on the tensor core while the diagonal blocks are inverted below.
+        if (tid == 0) {
+            tc_fence_after();
+            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
+            mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, true);    // Y^T += V^T A_rk^T
+            umma_commit(bar_dep);
+        }
         // ---------------- U = (I - A_ab)^-1 X is solved block-wise with 16-token blocks:
         // only the diagonal blocks T_bb = (I - A_bb)^-1 are formed here (forward substitution
         // in fp32, one column per thread); the coupling between blocks is part of the MMA
         // chain below.
         PHASE(5);
-        if (tid < 64) {
-            const int b = tid >> 4, cc = tid & 15;
+        if (tid >= 64 && tid < 128) {   // warps 2 and 3: warp 0 is busy issuing
+            const int b = (tid - 64) >> 4, cc = tid & 15;
             const float *Ab = Am + (16 * b) * kPitch;
             float x[16];
 #pragma unroll
@@ -423,47 +438,41 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             if (tid == 32) issue_tma(chunk + 1);   // not the thread that issues the MMAs
             ++tma_issued;
         }
-        // ---------------- state path: eight MMA groups chained through TMEM, one commit.
-        // Value-major products (M = value index i, 64 valid lanes): X^T and U^T stay in
-        // TMEM and feed the next group as its A operand; the B operands are the K-major
-        // tiles staged above.  Order: the groups that do not depend on X^T / U^T first.
+        // ---------------- state path, part 3: the triangular solve and what depends on U.
+        // X^T and U^T stay in TMEM and feed later MMAs as their A operand.  An MMA that
+        // reads a TMEM operand written by an earlier MMA is ordered after it only through a
+        // commit and a wait (MMAs with different accumulators are not guaranteed to execute
+        // in issue order); MMAs that do not depend on the pending result are issued between
+        // the commit and the wait so that the tensor core stays busy.
         PHASE(6);
         if (tid == 0) {
-            tc_fence_after();
-            constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
-            // An MMA that reads a TMEM operand written by an earlier MMA is ordered after it
-            // only through a commit and a wait: MMAs with different accumulators are not
-            // guaranteed to execute in issue order.
-            auto dep_sync = [&]() {
-                umma_commit(bar_dep);
+            auto dep_commit = [&]() { umma_commit(bar_dep); };
+            auto dep_wait = [&]() {
                 if (!mbar_wait_spin(bar_dep, dep_phase)) atomicOr(unsafe, 2);
                 dep_phase ^= 1;
                 tc_fence_after();
             };
-            mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
-            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
-            umma_commit(bar_dep);
-            // independent of X^T: they run while the commit above travels
-            mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
-            mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, true);    // Y^T += V^T A_rk^T
-            mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
-            if (!mbar_wait_spin(bar_dep, dep_phase)) atomicOr(unsafe, 2);
-            dep_phase ^= 1;
-            tc_fence_after();
+            auto leaves = [&](int b) {   // what U_b^T contributes to Y^T and dS
+                mma_ts_block<64>(tmem + kColYT, tmem + kColUT + b * kBlk, dBK, 64, b * kBlk, kBlk / 8, true);   // A_rb
+                mma_ts_block<64>(tmem + kColDS, tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, kBlk / 8, true);    // Bh
+            };
+            dep_wait();   // parts 1 and 2 have finished: X^T is complete
             // U^T = X^T (I - A_ab)^-T by block forward substitution over the token blocks b:
             // X_b^T += U_{<b}^T A_{b,<b}^T, then U_b^T = X_b^T T_bb^T.
 #pragma unroll
             for (int b = 0; b < kL / kBlk; ++b) {
                 if (b > 0) {
                     mma_ts_block<kBlk>(tmem + kColXT + b * kBlk, tmem + kColUT, dBK, b * kBlk, 0, b * kBlk / 8, true);
-                    dep_sync();
+                    dep_commit();
+                    leaves(b - 1);   // independent of the pending result
+                    dep_wait();
                 }
                 mma_ts_block<kBlk>(tmem + kColUT + b * kBlk, tmem + kColXT + b * kBlk, dBK, b * kBlk, b * kBlk,
                                    kBlk / 8, false);
-                dep_sync();
+                dep_commit();
+                dep_wait();
             }
-            mma_k64_ts<128, 64>(tmem + kColYT, tmem + kColUT, dBK + kLower, true);   // Y^T += U^T A_rb^T
-            mma_k64_ts<128, 64>(tmem + kColDS, tmem + kColUT, dZT, true);      // dS  += U^T Bh
+            leaves(kL / kBlk - 1);
             umma_commit(bar_mma);
         }
         // The other lanes of the issuing warp must not poll the barrier below while lane 0 is
