@@ -274,6 +274,83 @@ class Wkv7StatepassCall:
             _check(st)
 
 
+class Wkv7HostStatepass:
+    """Statepass for callers whose six sequence tensors, y and S_T live in pinned
+    host memory (an inference server that receives activations from another
+    process, a benchmark that counts the copies).  The batch is cut into equal
+    slices; slice ``i`` uses stream ``i % n_streams`` for its host-to-device copies,
+    its kernel and its device-to-host copies, so the copy of one slice overlaps
+    the kernel and the copy-back of the slices before it.  (b,h) chains are
+    independent, so slicing the batch changes no arithmetic: results are bitwise
+    those of one call on the whole batch.
+
+    ``host_state_in`` may be None (S0 = 0).  Device staging buffers for
+    ``n_streams`` slices are allocated once, here; ``__call__`` allocates nothing.
+    The call is asynchronous: work is ordered after the caller's current stream, and
+    the current stream waits for it, so ``torch.cuda.current_stream().synchronize()``
+    (or an event recorded after the call) marks completion."""
+
+    def __init__(self, host_six: Sequence[torch.Tensor], host_state_in: Optional[torch.Tensor],
+                 host_output: torch.Tensor, host_state_out: torch.Tensor, *, device,
+                 slices: Optional[int] = None, n_streams: int = 3, chunk_len: int = 16):
+        r = host_six[0]
+        if r.dim() != 4:
+            raise KernelInputsError(1, "AxisMismatch: expected [B, T, H, N] host tensors")
+        B, T, H, N = r.shape
+        for t in list(host_six) + [host_output, host_state_out] + ([host_state_in] if host_state_in is not None else []):
+            if t.is_cuda or not t.is_pinned() or not t.is_contiguous():
+                raise KernelInputsError(6, "NotContiguous: host tensors must be contiguous pinned CPU tensors")
+        if slices is None:
+            slices = next(s for s in (8, 4, 2, 1) if B % s == 0)
+        if slices < 1 or B % slices:
+            raise KernelInputsError(2, f"ShapeMismatch: {slices} slices do not divide B={B}")
+        self._device = torch.device(device)
+        self._rows = B // slices
+        self._slices = slices
+        n_streams = max(1, min(n_streams, slices))
+        self._streams = [torch.cuda.Stream(self._device) for _ in range(n_streams)]
+        self._host = (list(host_six), host_state_in, host_output, host_state_out)
+        self._sets = []
+        for _ in range(n_streams):
+            six = [torch.empty((self._rows, T, H, N), dtype=r.dtype, device=self._device) for _ in range(6)]
+            s_in = torch.zeros((self._rows, H, N, N), dtype=torch.float32, device=self._device)
+            y = torch.empty_like(six[0])
+            s_out = torch.empty_like(s_in)
+            ws, _ = _wkv7_workspace(six[0])
+            seq = Wkv7PretrainForwardInputs(*six, chunk_len=chunk_len)
+            self._sets.append((six, s_in, y, s_out, Wkv7StatepassCall(s_in, seq, y, s_out, ws)))
+
+    def __call__(self) -> None:
+        host_six, host_s_in, host_y, host_s_out = self._host
+        cur = torch.cuda.current_stream(self._device)
+        start = cur.record_event()
+        for st in self._streams:
+            st.wait_event(start)
+        n = len(self._streams)
+        for i in range(self._slices):
+            b0, b1 = i * self._rows, (i + 1) * self._rows
+            six, s_in, y, s_out, call = self._sets[i % n]
+            with torch.cuda.stream(self._streams[i % n]):
+                for d, h in zip(six, host_six):
+                    d.copy_(h[b0:b1], non_blocking=True)
+                if host_s_in is not None:
+                    s_in.copy_(host_s_in[b0:b1], non_blocking=True)
+                call()
+                host_y[b0:b1].copy_(y, non_blocking=True)
+                host_s_out[b0:b1].copy_(s_out, non_blocking=True)
+        for st in self._streams:
+            cur.wait_event(st.record_event())
+
+    def bytes_per_call(self) -> tuple[int, int]:
+        """(host-to-device, device-to-host) bytes one call moves."""
+        host_six, host_s_in, host_y, host_s_out = self._host
+        h2d = sum(t.numel() * t.element_size() for t in host_six)
+        if host_s_in is not None:
+            h2d += host_s_in.numel() * host_s_in.element_size()
+        d2h = host_y.numel() * host_y.element_size() + host_s_out.numel() * host_s_out.element_size()
+        return h2d, d2h
+
+
 def wkv7_statepass_noalloc(initial_state: torch.Tensor, sequence: Wkv7PretrainForwardInputs,
                            output: torch.Tensor, next_state: torch.Tensor) -> Wkv7StatepassForwardOutput:
     """``rwkv7_fused_wkv7_statepass_noalloc``: the statepass for callers that must

@@ -218,6 +218,30 @@ def test_shard_equals_single(pkg, workloads, cuda):
         assert torch.equal(part.next_state, full.next_state[bs, hs])
 
 
+def test_host_pipeline_equals_single_call(pkg, workloads, cuda):
+    """Pinned host buffers in and out, the batch cut into slices on several streams:
+    bitwise the result of one device-resident call on the whole batch."""
+    inp = workloads.wkv7_inputs(4, 192, 3, 64, seed=12, dtype=torch.bfloat16, state="normal")
+    gpu = {k: v.to(cuda) for k, v in inp.items()}
+    full = pkg.wkv7_statepass_custom(gpu["s0"], pkg.Wkv7PretrainForwardInputs(*[gpu[n] for n in "rwkvab"]),
+                                     reference_contract=False)
+    host_six = [inp[n].pin_memory() for n in "rwkvab"]
+    s_in = inp["s0"].pin_memory()
+    y_host = torch.empty(inp["r"].shape, dtype=torch.bfloat16).pin_memory()
+    s_host = torch.empty(inp["s0"].shape, dtype=torch.float32).pin_memory()
+    for slices, n_streams in ((4, 3), (2, 2), (1, 1)):
+        y_host.zero_(); s_host.zero_()
+        run = pkg.Wkv7HostStatepass(host_six, s_in, y_host, s_host, device=cuda, slices=slices, n_streams=n_streams)
+        run()
+        run()   # staging buffers are reused: a second call must give the same result
+        torch.cuda.current_stream(cuda).synchronize()
+        assert torch.equal(y_host, full.output.cpu())
+        assert torch.equal(s_host, full.next_state.cpu())
+        assert run.bytes_per_call() == (6 * y_host.numel() * 2 + s_in.numel() * 4, y_host.numel() * 2 + s_host.numel() * 4)
+    with pytest.raises(pkg.KernelInputsError):
+        pkg.Wkv7HostStatepass(host_six, s_in, y_host, s_host, device=cuda, slices=3)
+
+
 def test_full_size_config1_properties(pkg, workloads, cuda):
     """Benchmark configuration 1 (B=8, T=4096, H=12, N=64, bf16) is too long for the
     CPU oracle inside a test; check size-independent properties instead:
