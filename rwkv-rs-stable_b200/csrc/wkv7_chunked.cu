@@ -13,11 +13,14 @@
 //     G  = [At;Rt] [Bh;Kh]^T                     (128 x 128, one MMA group)
 //     A_ab = strict_lower(At Bh^T)  A_ak = strict_lower(At Kh^T)
 //     A_rb = lower(Rt Bh^T)         A_rk = lower(Rt Kh^T)
-//     T  = (I - A_ab)^-1                         (unit lower triangular, CUDA cores)
-//     X  = At Z0 + A_ak V           U = T X      (u_t = S_{t-1} a_t)
+//     X  = At Z0 + A_ak V           U = (I - A_ab)^-1 X      (u_t = S_{t-1} a_t)
+//         solved by 16-token blocks: T_bb = (I - A_bb)^-1 on CUDA cores, then
+//         X_b += A_{b,<b} U_{<b}, U_b = T_bb X_b on the tensor core
 //     Y  = Rt Z0 + A_rb U + A_rk V
 //     Z1 = diag(exp(c_L)) (Z0 + Bh^T U + Kh^T V)
-// Every MMA operand is fp32 rounded to tf32 (round-to-nearest) in shared memory;
+// The state path is computed transposed (value index on the TMEM lanes), so X^T
+// and U^T stay in TMEM and are the A operand of the MMAs that consume them.
+// Every shared-memory MMA operand is fp32 rounded to tf32 (round-to-nearest);
 // accumulation is fp32 in TMEM; the state itself never leaves fp32 registers
 // except as a tf32-rounded MMA operand.  exp(-c_t) stays finite because the
 // kernel requires |c_L| <= 80 per chunk (the model's decay range gives <= 38.9);
