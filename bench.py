@@ -350,6 +350,20 @@ def main():
                                        2 * 2 * elems),
         }
         del x, diff, mus
+        # the two time-mixer epilogues at the same layer shape (H = C / 64 heads)
+        Hs = Cs // 64
+        ep = workloads.time_mixer_epilogue_inputs(Bs, Ts, Hs, 64, seed=6, dtype=torch.bfloat16, device=dev)
+        wp = [ep[n] for n in ("key_precursor", "learning_rate_lora", "weight_decay_lora", "key_removal",
+                              "key_replacement")]
+        gr = [ep[n] for n in ("wkv7_output", "receptance", "replacement_key", "value", "gate",
+                              "group_norm_gamma", "group_norm_beta", "receptance_key_bonus")]
+        streaming["weight_prepare"] = timeit(
+            lambda: pkg.weight_prepare_epilogue(*wp, Hs, value_precursor=ep["value_precursor"],
+                                                value_from_first_cell=ep["value_from_first_cell"],
+                                                value_residual_lora=ep["value_residual_lora"]),
+            11 * 2 * elems)
+        streaming["gated_readout"] = timeit(lambda: pkg.gated_readout_epilogue(*gr, Hs), 6 * 2 * elems)
+        del ep, wp, gr
 
     # ---- fused LM-head cross entropy at the configuration-2 shape (tensor-core-bound) -----
     lm_head = None

@@ -233,6 +233,53 @@ int rwkv7_fused_token_shift_diff(const rwkv7_tensor *embedded_context,
                                  const rwkv7_tensor *batch_ids, rwkv7_tensor *token_shifted_diff,
                                  rwkv7_stream stream);
 
+/* -------------------------------------------------- time-mixer epilogues -- */
+/*
+ * The tail of WeightPrepare::forward (modules/time_mixer/weight_prepare.rs:252-287,
+ * functions/normalize.rs:9-41, functions/lerp.rs:4-10) in one pass.  The reference
+ * has no single operator for it: these are the tensor ops between the dense
+ * projections / LoRA products and the WKV7 call.  With lr = sigmoid(learning_rate_lora):
+ *   replacement_key        = key_precursor * (key_replacement * (lr - 1) + 1)
+ *   weight_decay           = -softplus(-weight_decay_lora) - 0.5
+ *   removal_key_normalized = -(key_precursor * key_removal) / max(||.||_2 over the head, 1e-12)
+ *   replacement            = -removal_key_normalized * lr
+ *   value                  = value_precursor + (value_from_first_cell - value_precursor)
+ *                            * sigmoid(value_residual_lora)       (cells after the first)
+ * The big tensors are [B,T,C] (or [B,T,H,N], the same memory) with C = num_heads * N;
+ * key_removal and key_replacement hold C elements ([1,1,C]).  The three value inputs
+ * and `value` are either all given or all NULL (first cell: value = value_precursor,
+ * nothing to compute).  Arithmetic is fp32, each output rounded once.
+ */
+int rwkv7_fused_weight_prepare(const rwkv7_tensor *key_precursor,
+                               const rwkv7_tensor *learning_rate_lora,
+                               const rwkv7_tensor *weight_decay_lora,
+                               const rwkv7_tensor *key_removal,
+                               const rwkv7_tensor *key_replacement,
+                               const rwkv7_tensor *value_precursor,
+                               const rwkv7_tensor *value_from_first_cell,
+                               const rwkv7_tensor *value_residual_lora, int64_t num_heads,
+                               rwkv7_tensor *weight_decay, rwkv7_tensor *replacement_key,
+                               rwkv7_tensor *removal_key_normalized, rwkv7_tensor *replacement,
+                               rwkv7_tensor *value, rwkv7_stream stream);
+
+/*
+ * The body of GatedReadout::forward between the gate LoRA and the output projection
+ * (modules/time_mixer/gated_readout.rs:110-145) in one pass:
+ *   norm   = GroupNorm(num_groups = num_heads, eps = epsilon; the module uses 64e-5)
+ *            of wkv7_output per (b,t): (y - mean_h) / sqrt(var_h + eps) * gamma + beta,
+ *            mean and (biased) variance over the N channels of head h
+ *   bonus  = (sum_n receptance * replacement_key * receptance_key_bonus[h,n]) * value
+ *   output = (norm + bonus) * gate
+ * Big tensors [B,T,C] or [B,T,H,N]; group_norm_gamma, group_norm_beta and
+ * receptance_key_bonus ([H,N]) hold C elements each.
+ */
+int rwkv7_fused_gated_readout(const rwkv7_tensor *wkv7_output, const rwkv7_tensor *receptance,
+                              const rwkv7_tensor *replacement_key, const rwkv7_tensor *value,
+                              const rwkv7_tensor *gate, const rwkv7_tensor *group_norm_gamma,
+                              const rwkv7_tensor *group_norm_beta,
+                              const rwkv7_tensor *receptance_key_bonus, double epsilon,
+                              int64_t num_heads, rwkv7_tensor *output, rwkv7_stream stream);
+
 /* ------------------------------------------------------------ lm_head_ce -- */
 /*
  * Fused LM-head cross entropy.  The reference only reserves the module

@@ -170,6 +170,46 @@ inline void token_shift_diff_custom(const TensorView &embedded_context, TensorVi
                                               token_shifted_diff.m(), stream));
 }
 
+// Tail of WeightPrepare::forward (modules/time_mixer/weight_prepare.rs:252-287); field names
+// follow WeightPrepareOutput (:289-297).  Leave the three value inputs and `value` default-constructed
+// for the first cell.
+struct WeightPrepareEpilogueInputs {
+    TensorView key_precursor, learning_rate_lora, weight_decay_lora, key_removal, key_replacement;
+    TensorView value_precursor, value_from_first_cell, value_residual_lora;
+    int64_t num_heads = 0;
+};
+struct WeightPrepareEpilogueOutput {
+    TensorView weight_decay, replacement_key, value, removal_key_normalized, replacement;
+};
+inline void weight_prepare_epilogue(const WeightPrepareEpilogueInputs &in, WeightPrepareEpilogueOutput &out,
+                                    rwkv7_stream stream = nullptr) {
+    const bool with_value = in.value_precursor.t.data != nullptr;
+    check_status(rwkv7_fused_weight_prepare(
+        in.key_precursor.c(), in.learning_rate_lora.c(), in.weight_decay_lora.c(), in.key_removal.c(),
+        in.key_replacement.c(), with_value ? in.value_precursor.c() : nullptr,
+        with_value ? in.value_from_first_cell.c() : nullptr, with_value ? in.value_residual_lora.c() : nullptr,
+        in.num_heads, out.weight_decay.m(), out.replacement_key.m(), out.removal_key_normalized.m(),
+        out.replacement.m(), with_value ? out.value.m() : nullptr, stream));
+}
+
+// GatedReadout::forward between the gate LoRA and the output projection
+// (modules/time_mixer/gated_readout.rs:123-141); names follow GatedReadoutInput.
+struct GatedReadoutEpilogueInputs {
+    TensorView gate, wkv7_forward_output, wkv7_forward_input_receptance, wkv7_forward_input_replacement_key,
+        wkv7_forward_input_value;
+    TensorView group_norm_gamma, group_norm_beta, receptance_key_bonus;
+    double epsilon = 64e-5;
+    int64_t num_heads = 0;
+};
+inline void gated_readout_epilogue(const GatedReadoutEpilogueInputs &in, TensorView &output,
+                                   rwkv7_stream stream = nullptr) {
+    check_status(rwkv7_fused_gated_readout(
+        in.wkv7_forward_output.c(), in.wkv7_forward_input_receptance.c(),
+        in.wkv7_forward_input_replacement_key.c(), in.wkv7_forward_input_value.c(), in.gate.c(),
+        in.group_norm_gamma.c(), in.group_norm_beta.c(), in.receptance_key_bonus.c(), in.epsilon, in.num_heads,
+        output.m(), stream));
+}
+
 }  // namespace rwkv7b200
 
 #endif  // RWKV7_B200_HPP_

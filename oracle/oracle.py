@@ -94,6 +94,53 @@ def addcmul(base, diff, scales):
     return out
 
 
+def weight_prepare(key_precursor, learning_rate_lora, weight_decay_lora, key_removal, key_replacement,
+                   num_heads, value_precursor=None, value_from_first_cell=None, value_residual_lora=None):
+    """Tail of ``WeightPrepare::forward``; returns float64 ``dict(weight_decay, replacement_key,
+    removal_key_normalized, replacement, value)`` (``value`` None without the value inputs)."""
+    k = _f32(key_precursor)
+    shape = k.shape
+    C = int(np.prod(shape[2:]))
+    H = int(num_heads)
+    N = C // H
+    rows = shape[0] * shape[1] * H
+    lr, d = _f32(learning_rate_lora), _f32(weight_decay_lora)
+    xi, al = _f32(key_removal).reshape(C), _f32(key_replacement).reshape(C)
+    with_value = value_precursor is not None
+    vp = _f32(value_precursor) if with_value else None
+    vf = _f32(value_from_first_cell) if with_value else None
+    nu = _f32(value_residual_lora) if with_value else None
+    outs = {n: np.empty(shape, dtype=np.float64) for n in
+            ("weight_decay", "replacement_key", "removal_key_normalized", "replacement")}
+    value = np.empty(shape, dtype=np.float64) if with_value else None
+    null = ctypes.c_void_p(0)
+    lib().oracle_weight_prepare_f64(
+        _p(k), _p(lr), _p(d), _p(xi), _p(al), _p(vp) if with_value else null, _p(vf) if with_value else null,
+        _p(nu) if with_value else null, _p(outs["weight_decay"]), _p(outs["replacement_key"]),
+        _p(outs["removal_key_normalized"]), _p(outs["replacement"]), _p(value) if with_value else null,
+        ctypes.c_int64(rows), ctypes.c_int64(H), ctypes.c_int64(N))
+    outs["value"] = value
+    return outs
+
+
+def gated_readout(wkv7_output, receptance, replacement_key, value, gate, gamma, beta, bonus, num_heads,
+                  epsilon=64e-5):
+    """``GatedReadout::forward`` between the gate LoRA and the output projection; float64."""
+    y = _f32(wkv7_output)
+    shape = y.shape
+    C = int(np.prod(shape[2:]))
+    H = int(num_heads)
+    N = C // H
+    rows = shape[0] * shape[1] * H
+    r, k, v, g = _f32(receptance), _f32(replacement_key), _f32(value), _f32(gate)
+    ga, be, rho = _f32(gamma).reshape(C), _f32(beta).reshape(C), _f32(bonus).reshape(C)
+    out = np.empty(shape, dtype=np.float64)
+    lib().oracle_gated_readout_f64(_p(y), _p(r), _p(k), _p(v), _p(g), _p(ga), _p(be), _p(rho),
+                                   ctypes.c_double(epsilon), _p(out), ctypes.c_int64(rows),
+                                   ctypes.c_int64(H), ctypes.c_int64(N))
+    return out
+
+
 def token_shift_diff(x, state, ids):
     """Returns ``(diff, next_state)``; ``state`` is not modified."""
     x = _f32(x)

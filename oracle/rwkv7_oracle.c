@@ -25,6 +25,11 @@
  *   token_shift_diff
  *             crates/rwkv-nn/src/kernels/template/token_shift_diff/mod.rs:114-155,
  *             :170-200, kernel.rs:16-45
+ *   weight_prepare  crates/rwkv-nn/src/modules/time_mixer/weight_prepare.rs:252-287,
+ *             crates/rwkv-nn/src/functions/normalize.rs:9-41, functions/lerp.rs:4-10
+ *   gated_readout  crates/rwkv-nn/src/modules/time_mixer/gated_readout.rs:110-145
+ *             (GroupNorm itself lives in Burn, which is not part of the reference
+ *             tree: the published definition is restated, biased variance)
  *   lm_head_ce  no reference implementation exists (lm_head_l2wrap_ce/mod.rs is
  *             empty); the specification is z = x W^T, lse = log sum exp z,
  *             loss = lse - z[target].
@@ -185,6 +190,82 @@ void oracle_addcmul_f64(const float *base, const float *diff, const float *const
             for (int s = 0; s < nscale; ++s)
                 out[(int64_t)s * n + e] = (double)base[e] + (double)diff[e] * (double)scale[s][c];
         }
+}
+
+/* -------------------------------------------------- time-mixer epilogues -- */
+
+static double sigmoid64(double x) { return 1.0 / (1.0 + exp(-x)); }
+/* softplus with beta = 1: log(1 + e^z), evaluated without overflow */
+static double softplus64(double z) { return (z > 0.0 ? z : 0.0) + log1p(exp(-fabs(z))); }
+
+/*
+ * Tail of WeightPrepare::forward (weight_prepare.rs:252-287).  rows = B*T*H head
+ * rows of N channels; xi (param_key_removal) and alpha (param_key_replacement)
+ * hold H*N values.  lr = sigmoid(lr_lora) (:252);
+ *   replacement_key = k * (alpha * (lr - 1) + 1)                    (:254-257)
+ *   weight_decay    = -softplus(-d) - 0.5                            (:272-274)
+ *   removal_key_normalized = -(k*xi) / max(||k*xi||_2, 1e-12) per head   (:276-285, normalize.rs:32-40)
+ *   replacement     = -removal_key_normalized * lr                   (:287)
+ *   value           = vp + (vf - vp) * sigmoid(nu)   when vp != NULL  (:259-268, lerp.rs:9)
+ */
+void oracle_weight_prepare_f64(const float *k, const float *lr_lora, const float *d, const float *xi,
+                               const float *alpha, const float *vp, const float *vf, const float *nu,
+                               double *weight_decay, double *replacement_key, double *removal_key_normalized,
+                               double *replacement, double *value, int64_t rows, int64_t H, int64_t N) {
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < rows; ++row) {
+        const int64_t base = row * N, cbase = (row % H) * N;
+        double ss = 0.0;
+        for (int64_t n = 0; n < N; ++n) {
+            const double rk = (double)k[base + n] * (double)xi[cbase + n];
+            ss += rk * rk;
+        }
+        double denom = sqrt(ss);
+        if (denom < 1e-12) denom = 1e-12;
+        for (int64_t n = 0; n < N; ++n) {
+            const int64_t e = base + n;
+            const double lr = sigmoid64((double)lr_lora[e]);
+            const double kappa = (double)k[e] * (double)xi[cbase + n] / denom;
+            replacement_key[e] = (double)k[e] * ((double)alpha[cbase + n] * (lr - 1.0) + 1.0);
+            weight_decay[e] = -softplus64(-(double)d[e]) - 0.5;
+            removal_key_normalized[e] = -kappa;
+            replacement[e] = kappa * lr;
+            if (vp) value[e] = (double)vp[e] + ((double)vf[e] - (double)vp[e]) * sigmoid64((double)nu[e]);
+        }
+    }
+}
+
+/*
+ * GatedReadout::forward between the gate LoRA and the output projection
+ * (gated_readout.rs:123-141): GroupNorm with one group per head over the N
+ * channels of the head (mean, biased variance, eps inside the square root,
+ * per-channel gamma and beta), bonus = (sum_n r*k*rho[h,n]) * v, (norm + bonus) * gate.
+ */
+void oracle_gated_readout_f64(const float *y, const float *r, const float *k, const float *v,
+                              const float *gate, const float *gamma, const float *beta, const float *rho,
+                              double eps, double *out, int64_t rows, int64_t H, int64_t N) {
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < rows; ++row) {
+        const int64_t base = row * N, cbase = (row % H) * N;
+        double mean = 0.0, dot = 0.0;
+        for (int64_t n = 0; n < N; ++n) {
+            mean += (double)y[base + n];
+            dot += (double)r[base + n] * (double)k[base + n] * (double)rho[cbase + n];
+        }
+        mean /= (double)N;
+        double var = 0.0;
+        for (int64_t n = 0; n < N; ++n) {
+            const double dlt = (double)y[base + n] - mean;
+            var += dlt * dlt;
+        }
+        var /= (double)N;
+        const double rstd = 1.0 / sqrt(var + eps);
+        for (int64_t n = 0; n < N; ++n) {
+            const int64_t e = base + n;
+            const double nrm = ((double)y[e] - mean) * rstd * (double)gamma[cbase + n] + (double)beta[cbase + n];
+            out[e] = (nrm + dot * (double)v[e]) * (double)gate[e];
+        }
+    }
 }
 
 /* ------------------------------------------------------ token_shift_diff -- */

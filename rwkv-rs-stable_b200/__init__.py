@@ -466,6 +466,59 @@ token_shift_diff = token_shift_diff_custom
 # ---------------------------------------------------------------- lm_head_ce --
 
 
+@dataclass
+class WeightPrepareEpilogueOutput:
+    """The WKV7-ready fields of ``WeightPrepareOutput``
+    (``modules/time_mixer/weight_prepare.rs:289-297``) that the epilogue computes."""
+
+    weight_decay: torch.Tensor
+    replacement_key: torch.Tensor
+    value: Optional[torch.Tensor]
+    removal_key_normalized: torch.Tensor
+    replacement: torch.Tensor
+
+
+def weight_prepare_epilogue(key_precursor: torch.Tensor, learning_rate_lora: torch.Tensor,
+                            weight_decay_lora: torch.Tensor, key_removal: torch.Tensor,
+                            key_replacement: torch.Tensor, num_heads: int, *,
+                            value_precursor: Optional[torch.Tensor] = None,
+                            value_from_first_cell: Optional[torch.Tensor] = None,
+                            value_residual_lora: Optional[torch.Tensor] = None) -> WeightPrepareEpilogueOutput:
+    """The tail of ``WeightPrepare::forward`` (``weight_prepare.rs:252-287``) in one kernel.
+    ``learning_rate_lora``, ``weight_decay_lora`` and ``value_residual_lora`` are the LoRA
+    outputs *before* their sigmoid / softplus; the three value tensors are given for every
+    cell but the first (there ``value`` is ``value_precursor`` and is returned as is)."""
+    outs = [torch.empty_like(key_precursor) for _ in range(4)]
+    with_value = value_precursor is not None
+    value = torch.empty_like(key_precursor) if with_value else None
+    descs = [describe(t) for t in (key_precursor, learning_rate_lora, weight_decay_lora, key_removal,
+                                   key_replacement, value_precursor, value_from_first_cell,
+                                   value_residual_lora)]
+    od = [describe(t) for t in outs] + [describe(value)]
+    _check(lib().rwkv7_fused_weight_prepare(*[_ref(d) for d in descs], ctypes.c_int64(num_heads),
+                                            *[_ref(d) for d in od], _stream(key_precursor)))
+    return WeightPrepareEpilogueOutput(weight_decay=outs[0], replacement_key=outs[1],
+                                       value=value if with_value else None,
+                                       removal_key_normalized=outs[2], replacement=outs[3])
+
+
+def gated_readout_epilogue(wkv7_output: torch.Tensor, receptance: torch.Tensor, replacement_key: torch.Tensor,
+                           value: torch.Tensor, gate: torch.Tensor, group_norm_gamma: torch.Tensor,
+                           group_norm_beta: torch.Tensor, receptance_key_bonus: torch.Tensor,
+                           num_heads: int, epsilon: float = 64e-5) -> torch.Tensor:
+    """``GatedReadout::forward`` between the gate LoRA and the output projection
+    (``gated_readout.rs:123-141``): per-head GroupNorm of the WKV7 output, the
+    receptance-key bonus and the gate, in one kernel.  Returns ``[B,T,C]``-shaped
+    like ``wkv7_output``; ``gate`` is the LoRA output after its sigmoid."""
+    out = torch.empty_like(wkv7_output)
+    descs = [describe(t) for t in (wkv7_output, receptance, replacement_key, value, gate, group_norm_gamma,
+                                   group_norm_beta, receptance_key_bonus)]
+    od = describe(out)
+    _check(lib().rwkv7_fused_gated_readout(*[_ref(d) for d in descs], ctypes.c_double(epsilon),
+                                           ctypes.c_int64(num_heads), _ref(od), _stream(wkv7_output)))
+    return out
+
+
 def lm_head_ce_partial(x: torch.Tensor, weight_shard: torch.Tensor, targets: torch.Tensor,
                        vocab_offset: int = 0) -> torch.Tensor:
     """Per-row ``(max, sumexp, target logit)`` of ``x @ weight_shard.T`` over one

@@ -453,6 +453,142 @@ int rwkv7_fused_token_shift_diff(const rwkv7_tensor *x_t, rwkv7_tensor *state_t,
     return RWKV7_OK;
 }
 
+namespace {
+
+// A [B,T,C] or [B,T,H,N] tensor (the same memory): non-null, 3 or 4 axes, contiguous.
+int check_sequence_tensor(const TensorInfo &x) {
+    if (x.t == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: %s descriptor is null", x.name);
+    if (x.t->ndim != 3 && x.t->ndim != 4)
+        return fail(RWKV7_ERR_AXIS_MISMATCH, "AxisMismatch: %s has %d axes, expected [B,T,C] or [B,T,H,N]", x.name,
+                    x.t->ndim);
+    RWKV7_TRY(check_present(x, x.t->ndim));
+    return check_contiguous(x);
+}
+
+int64_t channels_of(const rwkv7_tensor *t) { return t->ndim == 4 ? t->shape[2] * t->shape[3] : t->shape[2]; }
+
+// Same batch, context length, channel count, dtype and device as `ref` (either axis form).
+int check_sequence_like(const TensorInfo &ref, const TensorInfo &x) {
+    RWKV7_TRY(check_sequence_tensor(x));
+    if (x.dim(0) != ref.dim(0) || x.dim(1) != ref.dim(1) || channels_of(x.t) != channels_of(ref.t))
+        return fail(RWKV7_ERR_SHAPE_MISMATCH, "ShapeMismatch: %s is %s, expected the extent of %s %s", x.name,
+                    shape_string(x.t->shape, x.t->ndim).c_str(), ref.name,
+                    shape_string(ref.t->shape, ref.t->ndim).c_str());
+    RWKV7_TRY(check_same_dtype({ref, x}));
+    return check_same_device({ref, x});
+}
+
+// A per-channel parameter: any contiguous shape with C elements.
+int check_channel_param(const TensorInfo &ref, const TensorInfo &x, int64_t C) {
+    if (x.t == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: %s descriptor is null", x.name);
+    RWKV7_TRY(check_present(x, x.t->ndim));
+    if (num_elements(x.t) != C)
+        return fail(RWKV7_ERR_SHAPE_MISMATCH, "ShapeMismatch: %s is %s, expected %lld elements", x.name,
+                    shape_string(x.t->shape, x.t->ndim).c_str(), (long long)C);
+    RWKV7_TRY(check_same_dtype({ref, x}));
+    RWKV7_TRY(check_same_device({ref, x}));
+    return check_contiguous(x);
+}
+
+int check_heads(int64_t C, int64_t num_heads, const rwkv7_tensor *ref) {
+    if (num_heads <= 0 || C % num_heads != 0)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: num_heads %lld does not divide %lld channels",
+                    (long long)num_heads, (long long)C);
+    if (ref->ndim == 4 && ref->shape[2] != num_heads)
+        return fail(RWKV7_ERR_SHAPE_MISMATCH, "ShapeMismatch: tensor has %lld heads, num_heads is %lld",
+                    (long long)ref->shape[2], (long long)num_heads);
+    return RWKV7_OK;
+}
+
+}  // namespace
+
+int rwkv7_fused_weight_prepare(const rwkv7_tensor *k_t, const rwkv7_tensor *lr_t, const rwkv7_tensor *wd_t,
+                               const rwkv7_tensor *xi_t, const rwkv7_tensor *alpha_t,
+                               const rwkv7_tensor *vp_t, const rwkv7_tensor *vf_t, const rwkv7_tensor *nu_t,
+                               int64_t num_heads, rwkv7_tensor *w_t, rwkv7_tensor *kt_t, rwkv7_tensor *a_t,
+                               rwkv7_tensor *b_t, rwkv7_tensor *v_t, rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo k{"key_precursor", k_t};
+    RWKV7_TRY(check_sequence_tensor(k));
+    RWKV7_TRY(check_axis_non_empty(k, 2));
+    const int64_t C = channels_of(k_t);
+    RWKV7_TRY(check_heads(C, num_heads, k_t));
+    RWKV7_TRY(check_sequence_like(k, TensorInfo{"learning_rate_lora", lr_t}));
+    RWKV7_TRY(check_sequence_like(k, TensorInfo{"weight_decay_lora", wd_t}));
+    RWKV7_TRY(check_channel_param(k, TensorInfo{"key_removal", xi_t}, C));
+    RWKV7_TRY(check_channel_param(k, TensorInfo{"key_replacement", alpha_t}, C));
+    const int n_value = (vp_t != nullptr) + (vf_t != nullptr) + (nu_t != nullptr) + (v_t != nullptr);
+    if (n_value != 0 && n_value != 4)
+        return fail(RWKV7_ERR_NULL_POINTER,
+                    "NullPointer: value_precursor, value_from_first_cell, value_residual_lora and value "
+                    "must be all given or all null");
+    if (n_value == 4) {
+        RWKV7_TRY(check_sequence_like(k, TensorInfo{"value_precursor", vp_t}));
+        RWKV7_TRY(check_sequence_like(k, TensorInfo{"value_from_first_cell", vf_t}));
+        RWKV7_TRY(check_sequence_like(k, TensorInfo{"value_residual_lora", nu_t}));
+        RWKV7_TRY(check_sequence_like(k, TensorInfo{"value", v_t}));
+    }
+    if (!float_dtype_supported(k_t->dtype))
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: weight_prepare computes F32 or BF16, got %s", dtype_name(k_t->dtype));
+    RWKV7_TRY(check_sequence_like(k, TensorInfo{"weight_decay", w_t}));
+    RWKV7_TRY(check_sequence_like(k, TensorInfo{"replacement_key", kt_t}));
+    RWKV7_TRY(check_sequence_like(k, TensorInfo{"removal_key_normalized", a_t}));
+    RWKV7_TRY(check_sequence_like(k, TensorInfo{"replacement", b_t}));
+    WeightPrepareArgs p{};
+    p.key_precursor = k_t->data; p.learning_rate_lora = lr_t->data; p.weight_decay_lora = wd_t->data;
+    p.key_removal = xi_t->data; p.key_replacement = alpha_t->data;
+    if (n_value == 4) {
+        p.value_precursor = vp_t->data; p.value_from_first_cell = vf_t->data; p.value_residual_lora = nu_t->data;
+        p.value = v_t->data;
+    }
+    p.weight_decay = w_t->data; p.replacement_key = kt_t->data; p.removal_key_normalized = a_t->data;
+    p.replacement = b_t->data;
+    p.H = num_heads; p.N = C / num_heads; p.rows = k.dim(0) * k.dim(1) * num_heads;
+    p.bf16 = k_t->dtype == RWKV7_BF16;
+    if (p.rows == 0) return RWKV7_OK;
+    DeviceGuard guard(k_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(k_t->device, &p.num_sms));
+    if (int e = launch_weight_prepare(p, (cudaStream_t)stream)) return cuda_fail("weight_prepare launch", e);
+    return RWKV7_OK;
+}
+
+int rwkv7_fused_gated_readout(const rwkv7_tensor *y_t, const rwkv7_tensor *r_t, const rwkv7_tensor *kt_t,
+                              const rwkv7_tensor *v_t, const rwkv7_tensor *gate_t, const rwkv7_tensor *gamma_t,
+                              const rwkv7_tensor *beta_t, const rwkv7_tensor *bonus_t, double epsilon,
+                              int64_t num_heads, rwkv7_tensor *out_t, rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo y{"wkv7_output", y_t};
+    RWKV7_TRY(check_sequence_tensor(y));
+    RWKV7_TRY(check_axis_non_empty(y, 2));
+    const int64_t C = channels_of(y_t);
+    RWKV7_TRY(check_heads(C, num_heads, y_t));
+    RWKV7_TRY(check_sequence_like(y, TensorInfo{"receptance", r_t}));
+    RWKV7_TRY(check_sequence_like(y, TensorInfo{"replacement_key", kt_t}));
+    RWKV7_TRY(check_sequence_like(y, TensorInfo{"value", v_t}));
+    RWKV7_TRY(check_sequence_like(y, TensorInfo{"gate", gate_t}));
+    RWKV7_TRY(check_channel_param(y, TensorInfo{"group_norm_gamma", gamma_t}, C));
+    RWKV7_TRY(check_channel_param(y, TensorInfo{"group_norm_beta", beta_t}, C));
+    RWKV7_TRY(check_channel_param(y, TensorInfo{"receptance_key_bonus", bonus_t}, C));
+    if (!(epsilon >= 0.0))
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: epsilon must be non-negative, got %g", epsilon);
+    if (!float_dtype_supported(y_t->dtype))
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: gated_readout computes F32 or BF16, got %s", dtype_name(y_t->dtype));
+    RWKV7_TRY(check_sequence_like(y, TensorInfo{"output", out_t}));
+    GatedReadoutArgs p{};
+    p.wkv7_output = y_t->data; p.receptance = r_t->data; p.replacement_key = kt_t->data; p.value = v_t->data;
+    p.gate = gate_t->data; p.gamma = gamma_t->data; p.beta = beta_t->data; p.bonus = bonus_t->data;
+    p.output = out_t->data; p.epsilon = (float)epsilon;
+    p.H = num_heads; p.N = C / num_heads; p.rows = y.dim(0) * y.dim(1) * num_heads;
+    p.bf16 = y_t->dtype == RWKV7_BF16;
+    if (p.rows == 0) return RWKV7_OK;
+    DeviceGuard guard(y_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(y_t->device, &p.num_sms));
+    if (int e = launch_gated_readout(p, (cudaStream_t)stream)) return cuda_fail("gated_readout launch", e);
+    return RWKV7_OK;
+}
+
 size_t rwkv7_lm_head_ce_workspace_bytes(int64_t R, int64_t C, int64_t V_shard) {
     return lm_head_ce_workspace_bytes(R, C, V_shard);
 }

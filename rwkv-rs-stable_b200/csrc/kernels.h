@@ -68,6 +68,31 @@ struct AddcmulArgs {
 };
 int launch_addcmul(const AddcmulArgs &p, cudaStream_t stream);
 
+// Tail of WeightPrepare::forward: rows = B*T*H head rows of N elements; parameters are [H*N].
+struct WeightPrepareArgs {
+    const void *key_precursor, *learning_rate_lora, *weight_decay_lora;   // [rows,N]
+    const void *key_removal, *key_replacement;                             // [H*N]
+    const void *value_precursor, *value_from_first_cell, *value_residual_lora;   // [rows,N] or all null
+    void *weight_decay, *replacement_key, *removal_key_normalized, *replacement;  // [rows,N]
+    void *value;                                                           // [rows,N] or null
+    int64_t rows, H, N;
+    bool bf16;
+    int num_sms;
+};
+int launch_weight_prepare(const WeightPrepareArgs &p, cudaStream_t stream);
+
+// Body of GatedReadout::forward between the gate LoRA and the output projection.
+struct GatedReadoutArgs {
+    const void *wkv7_output, *receptance, *replacement_key, *value, *gate;   // [rows,N]
+    const void *gamma, *beta, *bonus;                                        // [H*N]
+    void *output;                                                            // [rows,N]
+    float epsilon;
+    int64_t rows, H, N;
+    bool bf16;
+    int num_sms;
+};
+int launch_gated_readout(const GatedReadoutArgs &p, cudaStream_t stream);
+
 struct TokenShiftArgs {
     const void *x;     // [B,T,C]
     void *state;       // [S,C], updated in place

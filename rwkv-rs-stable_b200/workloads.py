@@ -77,3 +77,30 @@ def lm_head_inputs(R: int, C: int, V: int, *, seed: int = 0, device="cpu"):
     w = (torch.randn((V, C), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
     tg = torch.randint(0, V, (R,), generator=g, device=device, dtype=torch.int64)
     return x, w, tg
+
+
+def time_mixer_epilogue_inputs(B: int, T: int, H: int, N: int, *, seed: int = 0, dtype=torch.float32,
+                               device="cpu"):
+    """Inputs of the two time-mixer epilogues at model-like scales: projections and LoRA
+    outputs ``N(0,1)``, ``key_removal`` / ``key_replacement`` around their initial values 0.71 /
+    1.02 (``weight_prepare.rs:200-201``), GroupNorm gamma around 1, beta and the
+    receptance-key bonus small, gate in (0,1)."""
+    g = _gen(device, 15485863 + seed)
+    C = H * N
+
+    def big(scale=1.0):
+        return (torch.randn((B, T, C), generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+
+    def chan(mean, spread):
+        return (mean + spread * torch.randn((1, 1, C), generator=g, device=device, dtype=torch.float32)).to(dtype)
+
+    out = {name: big() for name in ("key_precursor", "learning_rate_lora", "weight_decay_lora",
+                                    "value_precursor", "value_from_first_cell", "value_residual_lora",
+                                    "wkv7_output", "receptance", "replacement_key", "value")}
+    out["gate"] = torch.sigmoid(big().float()).to(dtype)
+    out["key_removal"] = chan(0.71, 0.1)
+    out["key_replacement"] = chan(1.02, 0.1)
+    out["group_norm_gamma"] = chan(1.0, 0.2).reshape(C)
+    out["group_norm_beta"] = chan(0.0, 0.1).reshape(C)
+    out["receptance_key_bonus"] = chan(0.0, 0.1).reshape(H, N)
+    return out

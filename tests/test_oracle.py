@@ -137,3 +137,48 @@ def test_oracle_lm_head_ce(oracle, workloads):
     ce = torch.nn.functional.cross_entropy(z, tg.clamp_min(0), reduction="none")
     ce[3] = 0
     np.testing.assert_allclose(loss, ce.numpy(), rtol=1e-10, atol=1e-12)
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 3, 64), (1, 4, 2, 20), (3, 2, 1, 7)])
+def test_time_mixer_epilogues_match_torch_restatement(oracle, workloads, shape):
+    """The C restatements of the WeightPrepare tail and of GatedReadout against independent
+    torch fp64 versions written with the reference's tensor ops (torch's own softplus,
+    GroupNorm and clamp_min)."""
+    import torch_restatement as tr
+    B, T, H, N = shape
+    inp = workloads.time_mixer_epilogue_inputs(B, T, H, N, seed=4)
+    d = {k: v.double() for k, v in inp.items()}
+    ref = tr.weight_prepare_reference(d["key_precursor"], d["learning_rate_lora"], d["weight_decay_lora"],
+                                      d["key_removal"], d["key_replacement"], H, d["value_precursor"],
+                                      d["value_from_first_cell"], d["value_residual_lora"])
+    got = oracle.weight_prepare(inp["key_precursor"].numpy(), inp["learning_rate_lora"].numpy(),
+                                inp["weight_decay_lora"].numpy(), inp["key_removal"].numpy(),
+                                inp["key_replacement"].numpy(), H, inp["value_precursor"].numpy(),
+                                inp["value_from_first_cell"].numpy(), inp["value_residual_lora"].numpy())
+    for name, r in ref.items():
+        np.testing.assert_allclose(got[name], r.numpy(), rtol=1e-12, atol=1e-12, err_msg=name)
+    first = oracle.weight_prepare(inp["key_precursor"].numpy(), inp["learning_rate_lora"].numpy(),
+                                  inp["weight_decay_lora"].numpy(), inp["key_removal"].numpy(),
+                                  inp["key_replacement"].numpy(), H)
+    assert first["value"] is None and np.array_equal(first["replacement"], got["replacement"])
+    # known answers: unit norm per head, b = -a * lr, decay precursor below -0.5
+    a = got["removal_key_normalized"].reshape(B, T, H, N)
+    np.testing.assert_allclose((a * a).sum(-1), 1.0, rtol=1e-12)
+    assert (got["weight_decay"] < -0.5).all()
+
+    ref = tr.gated_readout_reference(d["wkv7_output"], d["receptance"], d["replacement_key"], d["value"],
+                                     d["gate"], d["group_norm_gamma"], d["group_norm_beta"],
+                                     d["receptance_key_bonus"], H)
+    got = oracle.gated_readout(*[inp[n].numpy() for n in ("wkv7_output", "receptance", "replacement_key", "value",
+                                                          "gate", "group_norm_gamma", "group_norm_beta",
+                                                          "receptance_key_bonus")], H)
+    np.testing.assert_allclose(got, ref.numpy(), rtol=1e-11, atol=1e-11)
+
+
+def test_weight_prepare_zero_key_uses_the_epsilon(oracle):
+    """normalize.rs:38-40 clamps the norm at 1e-12: an all-zero head gives zeros, not NaN."""
+    z = np.zeros((1, 1, 8), dtype=np.float32)
+    one = np.ones((1, 1, 8), dtype=np.float32)
+    got = oracle.weight_prepare(z, z, z, one, one, 2)
+    assert np.array_equal(got["removal_key_normalized"], np.zeros_like(z, dtype=np.float64))
+    np.testing.assert_allclose(got["weight_decay"], -np.log(2.0) - 0.5)

@@ -56,3 +56,37 @@ def token_shift_diff_reference(x, state, ids):
     selected = torch.zeros(state.shape[0], dtype=state.dtype).index_add(0, ids, torch.ones(B, dtype=state.dtype))
     nxt = (state * (1 - selected).unsqueeze(1)).index_add(0, ids, last)
     return diff, nxt
+
+
+def weight_prepare_reference(key_precursor, learning_rate_lora, weight_decay_lora, key_removal, key_replacement,
+                             num_heads, value_precursor=None, value_from_first_cell=None,
+                             value_residual_lora=None):
+    """``WeightPrepare::forward`` after the projections (``weight_prepare.rs:252-287``), with torch
+    tensor ops in the order the reference applies them."""
+    B, T, C = key_precursor.shape
+    learning_rate = torch.sigmoid(learning_rate_lora)
+    alpha_modulated = key_replacement * (learning_rate - 1.0) + 1.0
+    replacement_key = key_precursor * alpha_modulated
+    weight_decay = -torch.nn.functional.softplus(-weight_decay_lora, beta=1.0, threshold=1e9) - 0.5
+    removal_key = (key_precursor * key_removal).reshape(B, T, num_heads, C // num_heads)
+    norm = removal_key.abs().pow(2.0).sum(-1, keepdim=True).pow(0.5).clamp_min(1e-12)
+    removal_key_normalized = -(removal_key / norm).reshape(B, T, C)
+    replacement = -removal_key_normalized * learning_rate
+    value = None
+    if value_precursor is not None:
+        nu = torch.sigmoid(value_residual_lora)
+        value = value_precursor + (value_from_first_cell - value_precursor) * nu
+    return dict(weight_decay=weight_decay, replacement_key=replacement_key,
+                removal_key_normalized=removal_key_normalized, replacement=replacement, value=value)
+
+
+def gated_readout_reference(wkv7_output, receptance, replacement_key, value, gate, gamma, beta, bonus,
+                            num_heads, epsilon=64e-5):
+    """``GatedReadout::forward`` (``gated_readout.rs:123-141``) with torch's own GroupNorm."""
+    B, T, C = wkv7_output.shape
+    N = C // num_heads
+    norm = torch.nn.functional.group_norm(wkv7_output.reshape(B * T, C), num_heads, gamma.reshape(C),
+                                          beta.reshape(C), epsilon).reshape(B, T, C)
+    r4, k4, v4 = (t.reshape(B, T, num_heads, N) for t in (receptance, replacement_key, value))
+    bonus4 = (r4 * k4 * bonus.reshape(1, 1, num_heads, N)).sum(3, keepdim=True) * v4
+    return (norm + bonus4.reshape(B, T, C)) * gate
