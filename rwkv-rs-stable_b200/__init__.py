@@ -486,7 +486,7 @@ def weight_prepare_epilogue(key_precursor: torch.Tensor, learning_rate_lora: tor
                             value_residual_lora: Optional[torch.Tensor] = None) -> WeightPrepareEpilogueOutput:
     """The tail of ``WeightPrepare::forward`` (``weight_prepare.rs:252-287``) in one kernel.
     ``learning_rate_lora``, ``weight_decay_lora`` and ``value_residual_lora`` are the LoRA
-    outputs *before* their sigmoid / softplus; the three value tensors are given for every
+    modules' outputs, before the sigmoid / softplus that ``forward`` applies to them; the three value tensors are given for every
     cell but the first (there ``value`` is ``value_precursor`` and is returned as is)."""
     outs = [torch.empty_like(key_precursor) for _ in range(4)]
     with_value = value_precursor is not None
@@ -509,7 +509,7 @@ def gated_readout_epilogue(wkv7_output: torch.Tensor, receptance: torch.Tensor, 
     """``GatedReadout::forward`` between the gate LoRA and the output projection
     (``gated_readout.rs:123-141``): per-head GroupNorm of the WKV7 output, the
     receptance-key bonus and the gate, in one kernel.  Returns ``[B,T,C]``-shaped
-    like ``wkv7_output``; ``gate`` is the LoRA output after its sigmoid."""
+    like ``wkv7_output``; ``gate`` is the gate LoRA's output as it is (``gated_readout.rs:121``)."""
     out = torch.empty_like(wkv7_output)
     descs = [describe(t) for t in (wkv7_output, receptance, replacement_key, value, gate, group_norm_gamma,
                                    group_norm_beta, receptance_key_bonus)]
