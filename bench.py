@@ -52,7 +52,7 @@ def bench_config(B, T, H, N, path="auto"):
 # DRAM bytes of one prefill launch from the ncu capture of the B=4 case (151.9 MB read +
 # 15.2 MB written; y still partly in L2 at kernel end), scaled x2 to B=8: traffic is
 # proportional to the number of chains.  See profiles/wkv7_chunked_prefill_cfg1.md.
-NCU_TRAFFIC_BYTES_CFG1 = 2 * (151.9e6 + 15.2e6)
+NCU_TRAFFIC_BYTES_CFG1 = 337.2e6   # ncu dram read+write of the B=4 capture (151.9 + 16.7 MB), scaled to B=8
 
 
 def measured_peaks():
@@ -194,6 +194,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-streaming", action="store_true")
+    ap.add_argument("--no-channel-mixer", action="store_true")
     ap.add_argument("--no-lm-head", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
@@ -394,6 +395,38 @@ def main():
                    "mean_loss": float(loss.mean().item())}
         del xl, wl, tl
 
+    # ---- channel mixer at the configuration-2 layer shape (two tensor-core projections) ---
+    channel_mixer = None
+    if not args.no_channel_mixer and rank == 0:
+        Bc, Tc, Cc, Fc = (2, 4096, 2048, 8192) if args.small else (16, 8192, 2048, 8192)
+        cx, cks, ckw, cvw = workloads.channel_mixer_inputs(Bc, Tc, Cc, Fc, seed=7, device=dev)
+        cws = torch.empty(int(pkg.lib().rwkv7_channel_mixer_workspace_bytes(Bc, Tc, Cc, Fc)) or 1,
+                          dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            pkg.channel_mixer_custom(cx, cks, ckw, cvw, workspace=cws)
+        torch.cuda.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_cm = 5
+        c0.record()
+        for _ in range(n_cm):
+            cout = pkg.channel_mixer_custom(cx, cks, ckw, cvw, workspace=cws)
+        c1.record()
+        torch.cuda.synchronize()
+        cms = c0.elapsed_time(c1) / n_cm
+        cflops = 4.0 * Bc * Tc * Cc * Fc
+        tf_peak_cm = 1653.6
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tf_peak_cm = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            pass
+        channel_mixer = {"workload": f"B={Bc} T={Tc} C={Cc} F={Fc} bf16: token-shift mix, key projection with relu^2 "
+                                     "epilogue, value projection",
+                         "ms": cms, "tflops": cflops / (cms * 1e-3) / 1e12, "peak_tflops": tf_peak_cm,
+                         "frac_of_bf16_peak": cflops / (cms * 1e-3) / 1e12 / tf_peak_cm,
+                         "output_abs_mean": float(cout.float().abs().mean().item())}
+        del cx, ckw, cvw, cws, cout
+
     if world > 1:
         dist.barrier()
     if rank != 0:
@@ -423,6 +456,7 @@ def main():
         "decode": decode,
         "streaming": streaming,
         "lm_head_ce": lm_head,
+        "channel_mixer": channel_mixer,
     }
     if not args.no_cpu_baseline:
         oracle = entry.load_oracle()

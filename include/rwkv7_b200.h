@@ -280,6 +280,26 @@ int rwkv7_fused_gated_readout(const rwkv7_tensor *wkv7_output, const rwkv7_tenso
                               const rwkv7_tensor *receptance_key_bonus, double epsilon,
                               int64_t num_heads, rwkv7_tensor *output, rwkv7_stream stream);
 
+/* --------------------------------------------------------- channel mixer -- */
+/*
+ * Replaces ChannelMixerBackend::fused_channel_mixer (kernels/train/channel_mixer/mod.rs,
+ * host forward.rs:52-88, definition channel_mixer_reference mod.rs:96-128):
+ *   shifted[b,t,:] = x[b,t-1,:] (zero at t == 0); key_input = x + (shifted - x) * key_scale;
+ *   output = relu(key_input . key_weight^T)^2 . value_weight^T.
+ * embedded_context and output [B,T,C], key_scale [C], key_weight [F,C], value_weight [C,F];
+ * checks in the order of ChannelMixerForwardInputs::check (channel_mixer/io.rs:40-62).
+ * Both projections run on the tensor cores in BF16 with fp32 accumulation; the
+ * activation is part of the first projection's epilogue.  BF16 tensors only (F32 returns
+ * RWKV7_ERR_UNSUPPORTED); C and F must be multiples of 8.  The workspace holds key_input
+ * and the activated hidden tensor: rwkv7_channel_mixer_workspace_bytes(B, T, C, F).
+ */
+size_t rwkv7_channel_mixer_workspace_bytes(int64_t B, int64_t T, int64_t C, int64_t F);
+
+int rwkv7_fused_channel_mixer(const rwkv7_tensor *embedded_context, const rwkv7_tensor *key_scale,
+                              const rwkv7_tensor *key_weight, const rwkv7_tensor *value_weight,
+                              rwkv7_tensor *output, void *workspace, size_t workspace_bytes,
+                              rwkv7_stream stream);
+
 /* ------------------------------------------------------------ lm_head_ce -- */
 /*
  * Fused LM-head cross entropy.  The reference only reserves the module

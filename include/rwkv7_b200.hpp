@@ -210,6 +210,23 @@ inline void gated_readout_epilogue(const GatedReadoutEpilogueInputs &in, TensorV
         output.m(), stream));
 }
 
+// ChannelMixerForwardInputs (kernels/train/channel_mixer/io.rs:17-22) and channel_mixer_custom
+// (mod.rs:80-94).
+struct ChannelMixerForwardInputs {
+    TensorView embedded_context, key_scale, key_weight, value_weight;
+};
+inline size_t channel_mixer_workspace_bytes(const ChannelMixerForwardInputs &in) {
+    const rwkv7_tensor &x = in.embedded_context.t;
+    return x.ndim == 3 && in.key_weight.t.ndim == 2
+               ? rwkv7_channel_mixer_workspace_bytes(x.shape[0], x.shape[1], x.shape[2], in.key_weight.t.shape[0])
+               : 0;
+}
+inline void channel_mixer_custom(const ChannelMixerForwardInputs &in, TensorView &output, Workspace ws,
+                                 rwkv7_stream stream = nullptr) {
+    check_status(rwkv7_fused_channel_mixer(in.embedded_context.c(), in.key_scale.c(), in.key_weight.c(),
+                                           in.value_weight.c(), output.m(), ws.data, ws.bytes, stream));
+}
+
 }  // namespace rwkv7b200
 
 #endif  // RWKV7_B200_HPP_

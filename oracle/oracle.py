@@ -141,6 +141,18 @@ def gated_readout(wkv7_output, receptance, replacement_key, value, gate, gamma, 
     return out
 
 
+def channel_mixer(x, key_scale, key_weight, value_weight):
+    """``channel_mixer_reference``; ``x`` ``[B,T,C]``, ``key_weight`` ``[F,C]``, ``value_weight`` ``[C,F]``; float64."""
+    x = _f32(x)
+    B, T, C = x.shape
+    kw, vw = _f32(key_weight), _f32(value_weight)
+    F = kw.shape[0]
+    out = np.empty((B, T, C), dtype=np.float64)
+    lib().oracle_channel_mixer_f64(_p(x), _p(_f32(key_scale).reshape(C)), _p(kw), _p(vw), _p(out),
+                                   ctypes.c_int64(B), ctypes.c_int64(T), ctypes.c_int64(C), ctypes.c_int64(F))
+    return out
+
+
 def token_shift_diff(x, state, ids):
     """Returns ``(diff, next_state)``; ``state`` is not modified."""
     x = _f32(x)

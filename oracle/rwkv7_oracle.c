@@ -30,6 +30,8 @@
  *   gated_readout  crates/rwkv-nn/src/modules/time_mixer/gated_readout.rs:110-145
  *             (GroupNorm itself lives in Burn, which is not part of the reference
  *             tree: the published definition is restated, biased variance)
+ *   channel_mixer  crates/rwkv-nn/src/kernels/train/channel_mixer/mod.rs:96-128
+ *             (channel_mixer_reference)
  *   lm_head_ce  no reference implementation exists (lm_head_l2wrap_ce/mod.rs is
  *             empty); the specification is z = x W^T, lse = log sum exp z,
  *             loss = lse - z[target].
@@ -265,6 +267,46 @@ void oracle_gated_readout_f64(const float *y, const float *r, const float *k, co
             const double nrm = ((double)y[e] - mean) * rstd * (double)gamma[cbase + n] + (double)beta[cbase + n];
             out[e] = (nrm + dot * (double)v[e]) * (double)gate[e];
         }
+    }
+}
+
+/* --------------------------------------------------------- channel mixer -- */
+
+/*
+ * channel_mixer_reference (channel_mixer/mod.rs:96-128): shifted = previous token
+ * (zero at t == 0); key_input = x + (shifted - x) * key_scale[c];
+ * hidden = relu(key_input . key_weight^T)^2 with key_weight [F][C];
+ * out = hidden . value_weight^T with value_weight [C][F].  Double throughout.
+ */
+void oracle_channel_mixer_f64(const float *x, const float *key_scale, const float *key_weight,
+                              const float *value_weight, double *out, int64_t B, int64_t T, int64_t C,
+                              int64_t F) {
+#pragma omp parallel
+    {
+        double *ki = (double *)malloc(sizeof(double) * (size_t)C);
+        double *hid = (double *)malloc(sizeof(double) * (size_t)F);
+#pragma omp for schedule(static)
+        for (int64_t row = 0; row < B * T; ++row) {
+            const int64_t t = row % T;
+            for (int64_t c = 0; c < C; ++c) {
+                const double cur = (double)x[row * C + c];
+                const double prev = (t == 0) ? 0.0 : (double)x[(row - 1) * C + c];
+                ki[c] = cur + (prev - cur) * (double)key_scale[c];
+            }
+            for (int64_t f = 0; f < F; ++f) {
+                double acc = 0.0;
+                for (int64_t c = 0; c < C; ++c) acc += ki[c] * (double)key_weight[f * C + c];
+                acc = acc > 0.0 ? acc : 0.0;
+                hid[f] = acc * acc;
+            }
+            for (int64_t c = 0; c < C; ++c) {
+                double acc = 0.0;
+                for (int64_t f = 0; f < F; ++f) acc += hid[f] * (double)value_weight[c * F + f];
+                out[row * C + c] = acc;
+            }
+        }
+        free(ki);
+        free(hid);
     }
 }
 

@@ -86,6 +86,8 @@ def lib() -> ctypes.CDLL:
         L.rwkv7_kernel_launch_count.restype = ctypes.c_int64
         L.rwkv7_lm_head_ce_workspace_bytes.restype = ctypes.c_size_t
         L.rwkv7_lm_head_ce_workspace_bytes.argtypes = [ctypes.c_int64] * 3
+        L.rwkv7_channel_mixer_workspace_bytes.restype = ctypes.c_size_t
+        L.rwkv7_channel_mixer_workspace_bytes.argtypes = [ctypes.c_int64] * 4
         _lib = L
     return _lib
 
@@ -517,6 +519,29 @@ def gated_readout_epilogue(wkv7_output: torch.Tensor, receptance: torch.Tensor, 
     _check(lib().rwkv7_fused_gated_readout(*[_ref(d) for d in descs], ctypes.c_double(epsilon),
                                            ctypes.c_int64(num_heads), _ref(od), _stream(wkv7_output)))
     return out
+
+
+def channel_mixer_custom(embedded_context: torch.Tensor, key_scale: torch.Tensor, key_weight: torch.Tensor,
+                         value_weight: torch.Tensor, *, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``channel_mixer`` (``kernels/train/channel_mixer/mod.rs:130-144``): token-shift mix, key
+    projection with relu^2 in its epilogue, value projection; bf16 tensors."""
+    out = torch.empty_like(embedded_context)
+    ws_ptr, ws_bytes = ctypes.c_void_p(0), 0
+    if embedded_context.dim() == 3 and key_weight.dim() == 2:
+        B, T, C = embedded_context.shape
+        ws_bytes = int(lib().rwkv7_channel_mixer_workspace_bytes(B, T, C, key_weight.shape[0]))
+        if workspace is None and ws_bytes:
+            workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=embedded_context.device)
+        if workspace is not None:
+            ws_ptr, ws_bytes = ctypes.c_void_p(workspace.data_ptr()), workspace.numel() * workspace.element_size()
+    descs = [describe(t) for t in (embedded_context, key_scale, key_weight, value_weight)]
+    od = describe(out)
+    _check(lib().rwkv7_fused_channel_mixer(*[_ref(d) for d in descs], _ref(od), ws_ptr, ctypes.c_size_t(ws_bytes),
+                                           _stream(embedded_context)))
+    return out
+
+
+channel_mixer = channel_mixer_custom
 
 
 def lm_head_ce_partial(x: torch.Tensor, weight_shard: torch.Tensor, targets: torch.Tensor,

@@ -589,6 +589,62 @@ int rwkv7_fused_gated_readout(const rwkv7_tensor *y_t, const rwkv7_tensor *r_t, 
     return RWKV7_OK;
 }
 
+size_t rwkv7_channel_mixer_workspace_bytes(int64_t B, int64_t T, int64_t C, int64_t F) {
+    if (B <= 0 || T <= 0) return 0;
+    return channel_mixer_workspace_bytes(B * T, C, F);
+}
+
+int rwkv7_fused_channel_mixer(const rwkv7_tensor *x_t, const rwkv7_tensor *scale_t, const rwkv7_tensor *kw_t,
+                              const rwkv7_tensor *vw_t, rwkv7_tensor *out_t, void *workspace,
+                              size_t workspace_bytes, rwkv7_stream stream) {
+    clear_error();
+    const TensorInfo x{"embedded_context", x_t}, scale{"key_scale", scale_t}, kw{"key_weight", kw_t},
+        vw{"value_weight", vw_t};
+    RWKV7_TRY(check_present(x, 3));
+    RWKV7_TRY(check_present(scale, 1));
+    RWKV7_TRY(check_present(kw, 2));
+    RWKV7_TRY(check_present(vw, 2));
+    // ChannelMixerForwardInputs::check (channel_mixer/io.rs:40-62)
+    RWKV7_TRY(check_axis_non_empty(x, 2));
+    RWKV7_TRY(check_axis_non_empty(kw, 0));
+    RWKV7_TRY(check_shape(scale, {x.dim(2)}));
+    RWKV7_TRY(check_axes_equal({{x, 2}, {kw, 1}, {vw, 0}}));
+    RWKV7_TRY(check_axes_equal({{kw, 0}, {vw, 1}}));
+    RWKV7_TRY(check_shape(vw, {x.dim(2), kw.dim(0)}));
+    RWKV7_TRY(check_same_dtype({x, scale, kw, vw}));
+    RWKV7_TRY(check_same_device({x, scale, kw, vw}));
+    RWKV7_TRY(check_contiguous(x));
+    RWKV7_TRY(check_contiguous(scale));
+    RWKV7_TRY(check_contiguous(kw));
+    RWKV7_TRY(check_contiguous(vw));
+    if (x_t->dtype != RWKV7_BF16)
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: channel_mixer computes BF16 tensors, got %s", dtype_name(x_t->dtype));
+    RWKV7_TRY(check_output_like(x, TensorInfo{"output", out_t}));
+    ChannelMixerArgs p{};
+    p.x = x_t->data; p.key_scale = scale_t->data; p.key_weight = kw_t->data; p.value_weight = vw_t->data;
+    p.out = out_t->data;
+    p.B = x.dim(0); p.T = x.dim(1); p.C = x.dim(2); p.F = kw.dim(0);
+    if (p.C % 8 != 0 || p.F % 8 != 0)
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: channel_mixer needs C and F to be multiples of 8, got %lld and %lld",
+                    (long long)p.C, (long long)p.F);
+    if (p.B == 0 || p.T == 0) return RWKV7_OK;   // channel_mixer/mod.rs:102-104: an empty context gives an empty output
+    for (const void *ptr : {p.x, p.key_scale, p.key_weight, p.value_weight, (const void *)p.out, (const void *)workspace})
+        if (reinterpret_cast<uintptr_t>(ptr) & 15u)
+            return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: channel_mixer tensors and workspace must be 16-byte aligned");
+    const size_t need = channel_mixer_workspace_bytes(p.B * p.T, p.C, p.F);
+    if (workspace == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: channel_mixer needs a workspace of %zu bytes", need);
+    if (workspace_bytes < need)
+        return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: channel_mixer needs %zu workspace bytes, got %zu", need,
+                    workspace_bytes);
+    DeviceGuard guard(x_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(x_t->device, &p.num_sms));
+    if (int e = device_status_ptr(x_t->device, &p.status)) return cuda_fail("device status word", e);
+    if (int e = launch_channel_mixer(p, workspace, workspace_bytes, (cudaStream_t)stream))
+        return cuda_fail("channel_mixer launch", e);
+    return RWKV7_OK;
+}
+
 size_t rwkv7_lm_head_ce_workspace_bytes(int64_t R, int64_t C, int64_t V_shard) {
     return lm_head_ce_workspace_bytes(R, C, V_shard);
 }

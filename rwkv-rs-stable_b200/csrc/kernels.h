@@ -93,6 +93,17 @@ struct GatedReadoutArgs {
 };
 int launch_gated_readout(const GatedReadoutArgs &p, cudaStream_t stream);
 
+// Channel mixer: x [B,T,C] bf16, key_scale [C], key_weight [F,C], value_weight [C,F], out [B,T,C].
+struct ChannelMixerArgs {
+    const void *x, *key_scale, *key_weight, *value_weight;
+    void *out;
+    int64_t B, T, C, F;
+    int *status;   // device status word
+    int num_sms;
+};
+size_t channel_mixer_workspace_bytes(int64_t rows, int64_t C, int64_t F);
+int launch_channel_mixer(const ChannelMixerArgs &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+
 struct TokenShiftArgs {
     const void *x;     // [B,T,C]
     void *state;       // [S,C], updated in place

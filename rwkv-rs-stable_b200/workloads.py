@@ -104,3 +104,14 @@ def time_mixer_epilogue_inputs(B: int, T: int, H: int, N: int, *, seed: int = 0,
     out["group_norm_beta"] = chan(0.0, 0.1).reshape(C)
     out["receptance_key_bonus"] = chan(0.0, 0.1).reshape(H, N)
     return out
+
+
+def channel_mixer_inputs(B: int, T: int, C: int, F: int, *, seed: int = 0, dtype=torch.bfloat16, device="cpu"):
+    """``x ~ N(0,1)``, ``key_scale ~ U[0,1)``, weights ``N(0, 1/sqrt(fan_in))`` so that the hidden
+    activation and the output stay O(1)."""
+    g = _gen(device, 32452843 + seed)
+    x = torch.randn((B, T, C), generator=g, device=device, dtype=torch.float32).to(dtype)
+    key_scale = torch.rand((C,), generator=g, device=device, dtype=torch.float32).to(dtype)
+    key_weight = (torch.randn((F, C), generator=g, device=device, dtype=torch.float32) / C ** 0.5).to(dtype)
+    value_weight = (torch.randn((C, F), generator=g, device=device, dtype=torch.float32) / F ** 0.5).to(dtype)
+    return x, key_scale, key_weight, value_weight

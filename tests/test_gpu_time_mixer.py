@@ -109,3 +109,49 @@ def test_epilogue_contracts(pkg, workloads, cuda):
     empty = torch.empty(0, 4, 128, device=cuda)
     out = pkg.gated_readout_epilogue(empty, empty, empty, empty, empty, *gr[5:], 2)
     assert out.numel() == 0
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 64, 256), (1, 130, 72, 264), (3, 33, 128, 520), (1, 1, 8, 8),
+                                   (2, 300, 768, 3072)])
+def test_channel_mixer(pkg, oracle, workloads, cuda, shape):
+    """Token-shift mix, key projection with relu^2 in the epilogue, value projection, against the fp64
+    oracle on the same bf16 inputs.  The tensor-core path rounds key_input and the hidden activation
+    to bf16 once each (the reference with F = bf16 rounds after every op), so the tolerance is the
+    bf16 rounding of those two operands through the contractions: 2e-2 of the output's largest
+    magnitude, plus one bf16 spacing for the output's own storage.  Shapes cover edge tiles in every
+    dimension (rows, C and F not multiples of the 128 x 256 x 64 tile)."""
+    B, T, C, F = shape
+    x, ks, kw, vw = workloads.channel_mixer_inputs(B, T, C, F, seed=3)
+    ref = oracle.channel_mixer(x.float().numpy(), ks.float().numpy(), kw.float().numpy(), vw.float().numpy())
+    out = pkg.channel_mixer_custom(x.to(cuda), ks.to(cuda), kw.to(cuda), vw.to(cuda))
+    torch.cuda.synchronize()
+    assert pkg.read_device_status(0) == 0
+    got = out.float().cpu().numpy().astype(np.float64)
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= 2e-2 * scale, np.abs(got - ref).max() / scale
+    assert parity.stats(got, ref)["cosine"] >= 0.9999
+    # a finer check against a restatement that rounds where the kernel rounds
+    ki = torch.cat([torch.zeros(B, 1, C), x.float()[:, :-1]], 1)
+    ki = (x.float() + (ki - x.float()) * ks.float()).to(torch.bfloat16).double().reshape(B * T, C)
+    hid = (torch.relu(ki @ kw.double().T) ** 2).to(torch.bfloat16).double()
+    fine = (hid @ vw.double().T).reshape(B, T, C).numpy()
+    tol = 2e-3 * np.abs(fine).max() + 2 * parity.BF16_ULP * np.abs(fine)
+    assert (np.abs(got - fine) <= tol).all(), float((np.abs(got - fine) - tol).max())
+
+
+def test_channel_mixer_contracts(pkg, workloads, cuda):
+    x, ks, kw, vw = (t.to(cuda) for t in workloads.channel_mixer_inputs(1, 4, 64, 128, seed=4))
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.channel_mixer_custom(x, ks[:32].contiguous(), kw, vw)
+    assert e.value.kind == "ShapeMismatch"
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.channel_mixer_custom(x, ks, kw, vw.T.contiguous())
+    assert e.value.kind in ("AxisMismatch", "ShapeMismatch")
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.channel_mixer_custom(x.float(), ks.float(), kw.float(), vw.float())
+    assert e.value.kind == "Unsupported"
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.channel_mixer_custom(x, ks, kw, vw, workspace=torch.empty(256, dtype=torch.uint8, device=cuda))
+    assert e.value.kind == "WorkspaceTooSmall"
+    empty = pkg.channel_mixer_custom(x[:, :0].contiguous(), ks, kw, vw)
+    assert empty.shape == (1, 0, 64)

@@ -182,3 +182,14 @@ def test_weight_prepare_zero_key_uses_the_epsilon(oracle):
     got = oracle.weight_prepare(z, z, z, one, one, 2)
     assert np.array_equal(got["removal_key_normalized"], np.zeros_like(z, dtype=np.float64))
     np.testing.assert_allclose(got["weight_decay"], -np.log(2.0) - 0.5)
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 16, 40), (1, 1, 8, 8), (3, 4, 24, 64)])
+def test_channel_mixer_matches_torch_restatement(oracle, workloads, shape):
+    """channel_mixer/mod.rs:204-232 compares the custom path with channel_mixer_reference; here
+    the C restatement against the same tensor ops in torch fp64."""
+    import torch_restatement as tr
+    x, ks, kw, vw = workloads.channel_mixer_inputs(*shape, seed=2, dtype=torch.float32)
+    ref = tr.channel_mixer_reference(x.double(), ks.double(), kw.double(), vw.double())
+    got = oracle.channel_mixer(x.numpy(), ks.numpy(), kw.numpy(), vw.numpy())
+    np.testing.assert_allclose(got, ref.numpy(), rtol=1e-12, atol=1e-12)

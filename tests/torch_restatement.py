@@ -90,3 +90,12 @@ def gated_readout_reference(wkv7_output, receptance, replacement_key, value, gat
     r4, k4, v4 = (t.reshape(B, T, num_heads, N) for t in (receptance, replacement_key, value))
     bonus4 = (r4 * k4 * bonus.reshape(1, 1, num_heads, N)).sum(3, keepdim=True) * v4
     return (norm + bonus4.reshape(B, T, C)) * gate
+
+
+def channel_mixer_reference(x, key_scale, key_weight, value_weight):
+    """``channel_mixer_reference`` (``kernels/train/channel_mixer/mod.rs:96-128``), op for op."""
+    B, T, C = x.shape
+    shifted = torch.cat([torch.zeros(B, 1, C, dtype=x.dtype), x[:, :T - 1]], 1) if T > 0 else x
+    key_input = x + (shifted - x) * key_scale.reshape(1, 1, C)
+    activated = torch.relu(key_input.reshape(B * T, C) @ key_weight.T).pow(2.0)
+    return (activated @ value_weight.T).reshape(B, T, C)
