@@ -195,6 +195,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-streaming", action="store_true")
     ap.add_argument("--no-channel-mixer", action="store_true")
+    ap.add_argument("--no-train", action="store_true")
     ap.add_argument("--no-lm-head", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
@@ -395,6 +396,39 @@ def main():
                    "mean_loss": float(loss.mean().item())}
         del xl, wl, tl
 
+    # ---- training forward (with saved tensors) and backward at configuration 1 ------------
+    train = None
+    if not args.no_train and rank == 0:
+        peak_gbs, _ = measured_peaks()
+        tin = pkg.Wkv7PretrainForwardInputs(*six)
+        saved = pkg.wkv7_forward_saved(tin, None, want_state=True)
+        dy = torch.randn_like(six[0])
+
+        def timed(fn, reps=3):
+            fn()
+            torch.cuda.synchronize()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(reps):
+                fn()
+            b_.record()
+            torch.cuda.synchronize()
+            return a_.elapsed_time(b_) / reps
+
+        seq_bytes = B * T * H * N * 2
+        snap_bytes = B * H * (T // 16) * N * N * 4
+        fwd_ms = timed(lambda: pkg.wkv7_forward_saved(tin, None, want_state=True))
+        bwd_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None))
+        fwd_bytes = 8 * seq_bytes + snap_bytes + B * H * STATE_BYTES             # 6 in, y and sa out, snapshots, S_T
+        bwd_bytes = 14 * seq_bytes + snap_bytes + B * H * STATE_BYTES            # 6 in, sa, dy, 6 grads, snapshots, dS0
+        train = {"workload": f"B={B} T={T} H={H} N={N} bf16, chunk_len 16",
+                 "forward_saved_ms": fwd_ms, "forward_saved_gb_per_s": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                 "forward_saved_frac_of_hbm_peak": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak_gbs,
+                 "backward_ms": bwd_ms, "backward_gb_per_s": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
+                 "backward_frac_of_hbm_peak": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak_gbs,
+                 "forward_algorithmic_bytes": fwd_bytes, "backward_algorithmic_bytes": bwd_bytes}
+        del saved, dy
+
     # ---- channel mixer at the configuration-2 layer shape (two tensor-core projections) ---
     channel_mixer = None
     if not args.no_channel_mixer and rank == 0:
@@ -457,6 +491,7 @@ def main():
         "streaming": streaming,
         "lm_head_ce": lm_head,
         "channel_mixer": channel_mixer,
+        "train": train,
     }
     if not args.no_cpu_baseline:
         oracle = entry.load_oracle()

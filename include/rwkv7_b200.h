@@ -191,6 +191,50 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *initial_state,
                                        rwkv7_tensor *output, rwkv7_tensor *next_state,
                                        rwkv7_stream stream);
 
+/* ------------------------------------------------------- wkv7 training -- */
+/*
+ * The forward pass as the reference runs it under autodiff: the recurrence of
+ * rwkv7_fused_wkv7_statepass plus the two tensors its backward pass consumes
+ * (wkv7/forward.rs:368-375,460-472; written by kernel.rs:60-196,198-364):
+ *   snapshots         [B, H, T/chunk_len, N, N]  the state after the last token of every chunk
+ *                     (index order kernel.rs:40-53); F32 here, where the reference stores
+ *                     the sequence dtype
+ *   state_replacement [B, T, H, N]  sa_t = S_{t-1} a_t, sequence dtype.
+ * initial_state may be NULL (pretrain: S0 = 0) and next_state may be NULL (pretrain,
+ * statetune).  T must be a multiple of chunk_len (the reference also asserts chunk_len == 16;
+ * any positive value is accepted here).  No workspace.
+ */
+int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *initial_state, const rwkv7_tensor *receptance,
+                                   const rwkv7_tensor *weight_decay,
+                                   const rwkv7_tensor *replacement_key, const rwkv7_tensor *value,
+                                   const rwkv7_tensor *removal_key_normalized,
+                                   const rwkv7_tensor *replacement, int64_t chunk_len,
+                                   rwkv7_tensor *output, rwkv7_tensor *next_state,
+                                   rwkv7_tensor *snapshots, rwkv7_tensor *state_replacement,
+                                   rwkv7_stream stream);
+
+/*
+ * Replaces launch_wkv7_backward / wkv7_backward_kernel (wkv7/backward.rs:583-703,
+ * kernel.rs:395-690): gradients of the six sequence tensors and of the initial state, given
+ * the gradient of y (output_grad) and of the final state (next_state_grad, NULL = zero).
+ * sequence_grads are in the order receptance, weight_decay, replacement_key, value,
+ * removal_key_normalized, replacement (Wkv7BackwardPrimitiveOutputs, backward.rs:567-575);
+ * state gradients are F32 [B,H,N,N]; initial_state_grad may be NULL.  initial_state is the
+ * state the forward started from (NULL = zero): the reference rebuilds the state before each
+ * token by dividing by the decay going backwards (kernel.rs:516-521), which loses all accuracy
+ * for small decays; here each chunk is replayed forwards from the snapshot at its start
+ * instead, which needs the initial state for the first chunk.  N <= 64; chunk_len 4, 8, 12 or 16.
+ */
+int rwkv7_fused_wkv7_backward(const rwkv7_tensor *initial_state, const rwkv7_tensor *receptance,
+                              const rwkv7_tensor *weight_decay, const rwkv7_tensor *replacement_key,
+                              const rwkv7_tensor *value,
+                              const rwkv7_tensor *removal_key_normalized,
+                              const rwkv7_tensor *replacement, const rwkv7_tensor *snapshots,
+                              const rwkv7_tensor *state_replacement, int64_t chunk_len,
+                              const rwkv7_tensor *output_grad, const rwkv7_tensor *next_state_grad,
+                              rwkv7_tensor *const sequence_grads[6],
+                              rwkv7_tensor *initial_state_grad, rwkv7_stream stream);
+
 /* ------------------------------------------------------------------ mix6 -- */
 /* Replaces Mix6Backend::fused_mix6 (mix6/mod.rs:25-28, impl :42-73; kernel
  * mix6/kernel.rs:25-57): prev = x[b,t-1,:] (0 at t == 0);

@@ -70,6 +70,35 @@ def wkv7(r, w, k, v, a, b, s0=None, *, precision="f64", want_state=True):
     return y, s_out
 
 
+def wkv7_train(r, w, k, v, a, b, s0=None, chunk_len=16):
+    """Training forward in float64: ``(y, s_out, snapshots [B,H,T/chunk_len,N,N], state_replacement)``."""
+    r, w, k, v, a, b = (_f32(t) for t in (r, w, k, v, a, b))
+    B, T, H, N = r.shape
+    s0d = None if s0 is None else np.ascontiguousarray(s0, dtype=np.float64)
+    y = np.empty((B, T, H, N), dtype=np.float64)
+    sa = np.empty((B, T, H, N), dtype=np.float64)
+    s_out = np.empty((B, H, N, N), dtype=np.float64)
+    snaps = np.empty((B, H, T // chunk_len, N, N), dtype=np.float64)
+    lib().oracle_wkv7_train_f64(_p(r), _p(w), _p(k), _p(v), _p(a), _p(b), _p(s0d), _p(y), _p(s_out), _p(snaps),
+                                _p(sa), *[ctypes.c_int64(x) for x in (B, T, H, N, chunk_len)])
+    return y, s_out, snaps, sa
+
+
+def wkv7_backward(r, w, k, v, a, b, dy, s0=None, ds_out=None):
+    """Exact reverse-mode gradients in float64: ``dict(r, w, k, v, a, b, s0)``."""
+    r, w, k, v, a, b = (_f32(t) for t in (r, w, k, v, a, b))
+    B, T, H, N = r.shape
+    s0d = None if s0 is None else np.ascontiguousarray(s0, dtype=np.float64)
+    dyd = np.ascontiguousarray(dy, dtype=np.float64)
+    dsd = None if ds_out is None else np.ascontiguousarray(ds_out, dtype=np.float64)
+    g = {n: np.empty((B, T, H, N), dtype=np.float64) for n in "rwkvab"}
+    g["s0"] = np.empty((B, H, N, N), dtype=np.float64)
+    lib().oracle_wkv7_backward_f64(_p(r), _p(w), _p(k), _p(v), _p(a), _p(b), _p(s0d), _p(dyd), _p(dsd),
+                                   _p(g["r"]), _p(g["w"]), _p(g["k"]), _p(g["v"]), _p(g["a"]), _p(g["b"]),
+                                   _p(g["s0"]), *[ctypes.c_int64(x) for x in (B, T, H, N)])
+    return g
+
+
 def mix6(x, mus):
     """Six token-shift mixes; returns a float64 array ``[6, B, T, C]``."""
     x = _f32(x)

@@ -154,6 +154,139 @@ void oracle_wkv7_f64(const float *r, const float *w, const float *k, const float
     }
 }
 
+/* -------------------------------------------------------- wkv7 training -- */
+
+/*
+ * Training forward (wkv7/kernel.rs:60-196,198-364 with forward.rs:368-375): the
+ * recurrence above, also returning what the reference saves for its backward pass:
+ * snapshots [B][H][T/chunk_len][N][N] = S after the last token of each chunk
+ * (index order kernel.rs:40-53) and state_replacement [B][T][H][N] = sa_t.
+ */
+void oracle_wkv7_train_f64(const float *r, const float *w, const float *k, const float *v,
+                           const float *a, const float *b, const double *s0, double *y,
+                           double *s_out, double *snapshots, double *state_replacement, int64_t B,
+                           int64_t T, int64_t H, int64_t N, int64_t chunk_len) {
+    const int64_t BH = B * H, nchunks = T / chunk_len;
+#pragma omp parallel
+    {
+        double *S = (double *)malloc(sizeof(double) * (size_t)(N * N));
+        double *d = (double *)malloc(sizeof(double) * (size_t)N);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t bh = 0; bh < BH; ++bh) {
+            const int64_t bi = bh / H, h = bh % H;
+            if (s0) memcpy(S, s0 + bh * N * N, sizeof(double) * (size_t)(N * N));
+            else memset(S, 0, sizeof(double) * (size_t)(N * N));
+            for (int64_t t = 0; t < T; ++t) {
+                const int64_t o = ((bi * T + t) * H + h) * N;
+                for (int64_t j = 0; j < N; ++j) d[j] = exp(-exp((double)w[o + j]));
+                for (int64_t i = 0; i < N; ++i) {
+                    double *Si = S + i * N;
+                    double sa = 0.0;
+                    for (int64_t j = 0; j < N; ++j) sa += Si[j] * (double)a[o + j];
+                    state_replacement[o + i] = sa;
+                    const double vi = (double)v[o + i];
+                    double acc = 0.0;
+                    for (int64_t j = 0; j < N; ++j) {
+                        const double u = Si[j] * d[j] + sa * (double)b[o + j] + vi * (double)k[o + j];
+                        Si[j] = u;
+                        acc += u * (double)r[o + j];
+                    }
+                    y[o + i] = acc;
+                }
+                if ((t + 1) % chunk_len == 0)
+                    memcpy(snapshots + (bh * nchunks + t / chunk_len) * N * N, S, sizeof(double) * (size_t)(N * N));
+            }
+            if (s_out) memcpy(s_out + bh * N * N, S, sizeof(double) * (size_t)(N * N));
+        }
+        free(S);
+        free(d);
+    }
+}
+
+/*
+ * Backward pass: exact reverse-mode differentiation of the recurrence, in double, with every
+ * intermediate state kept (no rebuilding by inverse decay, which is how the reference's kernel
+ * kernel.rs:395-690 saves memory).  Per token, with S the state before and S' after it:
+ *   dS' += dy r^T; dr = S'^T dy; dv = dS' k; dk = dS'^T v; dsa = dS' b; db = dS'^T sa;
+ *   dd_j = sum_i dS'_ij S_ij; dw = dd * (-exp(w) d); da = S^T dsa; dS = dS' diag(d) + dsa a^T.
+ * grads are laid out like the inputs; ds0 [B][H][N][N]; dsT may be NULL (zero).
+ */
+void oracle_wkv7_backward_f64(const float *r, const float *w, const float *k, const float *v,
+                              const float *a, const float *b, const double *s0, const double *dy,
+                              const double *dsT, double *dr, double *dw, double *dk, double *dv,
+                              double *da, double *db, double *ds0, int64_t B, int64_t T, int64_t H,
+                              int64_t N) {
+    const int64_t BH = B * H, NN = N * N;
+#pragma omp parallel
+    {
+        double *states = (double *)malloc(sizeof(double) * (size_t)((T + 1) * NN));   /* S_0 .. S_T */
+        double *sas = (double *)malloc(sizeof(double) * (size_t)(T * N));
+        double *dS = (double *)malloc(sizeof(double) * (size_t)NN);
+        double *d = (double *)malloc(sizeof(double) * (size_t)N);
+        double *dsa = (double *)malloc(sizeof(double) * (size_t)N);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t bh = 0; bh < BH; ++bh) {
+            const int64_t bi = bh / H, h = bh % H;
+            if (s0) memcpy(states, s0 + bh * NN, sizeof(double) * (size_t)NN);
+            else memset(states, 0, sizeof(double) * (size_t)NN);
+            for (int64_t t = 0; t < T; ++t) {
+                const int64_t o = ((bi * T + t) * H + h) * N;
+                const double *S = states + t * NN;
+                double *S1 = states + (t + 1) * NN;
+                for (int64_t i = 0; i < N; ++i) {
+                    double sa = 0.0;
+                    for (int64_t j = 0; j < N; ++j) sa += S[i * N + j] * (double)a[o + j];
+                    sas[t * N + i] = sa;
+                    for (int64_t j = 0; j < N; ++j)
+                        S1[i * N + j] = S[i * N + j] * exp(-exp((double)w[o + j])) + sa * (double)b[o + j] +
+                                        (double)v[o + i] * (double)k[o + j];
+                }
+            }
+            if (dsT) memcpy(dS, dsT + bh * NN, sizeof(double) * (size_t)NN);
+            else memset(dS, 0, sizeof(double) * (size_t)NN);
+            for (int64_t t = T - 1; t >= 0; --t) {
+                const int64_t o = ((bi * T + t) * H + h) * N;
+                const double *S = states + t * NN, *S1 = states + (t + 1) * NN;
+                for (int64_t j = 0; j < N; ++j) d[j] = exp(-exp((double)w[o + j]));
+                for (int64_t i = 0; i < N; ++i)
+                    for (int64_t j = 0; j < N; ++j) dS[i * N + j] += dy[o + i] * (double)r[o + j];
+                for (int64_t j = 0; j < N; ++j) {
+                    double g_r = 0.0, g_k = 0.0, g_b = 0.0, g_d = 0.0;
+                    for (int64_t i = 0; i < N; ++i) {
+                        g_r += S1[i * N + j] * dy[o + i];
+                        g_k += dS[i * N + j] * (double)v[o + i];
+                        g_b += dS[i * N + j] * sas[t * N + i];
+                        g_d += dS[i * N + j] * S[i * N + j];
+                    }
+                    dr[o + j] = g_r;
+                    dk[o + j] = g_k;
+                    db[o + j] = g_b;
+                    dw[o + j] = g_d * (-exp((double)w[o + j]) * d[j]);
+                }
+                for (int64_t i = 0; i < N; ++i) {
+                    double g_v = 0.0, g_sa = 0.0;
+                    for (int64_t j = 0; j < N; ++j) {
+                        g_v += dS[i * N + j] * (double)k[o + j];
+                        g_sa += dS[i * N + j] * (double)b[o + j];
+                    }
+                    dv[o + i] = g_v;
+                    dsa[i] = g_sa;
+                }
+                for (int64_t j = 0; j < N; ++j) {
+                    double g_a = 0.0;
+                    for (int64_t i = 0; i < N; ++i) g_a += S[i * N + j] * dsa[i];
+                    da[o + j] = g_a;
+                }
+                for (int64_t i = 0; i < N; ++i)
+                    for (int64_t j = 0; j < N; ++j)
+                        dS[i * N + j] = dS[i * N + j] * d[j] + dsa[i] * (double)a[o + j];
+            }
+            if (ds0) memcpy(ds0 + bh * NN, dS, sizeof(double) * (size_t)NN);
+        }
+        free(states); free(sas); free(dS); free(d); free(dsa);
+    }
+}
+
 /* ------------------------------------------------------------------ mix6 -- */
 
 /*

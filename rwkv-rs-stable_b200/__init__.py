@@ -276,6 +276,78 @@ class Wkv7StatepassCall:
             _check(st)
 
 
+@dataclass
+class Wkv7SavedForward:
+    """Outputs of the training forward: what the reference's forward kernels return under
+    autodiff (``wkv7/forward.rs:368-375``)."""
+
+    output: torch.Tensor
+    next_state: Optional[torch.Tensor]
+    snapshots: torch.Tensor            # [B, H, T/chunk_len, N, N] fp32
+    state_replacement: torch.Tensor    # [B, T, H, N]
+
+
+def wkv7_forward_saved(inputs: Wkv7PretrainForwardInputs, initial_state: Optional[torch.Tensor] = None, *,
+                       want_state: bool = False) -> Wkv7SavedForward:
+    """``rwkv7_fused_wkv7_forward_saved``: the recurrence plus the tensors the backward pass needs."""
+    inputs.check(True)
+    r = inputs.receptance
+    B, T, H, N = r.shape
+    y = torch.empty_like(r)
+    sa = torch.empty_like(r)
+    snaps = torch.empty((B, H, T // inputs.chunk_len, N, N), dtype=torch.float32, device=r.device)
+    s_out = torch.empty((B, H, N, N), dtype=torch.float32, device=r.device) if want_state else None
+    descs = [describe(initial_state)] + [describe(t) for t in inputs.six()]
+    outs = [describe(y), describe(s_out), describe(snaps), describe(sa)]
+    _check(lib().rwkv7_fused_wkv7_forward_saved(*[_ref(d) for d in descs], ctypes.c_int64(inputs.chunk_len),
+                                                *[_ref(d) for d in outs], _stream(r)))
+    return Wkv7SavedForward(output=y, next_state=s_out, snapshots=snaps, state_replacement=sa)
+
+
+def wkv7_backward(inputs: Wkv7PretrainForwardInputs, saved: Wkv7SavedForward, output_grad: torch.Tensor,
+                  next_state_grad: Optional[torch.Tensor] = None, *, initial_state: Optional[torch.Tensor] = None,
+                  want_state_grad: bool = True):
+    """``rwkv7_fused_wkv7_backward``: returns ``(six sequence gradients in input order,
+    initial_state_grad or None)`` (``Wkv7BackwardPrimitiveOutputs``, ``wkv7/backward.rs:567-575``)."""
+    r = inputs.receptance
+    B, T, H, N = r.shape
+    grads = [torch.empty_like(r) for _ in range(6)]
+    ds0 = torch.empty((B, H, N, N), dtype=torch.float32, device=r.device) if want_state_grad else None
+    gd = [describe(t) for t in grads]
+    arr = (ctypes.POINTER(Tensor) * 6)(*[ctypes.pointer(d) for d in gd])
+    descs = [describe(initial_state)] + [describe(t) for t in inputs.six()] + [describe(saved.snapshots),
+                                                                            describe(saved.state_replacement)]
+    dyd, dsd, ds0d = describe(output_grad.contiguous()), describe(next_state_grad), describe(ds0)
+    _check(lib().rwkv7_fused_wkv7_backward(*[_ref(d) for d in descs], ctypes.c_int64(inputs.chunk_len), _ref(dyd),
+                                           _ref(dsd), arr, _ref(ds0d), _stream(r)))
+    return grads, ds0
+
+
+class _Wkv7Function(torch.autograd.Function):
+    """The autodiff node of the reference (``Wkv7StatepassBackward``, ``wkv7/backward.rs:381-533``):
+    forward saves snapshots and state_replacement, backward runs the reverse kernel."""
+
+    @staticmethod
+    def forward(ctx, r, w, k, v, a, b, s0, chunk_len):
+        inputs = Wkv7PretrainForwardInputs(r, w, k, v, a, b, chunk_len=chunk_len)
+        saved = wkv7_forward_saved(inputs, s0, want_state=True)
+        ctx.inputs, ctx.saved, ctx.has_state, ctx.s0 = inputs, saved, s0 is not None, s0
+        ctx.mark_non_differentiable(saved.snapshots, saved.state_replacement)
+        return saved.output, saved.next_state
+
+    @staticmethod
+    def backward(ctx, dy, ds):
+        grads, ds0 = wkv7_backward(ctx.inputs, ctx.saved, dy, None if ds is None else ds.contiguous(),
+                                   initial_state=ctx.s0, want_state_grad=ctx.has_state)
+        return (*grads, ds0, None)
+
+
+def wkv7_statepass_autograd(initial_state: Optional[torch.Tensor], sequence: Wkv7PretrainForwardInputs):
+    """Differentiable statepass: ``(output, next_state)`` with gradients to the six sequence tensors and
+    the initial state, like ``wkv7_statepass_custom`` on the reference's Autodiff backend."""
+    return _Wkv7Function.apply(*[t.contiguous() for t in sequence.six()], initial_state, sequence.chunk_len)
+
+
 class Wkv7HostStatepass:
     """Statepass for callers whose six sequence tensors, y and S_T live in pinned
     host memory (an inference server that receives activations from another

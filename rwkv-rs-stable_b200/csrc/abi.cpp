@@ -322,6 +322,116 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *s0, const rwkv7_tenso
     return wkv7_run(s0, six, chunk_len, output, next_state, true, scratch, scratch_bytes, stream, true);
 }
 
+namespace {
+
+const char *kSixNames[6] = {"receptance", "weight_decay", "replacement_key",
+                            "value", "removal_key_normalized", "replacement"};
+
+// The reference's training contract (wkv7/io.rs:187,198-201): positive chunk_len dividing T.
+int check_training_chunks(const TensorInfo &r, int64_t chunk_len) {
+    if (r.dim(1) % chunk_len != 0)
+        return fail(RWKV7_ERR_BAD_CHUNK, "BadChunk: context_len must be a multiple of chunk_len");
+    return RWKV7_OK;
+}
+
+int check_snapshots(const TensorInfo &snap, const TensorInfo &r, int64_t chunk_len) {
+    RWKV7_TRY(check_present(snap, 5));
+    RWKV7_TRY(check_shape(snap, {r.dim(0), r.dim(2), r.dim(1) / chunk_len, r.dim(3), r.dim(3)}));
+    if (snap.t->dtype != RWKV7_F32)
+        return fail(RWKV7_ERR_DTYPE_MISMATCH, "DTypeMismatch: kernel input dtype mismatch: %s=%s, expected F32",
+                    snap.name, dtype_name(snap.t->dtype));
+    RWKV7_TRY(check_same_device({snap, r}));
+    return check_contiguous(snap);
+}
+
+}  // namespace
+
+int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, const rwkv7_tensor *w,
+                                   const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                                   const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
+                                   rwkv7_tensor *next_state, rwkv7_tensor *snapshots,
+                                   rwkv7_tensor *state_replacement, rwkv7_stream stream) {
+    clear_error();
+    const rwkv7_tensor *six_t[6] = {r_t, w, k, v, a, b};
+    TensorInfo six[6];
+    for (int i = 0; i < 6; ++i) six[i] = TensorInfo{kSixNames[i], six_t[i]};
+    RWKV7_TRY(check_wkv7_sequence(six, chunk_len));
+    const TensorInfo &r = six[0];
+    RWKV7_TRY(check_training_chunks(r, chunk_len));
+    if (s0 != nullptr) RWKV7_TRY(check_wkv7_state(TensorInfo{"initial_state", s0}, r));
+    RWKV7_TRY(check_output_like(r, TensorInfo{"output", output}));
+    if (next_state != nullptr) RWKV7_TRY(check_wkv7_state(TensorInfo{"next_state", next_state}, r));
+    RWKV7_TRY(check_snapshots(TensorInfo{"snapshots", snapshots}, r, chunk_len));
+    RWKV7_TRY(check_output_like(r, TensorInfo{"state_replacement", state_replacement}));
+    Wkv7Args p{};
+    p.r = r_t->data; p.w = w->data; p.k = k->data; p.v = v->data; p.a = a->data; p.b = b->data;
+    p.s0 = s0 ? static_cast<const float *>(s0->data) : nullptr;
+    p.y = output->data;
+    p.s_out = next_state ? static_cast<float *>(next_state->data) : nullptr;
+    p.B = r.dim(0); p.T = r.dim(1); p.H = r.dim(2); p.N = r.dim(3);
+    p.bf16 = r_t->dtype == RWKV7_BF16;
+    p.device = r_t->device;
+    if (p.B == 0 || p.H == 0) return RWKV7_OK;
+    if (p.N > 128) return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: head size N=%lld exceeds 128", (long long)p.N);
+    DeviceGuard guard(p.device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    RWKV7_TRY(num_sms(p.device, &p.num_sms));
+    if (int e = launch_wkv7_forward_saved(p, static_cast<float *>(snapshots->data), state_replacement->data,
+                                          (int)chunk_len, (cudaStream_t)stream))
+        return cuda_fail("wkv7 training forward launch", e);
+    return RWKV7_OK;
+}
+
+int rwkv7_fused_wkv7_backward(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, const rwkv7_tensor *w,
+                              const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                              const rwkv7_tensor *b, const rwkv7_tensor *snapshots, const rwkv7_tensor *state_replacement,
+                              int64_t chunk_len, const rwkv7_tensor *output_grad,
+                              const rwkv7_tensor *next_state_grad, rwkv7_tensor *const sequence_grads[6],
+                              rwkv7_tensor *initial_state_grad, rwkv7_stream stream) {
+    clear_error();
+    const rwkv7_tensor *six_t[6] = {r_t, w, k, v, a, b};
+    TensorInfo six[6];
+    for (int i = 0; i < 6; ++i) six[i] = TensorInfo{kSixNames[i], six_t[i]};
+    RWKV7_TRY(check_wkv7_sequence(six, chunk_len));
+    const TensorInfo &r = six[0];
+    RWKV7_TRY(check_training_chunks(r, chunk_len));
+    if (chunk_len > 16 || chunk_len % 4 != 0)
+        return fail(RWKV7_ERR_BAD_CHUNK, "BadChunk: the backward pass supports chunk_len 4, 8, 12 or 16, got %lld",
+                    (long long)chunk_len);
+    if (s0 != nullptr) RWKV7_TRY(check_wkv7_state(TensorInfo{"initial_state", s0}, r));
+    RWKV7_TRY(check_snapshots(TensorInfo{"snapshots", snapshots}, r, chunk_len));
+    RWKV7_TRY(check_output_like(r, TensorInfo{"state_replacement", state_replacement}));
+    RWKV7_TRY(check_output_like(r, TensorInfo{"output_grad", output_grad}));
+    if (next_state_grad != nullptr) RWKV7_TRY(check_wkv7_state(TensorInfo{"next_state_grad", next_state_grad}, r));
+    if (sequence_grads == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: sequence_grads array is null");
+    static const char *grad_names[6] = {"receptance_grad", "weight_decay_grad", "replacement_key_grad",
+                                        "value_grad", "removal_key_normalized_grad", "replacement_grad"};
+    for (int i = 0; i < 6; ++i) RWKV7_TRY(check_output_like(r, TensorInfo{grad_names[i], sequence_grads[i]}));
+    if (initial_state_grad != nullptr)
+        RWKV7_TRY(check_wkv7_state(TensorInfo{"initial_state_grad", initial_state_grad}, r));
+    Wkv7BackwardArgs p{};
+    p.r = r_t->data; p.w = w->data; p.k = k->data; p.v = v->data; p.a = a->data; p.b = b->data;
+    p.snapshots = static_cast<const float *>(snapshots->data);
+    p.state_replacement = state_replacement->data;
+    p.output_grad = output_grad->data;
+    p.initial_state = s0 ? static_cast<const float *>(s0->data) : nullptr;
+    p.next_state_grad = next_state_grad ? static_cast<const float *>(next_state_grad->data) : nullptr;
+    p.receptance_grad = sequence_grads[0]->data; p.weight_decay_grad = sequence_grads[1]->data;
+    p.replacement_key_grad = sequence_grads[2]->data; p.value_grad = sequence_grads[3]->data;
+    p.removal_key_normalized_grad = sequence_grads[4]->data; p.replacement_grad = sequence_grads[5]->data;
+    p.initial_state_grad = initial_state_grad ? static_cast<float *>(initial_state_grad->data) : nullptr;
+    p.B = r.dim(0); p.T = r.dim(1); p.H = r.dim(2); p.N = r.dim(3); p.chunk_len = chunk_len;
+    p.bf16 = r_t->dtype == RWKV7_BF16;
+    if (p.B == 0 || p.H == 0) return RWKV7_OK;
+    if (p.N > 64)
+        return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: the backward pass keeps its work matrices in shared memory, "
+                                           "head size N=%lld exceeds 64", (long long)p.N);
+    DeviceGuard guard(r_t->device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    if (int e = launch_wkv7_backward(p, (cudaStream_t)stream)) return cuda_fail("wkv7 backward launch", e);
+    return RWKV7_OK;
+}
+
 int rwkv7_fused_mix6(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6],
                      rwkv7_tensor *const outputs[6], rwkv7_stream stream) {
     clear_error();

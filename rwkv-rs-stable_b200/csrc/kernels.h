@@ -35,6 +35,26 @@ int launch_wkv7_sequential(const Wkv7Args &p, cudaStream_t stream);
 // Decode sweep (N == 64, a few tokens): one pass over the fp32 state per call.
 int launch_wkv7_decode(const Wkv7Args &p, cudaStream_t stream);
 
+// Training forward: the sequential scan, also writing snapshots [B,H,T/chunk_len,N,N] (fp32 state
+// after the last token of every chunk) and state_replacement [B,T,H,N] (sa_t, sequence dtype).
+int launch_wkv7_forward_saved(const Wkv7Args &p, float *snapshots, void *state_replacement, int chunk_len,
+                              cudaStream_t stream);
+
+// Backward pass over the tensors the training forward saved.
+struct Wkv7BackwardArgs {
+    const void *r, *w, *k, *v, *a, *b;          // [B,T,H,N]
+    const float *snapshots;                      // [B,H,T/chunk_len,N,N]
+    const void *state_replacement, *output_grad; // [B,T,H,N]
+    const float *initial_state;                  // [B,H,N,N] or null (zero): the state the forward started from
+    const float *next_state_grad;                // [B,H,N,N] or null (zero)
+    void *receptance_grad, *weight_decay_grad, *replacement_key_grad, *value_grad,
+        *removal_key_normalized_grad, *replacement_grad;   // [B,T,H,N]
+    float *initial_state_grad;                   // [B,H,N,N] or null
+    int64_t B, T, H, N, chunk_len;
+    bool bf16;
+};
+int launch_wkv7_backward(const Wkv7BackwardArgs &p, cudaStream_t stream);
+
 // Chunked tensor-core prefill (N == 64): tcgen05 MMAs with TMEM accumulators.
 size_t wkv7_chunked_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 bool wkv7_chunked_supported(const Wkv7Args &p);

@@ -65,10 +65,19 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
     return __float2bfloat16_rn(x);
 }
 
-template <typename T, int ROWS>
+// Tensors a training forward saves for the backward pass (wkv7/forward.rs:368-375):
+// snapshots [B,H,T/chunk_len,N,N] = the state after the last token of every chunk (fp32 here),
+// state_replacement [B,T,H,N] = sa_t = S_{t-1} a_t, in the sequence dtype.
+struct SavePtrs {
+    float *snapshots;
+    void *state_replacement;
+    int chunk_len;
+};
+
+template <typename T, int ROWS, bool SAVE = false>
 __global__ void __launch_bounds__(ROWS * 4)
 wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
-                  float *s_out, int Tlen, int H, const int *__restrict__ flags) {
+                  float *s_out, int Tlen, int H, const int *__restrict__ flags, SavePtrs save = SavePtrs{}) {
     constexpr int THREADS = ROWS * 4;
     constexpr int SPLITS = kN / ROWS;
     constexpr int EPV = Vec16<T>::kElems;
@@ -79,6 +88,7 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float *vec = reinterpret_cast<float *>(smem_raw);             // [2][kTile][6][kN]
     float *ytile = vec + 2 * kTile * 6 * kN;                      // [2][kTile][ROWS]
+    float *satile = ytile + 2 * kTile * ROWS;                     // [2][kTile][ROWS], SAVE only
 
     const int bh = blockIdx.x / SPLITS;
     // Fallback mode: only the chains another kernel flagged are (re)computed.
@@ -159,6 +169,7 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
         const int ntok = min(kTile, Tlen - tile * kTile);
         const float *tv = vec + (size_t)buf * kTile * 6 * kN;
         float *yt = ytile + (size_t)buf * kTile * ROWS;
+        float *sat = satile + (size_t)buf * kTile * ROWS;
 
         for (int tt = 0; tt < ntok; ++tt) {
             const float *base = tv + (size_t)tt * 6 * kN;
@@ -175,6 +186,9 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
             float sa = (sa0 + sa1) + (sa2 + sa3);
             sa += __shfl_xor_sync(0xffffffffu, sa, 1);
             sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+            if constexpr (SAVE) {
+                if (q == 0) sat[tt * ROWS + i] = sa;
+            }
             const float vi = base[VV * kN + row0 + i];
             const float4 *d4 = reinterpret_cast<const float4 *>(base + VD * kN);
             const float4 *b4 = reinterpret_cast<const float4 *>(base + VB * kN);
@@ -195,6 +209,17 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
             yy += __shfl_xor_sync(0xffffffffu, yy, 1);
             yy += __shfl_xor_sync(0xffffffffu, yy, 2);
             if (q == 0) yt[tt * ROWS + i] = yy;
+            if constexpr (SAVE) {
+                const int t = tile * kTile + tt;
+                if ((t + 1) % save.chunk_len == 0) {   // state after the last token of a chunk
+                    const int chunk = t / save.chunk_len, nchunks = Tlen / save.chunk_len;
+                    float4 *dst = reinterpret_cast<float4 *>(
+                        save.snapshots + (((size_t)bh * nchunks + chunk) * kN + row0 + i) * kN);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        dst[kk * 4 + q] = make_float4(S[kk * 4 + 0], S[kk * 4 + 1], S[kk * 4 + 2], S[kk * 4 + 3]);
+                }
+            }
         }
 
         if (tile + 1 < ntiles) commit_stage(buf ^ 1);
@@ -203,6 +228,7 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
             const int tt = idx / ROWS, rr = idx % ROWS;
             const size_t o = seq_base + (size_t)(tile * kTile + tt) * tok_stride + row0 + rr;
             y[o] = from_f32<T>(yt[tt * ROWS + rr]);
+            if constexpr (SAVE) reinterpret_cast<T *>(save.state_replacement)[o] = from_f32<T>(sat[tt * ROWS + rr]);
         }
     }
 
@@ -216,10 +242,10 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
 
 // Any head size N <= 128: thread i owns state row i, kept in shared memory with
 // a padded row pitch; the six token vectors are staged per token.
-template <typename T>
+template <typename T, bool SAVE = false>
 __global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *s0,
                                         T *__restrict__ y, float *s_out, int Tlen,
-                                        int H, int N) {
+                                        int H, int N, SavePtrs save = SavePtrs{}) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int pitch = N + 1;
     float *S = reinterpret_cast<float *>(smem_raw);  // [N][N+1]
@@ -256,6 +282,14 @@ __global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *s0,
                 acc = fmaf(s, vec[VR * N + j], acc);
             }
             y[o + tid] = from_f32<T>(acc);
+            if constexpr (SAVE) {
+                reinterpret_cast<T *>(save.state_replacement)[o + tid] = from_f32<T>(sa);
+                if ((t + 1) % save.chunk_len == 0) {
+                    float *dst = save.snapshots +
+                                 (((size_t)bh * (Tlen / save.chunk_len) + t / save.chunk_len) * N + tid) * N;
+                    for (int j = 0; j < N; ++j) dst[j] = Si[j];
+                }
+            }
         }
         __syncthreads();
     }
@@ -269,13 +303,13 @@ __global__ void wkv7_seq_generic_kernel(SeqPtrs ptrs, const float *s0,
 template <typename T, int ROWS>
 int launch_seq64(const Wkv7Args &p, cudaStream_t stream, const int *flags = nullptr) {
     SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
-    const size_t smem = sizeof(float) * (2 * kTile * 6 * kN + 2 * kTile * ROWS);
-    auto kern = wkv7_seq64_kernel<T, ROWS>;
+    const size_t smem = sizeof(float) * (2 * kTile * 6 * kN + 4 * kTile * ROWS);
+    auto kern = wkv7_seq64_kernel<T, ROWS, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const unsigned grid = (unsigned)(p.B * p.H * (kN / ROWS));
     kern<<<grid, ROWS * 4, smem, stream>>>(ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out,
-                                           (int)p.T, (int)p.H, flags);
+                                           (int)p.T, (int)p.H, flags, SavePtrs{});
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -300,17 +334,50 @@ int launch_seq(const Wkv7Args &p, cudaStream_t stream) {
     SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
     const int N = (int)p.N;
     const size_t smem = sizeof(float) * ((size_t)N * (N + 1) + 6 * N);
-    auto kern = wkv7_seq_generic_kernel<T>;
+    auto kern = wkv7_seq_generic_kernel<T, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int threads = ((N + 31) / 32) * 32;
     kern<<<(unsigned)(p.B * p.H), threads, smem, stream>>>(ptrs, p.s0, reinterpret_cast<T *>(p.y),
-                                                          p.s_out, (int)p.T, (int)p.H, N);
+                                                          p.s_out, (int)p.T, (int)p.H, N, SavePtrs{});
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+// Training forward: the scan above, also writing the tensors the backward pass needs.
+template <typename T>
+int launch_seq_saved(const Wkv7Args &p, float *snapshots, void *state_replacement, int chunk_len,
+                     cudaStream_t stream) {
+    SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
+    SavePtrs save{snapshots, state_replacement, chunk_len};
+    if (p.N == kN) {
+        constexpr int ROWS = 16;   // four CTAs per chain: rows of S never interact
+        const size_t smem = sizeof(float) * (2 * kTile * 6 * kN + 4 * kTile * ROWS);
+        auto kern = wkv7_seq64_kernel<T, ROWS, true>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<(unsigned)(p.B * p.H * (kN / ROWS)), ROWS * 4, smem, stream>>>(
+            ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out, (int)p.T, (int)p.H, nullptr, save);
+    } else {
+        const int N = (int)p.N;
+        const size_t smem = sizeof(float) * ((size_t)N * (N + 1) + 6 * N);
+        auto kern = wkv7_seq_generic_kernel<T, true>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<(unsigned)(p.B * p.H), ((N + 31) / 32) * 32, smem, stream>>>(
+            ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out, (int)p.T, (int)p.H, N, save);
+    }
     count_launch();
     return (int)cudaGetLastError();
 }
 
 }  // namespace
+
+int launch_wkv7_forward_saved(const Wkv7Args &p, float *snapshots, void *state_replacement, int chunk_len,
+                              cudaStream_t stream) {
+    return p.bf16 ? launch_seq_saved<__nv_bfloat16>(p, snapshots, state_replacement, chunk_len, stream)
+                  : launch_seq_saved<float>(p, snapshots, state_replacement, chunk_len, stream);
+}
 
 // N == 64 only: recomputes the chains with flags[b*H+h] != 0, 16 value rows per CTA.
 int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStream_t stream) {

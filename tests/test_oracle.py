@@ -193,3 +193,40 @@ def test_channel_mixer_matches_torch_restatement(oracle, workloads, shape):
     ref = tr.channel_mixer_reference(x.double(), ks.double(), kw.double(), vw.double())
     got = oracle.channel_mixer(x.numpy(), ks.numpy(), kw.numpy(), vw.numpy())
     np.testing.assert_allclose(got, ref.numpy(), rtol=1e-12, atol=1e-12)
+
+
+@pytest.mark.parametrize("shape,with_state", [((1, 16, 1, 4), False), ((2, 32, 2, 8), True), ((1, 48, 1, 16), True)])
+def test_wkv7_backward_matches_torch_autograd(oracle, workloads, shape, with_state):
+    """wkv7/mod.rs:294-328 differentiates sum(y) through the tensor-op reference with Burn's autodiff;
+    here the C reverse pass against torch autograd through the fp64 torch restatement, with a random
+    output gradient and a gradient on the final state as well."""
+    inp = workloads.wkv7_inputs(*shape, seed=21, state="normal" if with_state else None)
+    B, T, H, N = shape
+    g = torch.Generator().manual_seed(5)
+    dy = torch.randn(B, T, H, N, generator=g, dtype=torch.float64)
+    ds = torch.randn(B, H, N, N, generator=g, dtype=torch.float64)
+    leaves = {n: inp[n].double().requires_grad_(True) for n in "rwkvab"}
+    s0 = inp["s0"].double().requires_grad_(True) if with_state else torch.zeros(B, H, N, N, dtype=torch.float64)
+    y, s_out = tr.wkv7_reference_with_state(*[leaves[n] for n in "rwkvab"], s0)
+    ((y * dy).sum() + (s_out * ds).sum()).backward()
+    f = {n: inp[n].numpy() for n in "rwkvab"}
+    got = oracle.wkv7_backward(*[f[n] for n in "rwkvab"], dy.numpy(), s0=inp["s0"].numpy() if with_state else None,
+                               ds_out=ds.numpy())
+    for n in "rwkvab":
+        np.testing.assert_allclose(got[n], leaves[n].grad.numpy(), rtol=1e-9, atol=1e-9, err_msg=n)
+    if with_state:
+        np.testing.assert_allclose(got["s0"], s0.grad.numpy(), rtol=1e-9, atol=1e-9)
+
+
+def test_wkv7_train_forward_saves(oracle, workloads):
+    """snapshots hold the state after tokens 15, 31, ...; state_replacement is S_{t-1} a_t."""
+    inp = workloads.wkv7_inputs(2, 32, 2, 8, seed=22, state="normal")
+    f = {n: inp[n].numpy() for n in inp}
+    y, s_out, snaps, sa = oracle.wkv7_train(*[f[n] for n in "rwkvab"], s0=f["s0"], chunk_len=16)
+    y_ref, s_ref = oracle.wkv7(*[f[n] for n in "rwkvab"], f["s0"], precision="f64")
+    np.testing.assert_allclose(y, y_ref, rtol=1e-13, atol=1e-13)
+    np.testing.assert_allclose(snaps[:, :, 1], s_ref, rtol=1e-13, atol=1e-13)
+    _, s_half = oracle.wkv7(*[f[n][:, :16] for n in "rwkvab"], f["s0"], precision="f64")
+    np.testing.assert_allclose(snaps[:, :, 0], s_half, rtol=1e-13, atol=1e-13)
+    np.testing.assert_allclose(sa[:, 0], np.einsum("bhij,bhj->bhi", f["s0"].astype(np.float64),
+                                                   f["a"][:, 0].astype(np.float64)), rtol=1e-13, atol=1e-13)
