@@ -368,21 +368,38 @@ def main():
         del ep, wp, gr
 
     # ---- fused LM-head cross entropy at the configuration-2 shape (tensor-core-bound) -----
+    # One GPU: the whole vocabulary.  N GPUs: the vocabulary is sharded over the ranks (strong
+    # scaling of one LM head), every rank computes the partial triples of its shard, the triples
+    # are all-gathered over NCCL and combined on every rank.
     lm_head = None
-    if not args.no_lm_head and rank == 0:
+    if not args.no_lm_head:
+        from rwkv_rs_stable_b200 import dist as rdist
         Rl, Cl, Vl = (8192, 2048, 16384) if args.small else (16 * 8192, 2048, 65536)
-        xl, wl, tl = workloads.lm_head_inputs(Rl, Cl, Vl, seed=2, device=dev)
+        xl, wl, tl = workloads.lm_head_inputs(Rl, Cl, Vl, seed=2, device=dev)   # same seed on every rank
+        lo, hi = rdist.vocab_shard(Vl, rank, world)
+        w_shard = wl[lo:hi].contiguous()
+        if world > 1:
+            del wl
+
+        def lm_step():
+            if world > 1:
+                return rdist.lm_head_ce_sharded(pkg, xl, w_shard, tl, lo)
+            return pkg.lm_head_ce(xl, w_shard, tl)
+
         for _ in range(2):
-            pkg.lm_head_ce(xl, wl, tl)
-        torch.cuda.synchronize()
+            lm_step()
+        sync_all()
         l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         n_lm = 3
         l0.record()
         for _ in range(n_lm):
-            lse, loss = pkg.lm_head_ce(xl, wl, tl)
+            lse, loss = lm_step()
         l1.record()
-        torch.cuda.synchronize()
-        lms = l0.elapsed_time(l1) / n_lm
+        sync_all()
+        tl_ms = torch.tensor([l0.elapsed_time(l1) / n_lm], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tl_ms, op=dist.ReduceOp.MAX)
+        lms = float(tl_ms.item())
         flops = 2.0 * Rl * Cl * Vl
         tf_peak = 1653.6
         try:
@@ -391,10 +408,12 @@ def main():
         except Exception:
             pass
         lm_head = {"workload": f"R={Rl} C={Cl} V={Vl} bf16, logits never materialised (configuration 2)",
-                   "ms": lms, "tflops": flops / (lms * 1e-3) / 1e12, "peak_tflops": tf_peak,
-                   "frac_of_bf16_peak": flops / (lms * 1e-3) / 1e12 / tf_peak,
+                   "sharding": "none" if world == 1 else f"vocabulary over {world} GPUs, all-gather of [R,3] partials + combine",
+                   "scaling": "strong",
+                   "ms": lms, "tflops": flops / (lms * 1e-3) / 1e12, "peak_tflops": tf_peak * world,
+                   "frac_of_bf16_peak": flops / (lms * 1e-3) / 1e12 / (tf_peak * world),
                    "mean_loss": float(loss.mean().item())}
-        del xl, wl, tl
+        del xl, w_shard, tl
 
     # ---- training forward (with saved tensors) and backward at configuration 1 ------------
     train = None
