@@ -196,6 +196,7 @@ def main():
     ap.add_argument("--no-streaming", action="store_true")
     ap.add_argument("--no-channel-mixer", action="store_true")
     ap.add_argument("--no-train", action="store_true")
+    ap.add_argument("--no-prefill-other", action="store_true")
     ap.add_argument("--no-lm-head", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
@@ -415,6 +416,36 @@ def main():
                    "mean_loss": float(loss.mean().item())}
         del xl, w_shard, tl
 
+    # ---- the same prefill kernel at the other configurations' per-GPU shapes --------------
+    prefill_other = None
+    if not args.no_prefill_other and rank == 0 and not args.small:
+        peak_gbs, _ = measured_peaks()
+        prefill_other = {}
+        for name, (Bo, To, Ho) in (("cfg2_layer_1gpu", (16, 8192, 32)), ("cfg4_layer_shard_of_8", (4, 65536, 8))):
+            oin = workloads.wkv7_inputs(Bo, To, Ho, 64, seed=11, dtype=torch.bfloat16, device=dev)
+            oseq = pkg.Wkv7PretrainForwardInputs(*[oin[n] for n in "rwkvab"])
+            os0 = torch.zeros(Bo, Ho, 64, 64, device=dev)
+            oy, oso = torch.empty_like(oin["r"]), torch.empty_like(os0)
+            ows_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bo, To, Ho, 64, pkg.BF16))
+            ows = torch.empty(max(ows_bytes, 1), dtype=torch.uint8, device=dev)
+            ocall = pkg.Wkv7StatepassCall(os0, oseq, oy, oso, ows)
+            for _ in range(2):
+                ocall()
+            torch.cuda.synchronize()
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record()
+            for _ in range(3):
+                ocall()
+            o1.record()
+            torch.cuda.synchronize()
+            oms = o0.elapsed_time(o1) / 3
+            obytes = Bo * To * Ho * BYTES_PER_TOKEN_HEAD + Bo * Ho * STATE_BYTES
+            prefill_other[name] = {"shape": f"B={Bo} T={To} H={Ho} N=64 bf16 ({Bo * Ho} chains)", "ms": oms,
+                                   "tokens_per_s": Bo * To / (oms * 1e-3), "gb_per_s": obytes / (oms * 1e-3) / 1e9,
+                                   "frac_of_hbm_peak": obytes / (oms * 1e-3) / 1e9 / peak_gbs,
+                                   "algorithmic_bytes": obytes}
+            del oin, oseq, os0, oy, oso, ows, ocall
+
     # ---- training forward (with saved tensors) and backward at configuration 1 ------------
     train = None
     if not args.no_train and rank == 0:
@@ -511,6 +542,7 @@ def main():
         "lm_head_ce": lm_head,
         "channel_mixer": channel_mixer,
         "train": train,
+        "prefill_other_configs": prefill_other,
     }
     if not args.no_cpu_baseline:
         oracle = entry.load_oracle()
