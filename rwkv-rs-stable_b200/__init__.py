@@ -394,7 +394,12 @@ class Wkv7HostStatepass:
             seq = Wkv7PretrainForwardInputs(*six, chunk_len=chunk_len)
             self._sets.append((six, s_in, y, s_out, Wkv7StatepassCall(s_in, seq, y, s_out, ws)))
 
-    def __call__(self) -> None:
+    def __call__(self, join: bool = True) -> None:
+        """Enqueues one pass.  With ``join=False`` the caller's stream is not made to wait for the
+        pass: a caller that issues passes back to back (a server draining a queue) lets the
+        copy-in of the next pass overlap the tail of this one, and calls :meth:`join` (or a last
+        pass with ``join=True``) before it reads the host outputs.  Passes always execute in
+        issue order slice by slice, so the host buffers are never written out of order."""
         host_six, host_s_in, host_y, host_s_out = self._host
         cur = torch.cuda.current_stream(self._device)
         start = cur.record_event()
@@ -412,6 +417,12 @@ class Wkv7HostStatepass:
                 call()
                 host_y[b0:b1].copy_(y, non_blocking=True)
                 host_s_out[b0:b1].copy_(s_out, non_blocking=True)
+        if join:
+            self.join()
+
+    def join(self) -> None:
+        """Makes the caller's current stream wait for every pass issued so far."""
+        cur = torch.cuda.current_stream(self._device)
         for st in self._streams:
             cur.wait_event(st.record_event())
 

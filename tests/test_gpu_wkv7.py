@@ -232,8 +232,8 @@ def test_host_pipeline_equals_single_call(pkg, workloads, cuda):
     for slices, n_streams in ((4, 3), (2, 2), (1, 1)):
         y_host.zero_(); s_host.zero_()
         run = pkg.Wkv7HostStatepass(host_six, s_in, y_host, s_host, device=cuda, slices=slices, n_streams=n_streams)
-        run()
-        run()   # staging buffers are reused: a second call must give the same result
+        run(join=False)
+        run()   # staging buffers are reused, and this pass may overlap the tail of the first
         torch.cuda.current_stream(cuda).synchronize()
         assert torch.equal(y_host, full.output.cpu())
         assert torch.equal(s_host, full.next_state.cpu())
