@@ -58,8 +58,11 @@ __device__ __forceinline__ float quad_sum(float x) {
 
 enum { VR = 0, VD, VK, VV, VA, VB, VSA, VDY, VEW, kVecs };   // VD = decay, VEW = exp(w)
 enum { OR_ = 0, OW, OK_, OB, OV, kOuts };
+#ifndef RWKV7_BWD_ROWS
+#define RWKV7_BWD_ROWS 2
+#endif
 #ifndef RWKV7_BWD_COLS
-#define RWKV7_BWD_COLS 16
+#define RWKV7_BWD_COLS 4
 #endif
 constexpr int kGroup = 4;         // tokens between kept states
 constexpr int kMaxChunk = 16;     // chunk_len supported by the staging buffers
@@ -217,65 +220,78 @@ __global__ void wkv7_backward_kernel(Wkv7BackwardArgs p) {
             p.initial_state_grad[state_base + idx] = dS[(idx / N) * P + idx % N];
 }
 
-// N == 64: the same algorithm with every work matrix in registers.  Thread (row, q) owns the
-// 16 contiguous columns 16q .. 16q+15 of row `row` of S^T, dS and dS^T (no thread ever reads
-// another thread's matrix elements), so only the per-token vectors, dsa and the output staging
-// go through shared memory, read as 128-bit vectors.  The kept states of the chunk replay are
-// spilled to shared memory in a thread-private layout.
-template <typename T, int E>
-__global__ void __launch_bounds__(64 * (64 / E), 1) wkv7_backward64_kernel(Wkv7BackwardArgs p) {
-    constexpr int N = 64, TPR = N / E, THREADS = N * TPR;   // threads per row, per CTA
+// N == 64: the same algorithm with every work matrix in registers.  A thread owns an R x E
+// block (rows row0 .., columns c0 ..) of S^T, dS and dS^T; no thread ever reads another thread's
+// matrix elements, so only the per-token vectors, dsa and the output staging go through shared
+// memory, read as 128-bit vectors, and a row sum is finished by shuffles among the 64/E threads
+// of the row.  The kept states of the chunk replay are spilled to shared memory in a
+// thread-private layout.  Measured on B=8, T=4096, H=12: 1 x 16 per thread (256 threads) 9.6 ms,
+// bound by shared-memory bandwidth (every thread re-reads 16 columns of eight vectors per token);
+// 2 x 8 7.3 ms; 4 x 4 7.1 ms; 2 x 4 (512 threads) 6.9 ms, the default.
+template <typename T, int R, int E>
+__global__ void __launch_bounds__(64 * 64 / (R * E), 1) wkv7_backward64_kernel(Wkv7BackwardArgs p) {
+    static_assert(E % 4 == 0 && 64 % R == 0 && 64 % E == 0, "R rows x E columns of every work matrix per thread");
+    constexpr int N = 64, TPR = N / E, THREADS = N * N / (R * E), Q4 = R * E / 4;   // threads per row group
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float *vec = reinterpret_cast<float *>(smem_raw);        // [chunk_len][kVecs][N]
-    float *dsa = vec + (size_t)kMaxChunk * kVecs * N;        // [N]
-    float *outs = dsa + N;                                   // [kOuts][N]
-    float4 *keep = reinterpret_cast<float4 *>(outs + kOuts * N);   // [kStates - 1][E / 4][THREADS]: thread-private states
+    float *dsa2 = vec + (size_t)kMaxChunk * kVecs * N;       // [2][N], by token parity
+    float *outs2 = dsa2 + 2 * N;                             // [2][kOuts][N], by token parity
+    float4 *keep = reinterpret_cast<float4 *>(outs2 + 2 * kOuts * N);   // [kStates - 1][Q4][THREADS]: thread-private states
 
     const int bh = blockIdx.x, bi = bh / (int)p.H, h = bh % (int)p.H;
-    const int tid = threadIdx.x, row = tid / TPR, q = tid % TPR, c0 = q * E;
+    const int tid = threadIdx.x, row0 = (tid / TPR) * R, q = tid % TPR, c0 = q * E;
     const int Tlen = (int)p.T, chunk_len = (int)p.chunk_len, nchunks = Tlen / chunk_len;
     const size_t tok_stride = (size_t)p.H * N;
     const size_t seq_base = ((size_t)bi * Tlen * p.H + h) * N;
     const size_t state_base = (size_t)bh * N * N;
 
-    float dS[E], dSt[E];   // dS[row][c0 + e], dS^T[row][c0 + e] = dS[c0 + e][row]
+    // dS[row0 + rho][c0 + e] and dS^T[row0 + rho][c0 + e] = dS[c0 + e][row0 + rho]
+    float dS[R][E], dSt[R][E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-        dS[e] = p.next_state_grad ? p.next_state_grad[state_base + (size_t)row * N + c0 + e] : 0.f;
-        dSt[e] = p.next_state_grad ? p.next_state_grad[state_base + (size_t)(c0 + e) * N + row] : 0.f;
-    }
-    auto keep_store = [&](int slot, const float (&x)[E]) {
+    for (int rho = 0; rho < R; ++rho)
 #pragma unroll
-        for (int e4 = 0; e4 < E / 4; ++e4)
-            keep[((size_t)slot * (E / 4) + e4) * THREADS + tid] = make_float4(x[4 * e4], x[4 * e4 + 1], x[4 * e4 + 2], x[4 * e4 + 3]);
+        for (int e = 0; e < E; ++e) {
+            dS[rho][e] = p.next_state_grad ? p.next_state_grad[state_base + (size_t)(row0 + rho) * N + c0 + e] : 0.f;
+            dSt[rho][e] = p.next_state_grad ? p.next_state_grad[state_base + (size_t)(c0 + e) * N + row0 + rho] : 0.f;
+        }
+    auto keep_store = [&](int slot, const float (&x)[R][E]) {
+        const float *f = &x[0][0];
+#pragma unroll
+        for (int e4 = 0; e4 < Q4; ++e4)
+            keep[((size_t)slot * Q4 + e4) * THREADS + tid] = make_float4(f[4 * e4], f[4 * e4 + 1], f[4 * e4 + 2], f[4 * e4 + 3]);
     };
-    auto keep_load = [&](int slot, float (&x)[E]) {
+    auto keep_load = [&](int slot, float (&x)[R][E]) {
+        float *f = &x[0][0];
+#pragma unroll
+        for (int e4 = 0; e4 < Q4; ++e4) {
+            const float4 v = keep[((size_t)slot * Q4 + e4) * THREADS + tid];
+            f[4 * e4] = v.x; f[4 * e4 + 1] = v.y; f[4 * e4 + 2] = v.z; f[4 * e4 + 3] = v.w;
+        }
+    };
+    auto ldv = [&](const float *base, float (&x)[E]) {   // this thread's E columns of one staged vector
 #pragma unroll
         for (int e4 = 0; e4 < E / 4; ++e4) {
-            const float4 v = keep[((size_t)slot * (E / 4) + e4) * THREADS + tid];
+            const float4 v = *reinterpret_cast<const float4 *>(base + c0 + 4 * e4);
             x[4 * e4] = v.x; x[4 * e4 + 1] = v.y; x[4 * e4 + 2] = v.z; x[4 * e4 + 3] = v.w;
         }
     };
-    auto ldv = [&](const float *v_t, int which, float (&x)[E]) {   // 16 columns of one staged vector
-#pragma unroll
-        for (int e4 = 0; e4 < E / 4; ++e4) {
-            const float4 v = *reinterpret_cast<const float4 *>(v_t + which * N + c0 + 4 * e4);
-            x[4 * e4] = v.x; x[4 * e4 + 1] = v.y; x[4 * e4 + 2] = v.z; x[4 * e4 + 3] = v.w;
-        }
-    };
-    // One forward step on this thread's elements of S^T: x[c] = x[c] d[row] + b[row] sa[c] + k[row] v[c].
-    auto replay = [&](float (&x)[E], const float *v_t) {
-        const float d_j = v_t[VD * N + row], b_j = v_t[VB * N + row], k_j = v_t[VK * N + row];
+    // One forward step on this thread's elements of S^T: x[j][c] = x[j][c] d[j] + b[j] sa[c] + k[j] v[c].
+    auto replay = [&](float (&x)[R][E], const float *v_t) {
         float sa[E], vv[E];
-        ldv(v_t, VSA, sa);
-        ldv(v_t, VV, vv);
+        ldv(v_t + VSA * N, sa);
+        ldv(v_t + VV * N, vv);
 #pragma unroll
-        for (int e = 0; e < E; ++e) x[e] = fmaf(x[e], d_j, fmaf(b_j, sa[e], k_j * vv[e]));
+        for (int rho = 0; rho < R; ++rho) {
+            const float d_j = v_t[VD * N + row0 + rho], b_j = v_t[VB * N + row0 + rho], k_j = v_t[VK * N + row0 + rho];
+#pragma unroll
+            for (int e = 0; e < E; ++e) x[rho][e] = fmaf(x[rho][e], d_j, fmaf(b_j, sa[e], k_j * vv[e]));
+        }
     };
 
     const int ngroups = chunk_len / kGroup;
     for (int chunk = nchunks - 1; chunk >= 0; --chunk) {
         const int t0 = chunk * chunk_len;
+        __syncthreads();   // the previous chunk's vectors are no longer read
         // Stage the chunk's vectors: 16-byte loads, all requested before the first is used.
         {
             constexpr int EPV = 16 / (int)sizeof(T);            // elements per 16-byte vector
@@ -327,13 +343,15 @@ __global__ void __launch_bounds__(64 * (64 / E), 1) wkv7_backward64_kernel(Wkv7B
                 }
             }
         }
-        // state at the start of the chunk, transposed: S^T[row][c] = S[c][row]
-        float st_cur[E];
+        // state at the start of the chunk, transposed: S^T[j][c] = S[c][j]
+        float st_cur[R][E];
         {
             const float *start = chunk > 0 ? p.snapshots + ((size_t)bh * nchunks + chunk - 1) * N * N
                                            : (p.initial_state ? p.initial_state + state_base : nullptr);
 #pragma unroll
-            for (int e = 0; e < E; ++e) st_cur[e] = start ? start[(size_t)(c0 + e) * N + row] : 0.f;
+            for (int rho = 0; rho < R; ++rho)
+#pragma unroll
+                for (int e = 0; e < E; ++e) st_cur[rho][e] = start ? start[(size_t)(c0 + e) * N + row0 + rho] : 0.f;
         }
         __syncthreads();
         // replay the chunk forwards; slot g keeps the state before token kGroup * g
@@ -341,14 +359,16 @@ __global__ void __launch_bounds__(64 * (64 / E), 1) wkv7_backward64_kernel(Wkv7B
             if (tt % kGroup == 0) keep_store(tt / kGroup, st_cur);
             replay(st_cur, vec + (size_t)tt * kVecs * N);
         }
-        float s_new[E];   // state after the token being differentiated
+        float s_new[R][E];   // state after the token being differentiated
 #pragma unroll
-        for (int e = 0; e < E; ++e) s_new[e] = st_cur[e];
+        for (int rho = 0; rho < R; ++rho)
+#pragma unroll
+            for (int e = 0; e < E; ++e) s_new[rho][e] = st_cur[rho][e];
 
         for (int g = ngroups - 1; g >= 0; --g) {
-            // states before tokens kGroup*g + 1 .. kGroup*g + kGroup - 1 go to slots ngroups + u
+            // states before tokens kGroup*g + 1 .. kGroup*g + kGroup - 1 go to slots kMaxChunk/kGroup + u
             {
-                float x[E];
+                float x[R][E];
                 keep_load(g, x);
                 for (int u = 0; u + 1 < kGroup; ++u) {
                     replay(x, vec + (size_t)(g * kGroup + u) * kVecs * N);
@@ -359,41 +379,47 @@ __global__ void __launch_bounds__(64 * (64 / E), 1) wkv7_backward64_kernel(Wkv7B
                 const int tt = g * kGroup + u;
                 const size_t o = seq_base + (size_t)(t0 + tt) * tok_stride;
                 const float *v_t = vec + (size_t)tt * kVecs * N;
-                float s_old[E];   // state before the token
+                // dsa and the output staging alternate between two buffers, so that one barrier
+                // per token is enough: a buffer is rewritten two tokens later, after the barrier
+                // of the token in between, which every thread reaches only after reading it.
+                float *dsa = dsa2 + (tt & 1) * N, *outs = outs2 + (tt & 1) * kOuts * N;
+                float s_old[R][E];   // state before the token
                 keep_load(u == 0 ? g : kMaxChunk / kGroup + u - 1, s_old);
-                const float r_j = v_t[VR * N + row], dy_i = v_t[VDY * N + row];
-                float dyv[E], x[E];
-                ldv(v_t, VDY, dyv);
-                float dr = 0.f, dd = 0.f, dk = 0.f, db = 0.f, dv = 0.f, dsa_i = 0.f;
-                ldv(v_t, VR, x);
+                float dyv[E], rv[E], vv[E], sav[E], kv[E], bv[E];
+                ldv(v_t + VDY * N, dyv);
+                ldv(v_t + VR * N, rv);
+                ldv(v_t + VV * N, vv);
+                ldv(v_t + VSA * N, sav);
+                ldv(v_t + VK * N, kv);
+                ldv(v_t + VB * N, bv);
+                float dsa_i[R];
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    dr = fmaf(s_new[e], dyv[e], dr);
-                    dS[e] = fmaf(dy_i, x[e], dS[e]);
-                    dSt[e] = fmaf(r_j, dyv[e], dSt[e]);
-                    dd = fmaf(dSt[e], s_old[e], dd);
-                }
-                ldv(v_t, VV, x);
+                for (int rho = 0; rho < R; ++rho) {
+                    const int row = row0 + rho;
+                    const float r_j = v_t[VR * N + row], dy_i = v_t[VDY * N + row];
+                    float dr = 0.f, dd = 0.f, dk = 0.f, db = 0.f, dv = 0.f, ds = 0.f;
 #pragma unroll
-                for (int e = 0; e < E; ++e) dk = fmaf(dSt[e], x[e], dk);
-                ldv(v_t, VSA, x);
-#pragma unroll
-                for (int e = 0; e < E; ++e) db = fmaf(dSt[e], x[e], db);
-                ldv(v_t, VK, x);
-#pragma unroll
-                for (int e = 0; e < E; ++e) dv = fmaf(dS[e], x[e], dv);
-                ldv(v_t, VB, x);
-#pragma unroll
-                for (int e = 0; e < E; ++e) dsa_i = fmaf(dS[e], x[e], dsa_i);
-                dr = row_sum<TPR>(dr); dd = row_sum<TPR>(dd); dk = row_sum<TPR>(dk); db = row_sum<TPR>(db); dv = row_sum<TPR>(dv);
-                dsa_i = row_sum<TPR>(dsa_i);
-                if (q == 0) {
-                    outs[OR_ * N + row] = dr;
-                    outs[OW * N + row] = dd * (-v_t[VEW * N + row] * v_t[VD * N + row]);
-                    outs[OK_ * N + row] = dk;
-                    outs[OB * N + row] = db;
-                    outs[OV * N + row] = dv;
-                    dsa[row] = dsa_i;
+                    for (int e = 0; e < E; ++e) {
+                        dr = fmaf(s_new[rho][e], dyv[e], dr);
+                        dS[rho][e] = fmaf(dy_i, rv[e], dS[rho][e]);
+                        dSt[rho][e] = fmaf(r_j, dyv[e], dSt[rho][e]);
+                        dd = fmaf(dSt[rho][e], s_old[rho][e], dd);
+                        dk = fmaf(dSt[rho][e], vv[e], dk);
+                        db = fmaf(dSt[rho][e], sav[e], db);
+                        dv = fmaf(dS[rho][e], kv[e], dv);
+                        ds = fmaf(dS[rho][e], bv[e], ds);
+                    }
+                    dr = row_sum<TPR>(dr); dd = row_sum<TPR>(dd); dk = row_sum<TPR>(dk); db = row_sum<TPR>(db);
+                    dv = row_sum<TPR>(dv); ds = row_sum<TPR>(ds);
+                    dsa_i[rho] = ds;
+                    if (q == 0) {
+                        outs[OR_ * N + row] = dr;
+                        outs[OW * N + row] = dd * (-v_t[VEW * N + row] * v_t[VD * N + row]);
+                        outs[OK_ * N + row] = dk;
+                        outs[OB * N + row] = db;
+                        outs[OV * N + row] = dv;
+                        dsa[row] = ds;
+                    }
                 }
                 __syncthreads();
                 if (tid < N) {
@@ -403,34 +429,35 @@ __global__ void __launch_bounds__(64 * (64 / E), 1) wkv7_backward64_kernel(Wkv7B
                     st<T>(p.replacement_grad, o + tid, outs[OB * N + tid]);
                     st<T>(p.value_grad, o + tid, outs[OV * N + tid]);
                 }
-                const float d_j = v_t[VD * N + row], a_j = v_t[VA * N + row];
-                float dsav[E], av[E];
+                float dsav[E], dv_[E], av[E];
+                ldv(dsa, dsav);
+                ldv(v_t + VD * N, dv_);
+                ldv(v_t + VA * N, av);
 #pragma unroll
-                for (int e4 = 0; e4 < E / 4; ++e4) {
-                    const float4 v = *reinterpret_cast<const float4 *>(dsa + c0 + 4 * e4);
-                    dsav[4 * e4] = v.x; dsav[4 * e4 + 1] = v.y; dsav[4 * e4 + 2] = v.z; dsav[4 * e4 + 3] = v.w;
-                }
-                ldv(v_t, VD, x);
-                ldv(v_t, VA, av);
-                float da = 0.f;
+                for (int rho = 0; rho < R; ++rho) {
+                    const int row = row0 + rho;
+                    const float d_j = v_t[VD * N + row], a_j = v_t[VA * N + row];
+                    float da = 0.f;
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    da = fmaf(s_old[e], dsav[e], da);
-                    dS[e] = fmaf(dS[e], x[e], dsa_i * av[e]);
-                    dSt[e] = fmaf(dSt[e], d_j, a_j * dsav[e]);
-                    s_new[e] = s_old[e];
+                    for (int e = 0; e < E; ++e) {
+                        da = fmaf(s_old[rho][e], dsav[e], da);
+                        dS[rho][e] = fmaf(dS[rho][e], dv_[e], dsa_i[rho] * av[e]);
+                        dSt[rho][e] = fmaf(dSt[rho][e], d_j, a_j * dsav[e]);
+                        s_new[rho][e] = s_old[rho][e];
+                    }
+                    da = row_sum<TPR>(da);
+                    if (q == 0) st<T>(p.removal_key_normalized_grad, o + row, da);
                 }
-                da = row_sum<TPR>(da);
-                if (q == 0) st<T>(p.removal_key_normalized_grad, o + row, da);
-                __syncthreads();   // dsa and outs are rewritten by the next token
             }
         }
     }
     if (p.initial_state_grad) {
 #pragma unroll
-        for (int e4 = 0; e4 < E / 4; ++e4)
-            *reinterpret_cast<float4 *>(p.initial_state_grad + state_base + (size_t)row * N + c0 + 4 * e4) =
-                make_float4(dS[4 * e4], dS[4 * e4 + 1], dS[4 * e4 + 2], dS[4 * e4 + 3]);
+        for (int rho = 0; rho < R; ++rho)
+#pragma unroll
+            for (int e4 = 0; e4 < E / 4; ++e4)
+                *reinterpret_cast<float4 *>(p.initial_state_grad + state_base + (size_t)(row0 + rho) * N + c0 + 4 * e4) =
+                    make_float4(dS[rho][4 * e4], dS[rho][4 * e4 + 1], dS[rho][4 * e4 + 2], dS[rho][4 * e4 + 3]);
     }
 }
 
@@ -440,18 +467,18 @@ int launch_wkv7_backward(const Wkv7BackwardArgs &p, cudaStream_t stream) {
     if (p.B * p.H == 0 || p.T == 0) return 0;
     const int N = (int)p.N;
     if (N == 64) {
-        constexpr int E = RWKV7_BWD_COLS;   // columns per thread: 512 threads at 8, 256 at 16
-        constexpr int THREADS = 64 * (64 / E);
-        const size_t smem64 = sizeof(float) * ((size_t)(kMaxChunk * kVecs + 1 + kOuts) * 64 + (size_t)(kStates - 1) * E * THREADS);
+        constexpr int R = RWKV7_BWD_ROWS, E = RWKV7_BWD_COLS;   // rows x columns of every work matrix per thread
+        constexpr int THREADS = 64 * 64 / (R * E);
+        const size_t smem64 = sizeof(float) * ((size_t)(kMaxChunk * kVecs + 2 + 2 * kOuts) * 64 + (size_t)(kStates - 1) * 64 * 64);
         cudaError_t e64;
         if (p.bf16) {
-            e64 = cudaFuncSetAttribute(wkv7_backward64_kernel<__nv_bfloat16, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64);
+            e64 = cudaFuncSetAttribute(wkv7_backward64_kernel<__nv_bfloat16, R, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64);
             if (e64 != cudaSuccess) return (int)e64;
-            wkv7_backward64_kernel<__nv_bfloat16, E><<<(unsigned)(p.B * p.H), THREADS, smem64, stream>>>(p);
+            wkv7_backward64_kernel<__nv_bfloat16, R, E><<<(unsigned)(p.B * p.H), THREADS, smem64, stream>>>(p);
         } else {
-            e64 = cudaFuncSetAttribute(wkv7_backward64_kernel<float, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64);
+            e64 = cudaFuncSetAttribute(wkv7_backward64_kernel<float, R, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem64);
             if (e64 != cudaSuccess) return (int)e64;
-            wkv7_backward64_kernel<float, E><<<(unsigned)(p.B * p.H), THREADS, smem64, stream>>>(p);
+            wkv7_backward64_kernel<float, R, E><<<(unsigned)(p.B * p.H), THREADS, smem64, stream>>>(p);
         }
         count_launch();
         return (int)cudaGetLastError();
