@@ -4,12 +4,11 @@
 // Semantics: crates/rwkv-nn/src/kernels/train/time_mixer/wkv7/mod.rs:179-242 of
 // the reference at T == 1 (its custom kernel rejects T % 16 != 0, wkv7/io.rs:198-201).
 //
-// One CTA of 128 threads per (b,h): two threads share a state row, each holding
-// 32 columns as eight 128-bit pieces interleaved with its partner, so a warp's
-// load or store touches sixteen full 32-byte sectors.  The state loads are in
-// flight while the six token vectors are converted and staged in shared memory;
-// the two row reductions (S a and S r) are 32 FMAs and one shuffle each.  State
-// traffic uses streaming loads and stores since nothing is reused.
+// One CTA of 128 threads per (b,h); a thread holds a block of R rows x 32/R columns of the
+// state in registers, so a warp's loads and stores touch full 32-byte sectors of R rows.  The
+// state loads are in flight while the six token vectors are converted and staged in shared
+// memory; the two row reductions (S a and S r) end in shuffles among the threads of a row.
+// State traffic uses streaming loads and stores since nothing is reused.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -41,24 +40,38 @@ __device__ __forceinline__ void st_out<float>(float *p, float x) { *p = x; }
 template <>
 __device__ __forceinline__ void st_out<__nv_bfloat16>(__nv_bfloat16 *p, float x) { *p = __float2bfloat16_rn(x); }
 
-template <typename T>
+#ifndef RWKV7_DECODE_ROWS
+#define RWKV7_DECODE_ROWS 8
+#endif
+
+// A thread owns R rows x E columns of the state (R * E = 32, 128 threads per (b,h)): the E
+// columns of each token vector it needs are read from shared memory once for all R rows, which
+// is what keeps the shared-memory port from competing with the HBM stream (with one row of 32
+// columns per thread the kernel read 80 KB of shared memory per 32 KB of state traffic).
+template <typename T, int R>
 __global__ void __launch_bounds__(128, 8)
 wkv7_decode_kernel(DecPtrs ptrs, const float *s0, T *__restrict__ y, float *s_out,
                    int Tlen, int H) {
+    constexpr int E = 32 / R, TPR = kN / E, Q = E / 4;   // columns per thread, threads per row, float4s per row
     __shared__ __align__(16) float vec[6][kN];
     const int bh = blockIdx.x;
     const int bi = bh / H, h = bh % H;
     const int tid = threadIdx.x;
-    const int row = tid >> 1, hf = tid & 1;
+    const int row0 = (tid / TPR) * R, c0 = (tid % TPR) * E;
 
-    float4 S[8];
+    float4 S[R][Q];
     if (s0 != nullptr) {
-        const float4 *src = reinterpret_cast<const float4 *>(s0 + ((size_t)bh * kN + row) * kN);
 #pragma unroll
-        for (int m = 0; m < 8; ++m) S[m] = __ldcs(src + 2 * m + hf);
+        for (int rho = 0; rho < R; ++rho) {
+            const float4 *src = reinterpret_cast<const float4 *>(s0 + ((size_t)bh * kN + row0 + rho) * kN + c0);
+#pragma unroll
+            for (int m = 0; m < Q; ++m) S[rho][m] = __ldcs(src + m);
+        }
     } else {
 #pragma unroll
-        for (int m = 0; m < 8; ++m) S[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int rho = 0; rho < R; ++rho)
+#pragma unroll
+            for (int m = 0; m < Q; ++m) S[rho][m] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 
     for (int t = 0; t < Tlen; ++t) {
@@ -71,45 +84,61 @@ wkv7_decode_kernel(DecPtrs ptrs, const float *s0, T *__restrict__ y, float *s_ou
             vec[tensor][j] = x;
         }
         __syncthreads();
-        const float4 *a4 = reinterpret_cast<const float4 *>(vec[VA]);
-        float sa0 = 0.f, sa1 = 0.f;
+        float4 av[Q];
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            const float4 a = a4[2 * m + hf];
-            sa0 = fmaf(S[m].x, a.x, sa0);
-            sa1 = fmaf(S[m].y, a.y, sa1);
-            sa0 = fmaf(S[m].z, a.z, sa0);
-            sa1 = fmaf(S[m].w, a.w, sa1);
-        }
-        float sa = sa0 + sa1;
-        sa += __shfl_xor_sync(0xffffffffu, sa, 1);
-        const float vi = vec[VV][row];
-        const float4 *d4 = reinterpret_cast<const float4 *>(vec[VD]);
-        const float4 *b4 = reinterpret_cast<const float4 *>(vec[VB]);
-        const float4 *k4 = reinterpret_cast<const float4 *>(vec[VK]);
-        const float4 *r4 = reinterpret_cast<const float4 *>(vec[VR]);
-        float y0 = 0.f, y1 = 0.f;
+        for (int m = 0; m < Q; ++m) av[m] = *reinterpret_cast<const float4 *>(&vec[VA][c0 + 4 * m]);
+        float sa[R];
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            const float4 d = d4[2 * m + hf], b = b4[2 * m + hf], k = k4[2 * m + hf], r = r4[2 * m + hf];
-            S[m].x = fmaf(S[m].x, d.x, fmaf(sa, b.x, vi * k.x));
-            S[m].y = fmaf(S[m].y, d.y, fmaf(sa, b.y, vi * k.y));
-            S[m].z = fmaf(S[m].z, d.z, fmaf(sa, b.z, vi * k.z));
-            S[m].w = fmaf(S[m].w, d.w, fmaf(sa, b.w, vi * k.w));
-            y0 = fmaf(S[m].x, r.x, y0);
-            y1 = fmaf(S[m].y, r.y, y1);
-            y0 = fmaf(S[m].z, r.z, y0);
-            y1 = fmaf(S[m].w, r.w, y1);
+        for (int rho = 0; rho < R; ++rho) {
+            float s0_ = 0.f, s1_ = 0.f;
+#pragma unroll
+            for (int m = 0; m < Q; ++m) {
+                s0_ = fmaf(S[rho][m].x, av[m].x, s0_);
+                s1_ = fmaf(S[rho][m].y, av[m].y, s1_);
+                s0_ = fmaf(S[rho][m].z, av[m].z, s0_);
+                s1_ = fmaf(S[rho][m].w, av[m].w, s1_);
+            }
+            float x = s0_ + s1_;
+#pragma unroll
+            for (int off = TPR / 2; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+            sa[rho] = x;
         }
-        float yy = y0 + y1;
-        yy += __shfl_xor_sync(0xffffffffu, yy, 1);
-        if (hf == 0) st_out<T>(y + o + row, yy);
+        float yy[R];
+#pragma unroll
+        for (int rho = 0; rho < R; ++rho) yy[rho] = 0.f;
+#pragma unroll
+        for (int m = 0; m < Q; ++m) {
+            const float4 d = *reinterpret_cast<const float4 *>(&vec[VD][c0 + 4 * m]);
+            const float4 b = *reinterpret_cast<const float4 *>(&vec[VB][c0 + 4 * m]);
+            const float4 k = *reinterpret_cast<const float4 *>(&vec[VK][c0 + 4 * m]);
+            const float4 r = *reinterpret_cast<const float4 *>(&vec[VR][c0 + 4 * m]);
+#pragma unroll
+            for (int rho = 0; rho < R; ++rho) {
+                const float vi = vec[VV][row0 + rho];
+                float4 &x = S[rho][m];
+                x.x = fmaf(x.x, d.x, fmaf(sa[rho], b.x, vi * k.x));
+                x.y = fmaf(x.y, d.y, fmaf(sa[rho], b.y, vi * k.y));
+                x.z = fmaf(x.z, d.z, fmaf(sa[rho], b.z, vi * k.z));
+                x.w = fmaf(x.w, d.w, fmaf(sa[rho], b.w, vi * k.w));
+                yy[rho] = fmaf(x.x, r.x, fmaf(x.y, r.y, fmaf(x.z, r.z, fmaf(x.w, r.w, yy[rho]))));
+            }
+        }
+#pragma unroll
+        for (int rho = 0; rho < R; ++rho) {
+            float x = yy[rho];
+#pragma unroll
+            for (int off = TPR / 2; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+            if (tid % TPR == 0) st_out<T>(y + o + row0 + rho, x);
+        }
     }
 
     if (s_out != nullptr) {
-        float4 *dst = reinterpret_cast<float4 *>(s_out + ((size_t)bh * kN + row) * kN);
 #pragma unroll
-        for (int m = 0; m < 8; ++m) __stcs(dst + 2 * m + hf, S[m]);
+        for (int rho = 0; rho < R; ++rho) {
+            float4 *dst = reinterpret_cast<float4 *>(s_out + ((size_t)bh * kN + row0 + rho) * kN + c0);
+#pragma unroll
+            for (int m = 0; m < Q; ++m) __stcs(dst + m, S[rho][m]);
+        }
     }
 }
 
@@ -119,10 +148,10 @@ int launch_wkv7_decode(const Wkv7Args &p, cudaStream_t stream) {
     DecPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
     const unsigned grid = (unsigned)(p.B * p.H);
     if (p.bf16)
-        wkv7_decode_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(ptrs, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y),
+        wkv7_decode_kernel<__nv_bfloat16, RWKV7_DECODE_ROWS><<<grid, 128, 0, stream>>>(ptrs, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y),
                                                                     p.s_out, (int)p.T, (int)p.H);
     else
-        wkv7_decode_kernel<float><<<grid, 128, 0, stream>>>(ptrs, p.s0, reinterpret_cast<float *>(p.y), p.s_out,
+        wkv7_decode_kernel<float, RWKV7_DECODE_ROWS><<<grid, 128, 0, stream>>>(ptrs, p.s0, reinterpret_cast<float *>(p.y), p.s_out,
                                                             (int)p.T, (int)p.H);
     count_launch();
     return (int)cudaGetLastError();
