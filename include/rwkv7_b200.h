@@ -202,7 +202,10 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *initial_state,
  *   state_replacement [B, T, H, N]  sa_t = S_{t-1} a_t, sequence dtype.
  * initial_state may be NULL (pretrain: S0 = 0) and next_state may be NULL (pretrain,
  * statetune).  T must be a multiple of chunk_len (the reference also asserts chunk_len == 16;
- * any positive value is accepted here).  No workspace.
+ * any positive value is accepted here).  With chunk_len 16, N = 64 and BF16 tensors the
+ * tensor-core prefill kernel computes the saved tensors as well (state_replacement is its U,
+ * the snapshots are partial sums of its state update); it needs the workspace of
+ * rwkv7_wkv7_workspace_bytes.  Everything else takes the sequential scan.
  */
 int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *initial_state, const rwkv7_tensor *receptance,
                                    const rwkv7_tensor *weight_decay,
@@ -211,7 +214,7 @@ int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *initial_state, const rwkv
                                    const rwkv7_tensor *replacement, int64_t chunk_len,
                                    rwkv7_tensor *output, rwkv7_tensor *next_state,
                                    rwkv7_tensor *snapshots, rwkv7_tensor *state_replacement,
-                                   rwkv7_stream stream);
+                                   void *workspace, size_t workspace_bytes, rwkv7_stream stream);
 
 /*
  * Replaces launch_wkv7_backward / wkv7_backward_kernel (wkv7/backward.rs:583-703,

@@ -299,8 +299,10 @@ def wkv7_forward_saved(inputs: Wkv7PretrainForwardInputs, initial_state: Optiona
     s_out = torch.empty((B, H, N, N), dtype=torch.float32, device=r.device) if want_state else None
     descs = [describe(initial_state)] + [describe(t) for t in inputs.six()]
     outs = [describe(y), describe(s_out), describe(snaps), describe(sa)]
+    workspace, ws_bytes = _wkv7_workspace(r)
+    ws_ptr = ctypes.c_void_p(workspace.data_ptr() if workspace is not None else 0)
     _check(lib().rwkv7_fused_wkv7_forward_saved(*[_ref(d) for d in descs], ctypes.c_int64(inputs.chunk_len),
-                                                *[_ref(d) for d in outs], _stream(r)))
+                                                *[_ref(d) for d in outs], ws_ptr, ctypes.c_size_t(ws_bytes), _stream(r)))
     return Wkv7SavedForward(output=y, next_state=s_out, snapshots=snaps, state_replacement=sa)
 
 

@@ -350,7 +350,8 @@ int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *s0, const rwkv7_tensor *r
                                    const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
                                    const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
                                    rwkv7_tensor *next_state, rwkv7_tensor *snapshots,
-                                   rwkv7_tensor *state_replacement, rwkv7_stream stream) {
+                                   rwkv7_tensor *state_replacement, void *workspace, size_t workspace_bytes,
+                                   rwkv7_stream stream) {
     clear_error();
     const rwkv7_tensor *six_t[6] = {r_t, w, k, v, a, b};
     TensorInfo six[6];
@@ -376,6 +377,20 @@ int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *s0, const rwkv7_tensor *r
     DeviceGuard guard(p.device);
     if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
     RWKV7_TRY(num_sms(p.device, &p.num_sms));
+    // The tensor-core kernel writes snapshots every 16 tokens; other chunk lengths, head sizes and
+    // fp32 tensors take the sequential scan.
+    const int path = g_wkv7_path.load();
+    if (path != RWKV7_WKV7_SEQUENTIAL && chunk_len == 16 && p.T >= 64 && wkv7_chunked_supported(p) &&
+        (reinterpret_cast<uintptr_t>(state_replacement->data) & 15u) == 0) {
+        const size_t need = wkv7_chunked_workspace_bytes(p.B, p.T, p.H, p.N);
+        if (workspace == nullptr || workspace_bytes < need)
+            return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: wkv7 needs %zu workspace bytes, got %zu", need,
+                        workspace == nullptr ? (size_t)0 : workspace_bytes);
+        if (int e = launch_wkv7_chunked_saved(p, workspace, static_cast<float *>(snapshots->data),
+                                              state_replacement->data, (cudaStream_t)stream))
+            return cuda_fail("wkv7 training forward launch", e);
+        return RWKV7_OK;
+    }
     if (int e = launch_wkv7_forward_saved(p, static_cast<float *>(snapshots->data), state_replacement->data,
                                           (int)chunk_len, (cudaStream_t)stream))
         return cuda_fail("wkv7 training forward launch", e);

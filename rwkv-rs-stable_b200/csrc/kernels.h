@@ -61,6 +61,11 @@ bool wkv7_chunked_supported(const Wkv7Args &p);
 int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream);
 
+// Training forward on the tensor cores (N == 64, bf16, chunk_len 16): the chunked kernel also
+// writing snapshots and state_replacement; same workspace as launch_wkv7_chunked.
+int launch_wkv7_chunked_saved(const Wkv7Args &p, void *workspace, float *snapshots, void *state_replacement,
+                              cudaStream_t stream);
+
 // Fixed flag array inside the library image, usable in place of a workspace by
 // callers that must not allocate: device address (resolved on first use per
 // device, which must be current) and capacity.

@@ -139,6 +139,19 @@ __device__ __forceinline__ void mma_k64(uint32_t d_tmem, uint64_t a0, uint64_t b
     }
 }
 
+// Two consecutive K-steps (16 tokens) of the same product, starting a new accumulation.
+template <int A_ROWS, int B_ROWS, int N>
+__device__ __forceinline__ void mma_kpair(uint32_t d_tmem, uint64_t a0, uint64_t b0, int ks0) {
+    constexpr uint32_t idesc = make_idesc(kFmtTF32, 128, N, false, false);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int ks = ks0 + u;
+        const uint64_t ao = (uint64_t)(((ks >> 2) * A_ROWS * 128 + (ks & 3) * 32) >> 4);
+        const uint64_t bo = (uint64_t)(((ks >> 2) * B_ROWS * 128 + (ks & 3) * 32) >> 4);
+        umma_tf32(d_tmem, a0 + ao, b0 + bo, idesc, u > 0);
+    }
+}
+
 // Same with the A operand read from TMEM (a previous accumulator: 128 lanes x 64
 // fp32 columns, 8 columns per K-step; the tensor core truncates it to tf32).
 template <int B_ROWS, int N>
@@ -167,10 +180,16 @@ __device__ __forceinline__ void mma_ts_block(uint32_t d_tmem, uint32_t a_tmem, u
     }
 }
 
+// SAVE: also write what the backward pass needs (wkv7/forward.rs:368-375): the state after every
+// 16th token (snapshots [B,H,T/16,N,N], fp32) and state_replacement = U (sa_t = S_{t-1} a_t).  The
+// state update dS is then accumulated per 16-token block in four TMEM regions; the state after
+// token 16m-1 is diag(exp(c_{16m-1})) (Z0 + the first m blocks).
+template <bool SAVE>
 __global__ void __launch_bounds__(kThreads, 1)
 wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     __nv_bfloat16 *__restrict__ y, float *s_out, int *__restrict__ flags,
-                    int Tlen, int H, int *status) {
+                    int Tlen, int H, int *status, float *__restrict__ snapshots,
+                    __nv_bfloat16 *__restrict__ state_repl) {
     // Every pointer is derived from the array itself so that the accesses stay in
     // the shared address space; the 1024-byte alignment the swizzled tiles need is
     // what the runtime provides and is verified before anything else happens.
@@ -246,6 +265,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                    dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0);
     constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
     uint32_t mma_phase = 0, dep_phase = 0;
+    // TMEM columns of the dS accumulator of token block b (the last one reuses G's, dead by then)
+    auto ds_col = [](int b) -> uint32_t { return !SAVE ? kColDS : (b == 3 ? kColG : kColDS + 64u * (uint32_t)b); };
+    float *exp_sub = reinterpret_cast<float *>(tXU + 2048);   // [3][64] exp(c_15), exp(c_31), exp(c_47); SAVE only
     bool failed = false;
     int tma_issued = 1, tma_consumed = 0;  // tile batches requested / received
 
@@ -321,6 +343,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 *reinterpret_cast<float *>(pBK + 64 * 128 + o) = khv[u];
                 e_prev = e;
             }
+            if constexpr (SAVE) {
+                if ((tg & 1) && tg < 7) exp_sub[(tg >> 1) * 64 + j] = e_prev;   // exp(c_t) at t = 15, 31, 47
+            }
             // transposed copies: Bh^T, Kh^T [j][t] and V^T [i][s], 8 consecutive tokens per thread
 #pragma unroll
             for (int q4 = 0; q4 < 2; ++q4) {
@@ -342,7 +367,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             // need only this chunk's scaled operands.  They run while G is read back below.
             mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
             mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
-            mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
+            if constexpr (!SAVE) mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
         mma_phase ^= 1;
@@ -409,6 +434,11 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             tc_fence_after();
             mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
             mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, true);    // Y^T += V^T A_rk^T
+            if constexpr (SAVE) {
+#pragma unroll
+                for (int b = 0; b < kL / kBlk; ++b)   // dS_b = V^T Kh over the tokens of block b (G is dead now)
+                    mma_kpair<64, 128, 64>(tmem + ds_col(b), dVT, dZT + kLower, 2 * b);
+            }
             umma_commit(bar_dep);
         }
         // ---------------- U = (I - A_ab)^-1 X is solved block-wise with 16-token blocks:
@@ -457,7 +487,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             };
             auto leaves = [&](int b) {   // what U_b^T contributes to Y^T and dS
                 mma_ts_block<64>(tmem + kColYT, tmem + kColUT + b * kBlk, dBK, 64, b * kBlk, kBlk / 8, true);   // A_rb
-                mma_ts_block<64>(tmem + kColDS, tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, kBlk / 8, true);    // Bh
+                mma_ts_block<64>(tmem + ds_col(b), tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, kBlk / 8, true);    // Bh
             };
             dep_wait();   // parts 1 and 2 have finished: X^T is complete
             // U^T = X^T (I - A_ab)^-T by block forward substitution over the token blocks b:
@@ -488,7 +518,41 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         PHASE(11);
         if (quarter < 2) {
             uint32_t v[16];
-            tmem_ld16(tmem + lane_base + kColDS + cgrp * 16, v);
+            if constexpr (SAVE) {
+                // v accumulates the blocks; after block m the state after token 16m+15 is known
+                const size_t nsnap = (size_t)Tlen / 16;
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    uint32_t w[16];
+                    tmem_ld16(tmem + lane_base + ds_col(m) + cgrp * 16, w);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)
+                        v[e] = m == 0 ? w[e] : __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(w[e]));
+                    if (m < 3 && 16 * (m + 1) <= valid) {
+                        const float4 *e4 = reinterpret_cast<const float4 *>(exp_sub + m * 64 + cgrp * 16);
+                        float *dst = snapshots + (((size_t)bh * nsnap + (size_t)chunk * 4 + m) * kN + zj) * kN + cgrp * 16;
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const float4 g = e4[q4];
+                            *reinterpret_cast<float4 *>(dst + 4 * q4) =
+                                make_float4(g.x * (Z[4 * q4 + 0] + __uint_as_float(v[4 * q4 + 0])),
+                                            g.y * (Z[4 * q4 + 1] + __uint_as_float(v[4 * q4 + 1])),
+                                            g.z * (Z[4 * q4 + 2] + __uint_as_float(v[4 * q4 + 2])),
+                                            g.w * (Z[4 * q4 + 3] + __uint_as_float(v[4 * q4 + 3])));
+                        }
+                    }
+                }
+                uint32_t uv[16];   // U^T: this thread's value channel for tokens 16*cgrp .. +15
+                tmem_ld16(tmem + lane_base + kColUT + cgrp * 16, uv);
+                tmem_ld_wait();
+                __nv_bfloat16 *sr = state_repl + (((size_t)bi * Tlen + chunk * kL + cgrp * 16) * H + h) * kN + zj;
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (cgrp * 16 + e < valid) sr[(size_t)e * H * kN] = __float2bfloat16_rn(__uint_as_float(uv[e]));
+            } else {
+                tmem_ld16(tmem + lane_base + kColDS + cgrp * 16, v);
+            }
             uint32_t yv[16];
             tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
             tmem_ld_wait();
@@ -503,6 +567,14 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,   // operand of the next chunk
                          make_float4(round_tf32(Z[4 * q4]), round_tf32(Z[4 * q4 + 1]), round_tf32(Z[4 * q4 + 2]),
                                      round_tf32(Z[4 * q4 + 3])));
+            }
+            if constexpr (SAVE) {
+                if (valid == kL) {   // the state after the chunk's last token is its fourth snapshot
+                    float *sn = snapshots + (((size_t)bh * ((size_t)Tlen / 16) + (size_t)chunk * 4 + 3) * kN + zj) * kN + cgrp * 16;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<float4 *>(sn + 4 * q4) = make_float4(Z[4 * q4], Z[4 * q4 + 1], Z[4 * q4 + 2], Z[4 * q4 + 3]);
+                }
             }
             // y[t][i]: this thread holds value channel i = zj for tokens 16*cgrp .. +15
             __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + cgrp * 16) * H + h) * kN + zj;
@@ -618,8 +690,11 @@ bool wkv7_chunked_supported(const Wkv7Args &p) {
            aligned(p.b) && aligned(p.y) && p.B * p.T < (int64_t(1) << 31);
 }
 
-int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
-    (void)workspace_bytes;
+int launch_wkv7_sequential_flagged_saved(const Wkv7Args &p, const int *flags, float *snapshots,
+                                         void *state_replacement, int chunk_len, cudaStream_t stream);
+
+static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapshots, void *state_replacement,
+                               cudaStream_t stream) {
     EncodeTiledFn encode = encode_fn();
     if (encode == nullptr) return (int)cudaErrorNotSupported;
     TmaMaps maps;
@@ -636,18 +711,39 @@ int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_byt
     }
     int *status = nullptr;
     if (int e = device_status_ptr(p.device, &status)) return e;
-    cudaError_t e = cudaFuncSetAttribute(wkv7_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBytes);
+    const bool save = snapshots != nullptr;
+    cudaError_t e = save ? cudaFuncSetAttribute(wkv7_chunked_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)kSmemBytes)
+                         : cudaFuncSetAttribute(wkv7_chunked_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     int *flags = static_cast<int *>(workspace);
-    wkv7_chunked_kernel<<<(unsigned)(p.B * p.H), kThreads, kSmemBytes, stream>>>(
-        maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags, (int)p.T, (int)p.H, status);
+    if (save)
+        wkv7_chunked_kernel<true><<<(unsigned)(p.B * p.H), kThreads, kSmemBytes, stream>>>(
+            maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags, (int)p.T, (int)p.H, status, snapshots,
+            reinterpret_cast<__nv_bfloat16 *>(state_replacement));
+    else
+        wkv7_chunked_kernel<false><<<(unsigned)(p.B * p.H), kThreads, kSmemBytes, stream>>>(
+            maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags, (int)p.T, (int)p.H, status, nullptr,
+            nullptr);
     count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     // Chains whose decay left the safe range are recomputed token by token; the
     // kernel exits at once for every chain that is not flagged.
+    if (save) return launch_wkv7_sequential_flagged_saved(p, flags, snapshots, state_replacement, 16, stream);
     return launch_wkv7_sequential_flagged(p, flags, stream);
+}
+
+int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    (void)workspace_bytes;
+    return launch_chunked_impl(p, workspace, nullptr, nullptr, stream);
+}
+
+// Training forward on the tensor cores: chunk_len 16, T a multiple of 16.
+int launch_wkv7_chunked_saved(const Wkv7Args &p, void *workspace, float *snapshots, void *state_replacement,
+                              cudaStream_t stream) {
+    return launch_chunked_impl(p, workspace, snapshots, state_replacement, stream);
 }
 
 }  // namespace rwkv7

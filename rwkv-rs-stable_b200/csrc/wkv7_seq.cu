@@ -379,6 +379,32 @@ int launch_wkv7_forward_saved(const Wkv7Args &p, float *snapshots, void *state_r
                   : launch_seq_saved<float>(p, snapshots, state_replacement, chunk_len, stream);
 }
 
+// N == 64 only: the flagged chains again, with the saved tensors of the training forward.
+int launch_wkv7_sequential_flagged_saved(const Wkv7Args &p, const int *flags, float *snapshots,
+                                         void *state_replacement, int chunk_len, cudaStream_t stream) {
+    SeqPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
+    SavePtrs save{snapshots, state_replacement, chunk_len};
+    constexpr int ROWS = 16;
+    const size_t smem = sizeof(float) * (2 * kTile * 6 * kN + 4 * kTile * ROWS);
+    const unsigned grid = (unsigned)(p.B * p.H * (kN / ROWS));
+    cudaError_t e;
+    if (p.bf16) {
+        auto kern = wkv7_seq64_kernel<__nv_bfloat16, ROWS, true>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, ROWS * 4, smem, stream>>>(ptrs, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, (int)p.T,
+                                               (int)p.H, flags, save);
+    } else {
+        auto kern = wkv7_seq64_kernel<float, ROWS, true>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, ROWS * 4, smem, stream>>>(ptrs, p.s0, reinterpret_cast<float *>(p.y), p.s_out, (int)p.T, (int)p.H,
+                                               flags, save);
+    }
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
 // N == 64 only: recomputes the chains with flags[b*H+h] != 0, 16 value rows per CTA.
 int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStream_t stream) {
     return p.bf16 ? launch_seq64<__nv_bfloat16, 16>(p, stream, flags) : launch_seq64<float, 16>(p, stream, flags);

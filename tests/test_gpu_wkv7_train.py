@@ -37,6 +37,42 @@ def test_training_forward_saves(pkg, oracle, workloads, cuda, shape, state):
     parity.assert_close_f32(out.state_replacement.cpu().numpy(), sa_ref, 2e-5, "state_replacement")
 
 
+@pytest.mark.parametrize("shape,state", [((1, 64, 2, 64), "normal"), ((2, 192, 3, 64), None), ((1, 80, 2, 64), "normal"),
+                                         ((1, 1024, 2, 64), "normal")])
+def test_training_forward_on_tensor_cores(pkg, oracle, workloads, cuda, shape, state):
+    """bf16, N = 64, chunk_len 16: the tcgen05 prefill kernel also writes the saved tensors (tf32
+    operands: 1e-3 of max, plus bf16 storage where the tensor is bf16).  T = 80 ends in a partial
+    64-token chunk holding one 16-token block."""
+    inp = workloads.wkv7_inputs(*shape, seed=42, dtype=torch.bfloat16, state=state)
+    f = {n: inp[n].float().numpy() for n in inp}
+    y_ref, s_ref, snaps_ref, sa_ref = oracle.wkv7_train(*[f[n] for n in "rwkvab"], s0=f.get("s0"), chunk_len=16)
+    g = {n: t.to(cuda) for n, t in inp.items()}
+    pkg.set_wkv7_path(pkg.WKV7_CHUNKED)
+    try:
+        out = pkg.wkv7_forward_saved(pkg.Wkv7PretrainForwardInputs(*[g[n] for n in "rwkvab"]), g.get("s0"),
+                                     want_state=True)
+        torch.cuda.synchronize()
+    finally:
+        pkg.set_wkv7_path(pkg.WKV7_AUTO)
+    assert pkg.read_device_status(0) == 0
+    parity.assert_close_bf16_store(out.output.float().cpu().numpy(), y_ref, 1e-3, "y")
+    parity.assert_close_f32(out.next_state.cpu().numpy(), s_ref, 1e-3, "next_state")
+    parity.assert_close_f32(out.snapshots.cpu().numpy(), snaps_ref, 1e-3, "snapshots")
+    parity.assert_close_bf16_store(out.state_replacement.float().cpu().numpy(), sa_ref, 1e-3, "state_replacement")
+    # out-of-range decay in one batch row: flagged chains come from the sequential scan, saved tensors included
+    if shape[0] > 1:
+        w = g["w"].float()
+        w[0] = torch.rand_like(w[0]) + 0.5
+        g["w"] = w.to(torch.bfloat16)
+        f["w"] = g["w"].float().cpu().numpy()
+        y_ref, s_ref, snaps_ref, sa_ref = oracle.wkv7_train(*[f[n] for n in "rwkvab"], s0=f.get("s0"), chunk_len=16)
+        out = pkg.wkv7_forward_saved(pkg.Wkv7PretrainForwardInputs(*[g[n] for n in "rwkvab"]), g.get("s0"),
+                                     want_state=True)
+        torch.cuda.synchronize()
+        parity.assert_close_f32(out.snapshots.cpu().numpy(), snaps_ref, 1e-3, "snapshots (fallback)")
+        parity.assert_close_bf16_store(out.state_replacement.float().cpu().numpy(), sa_ref, 1e-3, "state_replacement (fallback)")
+
+
 def test_reference_backward_test(pkg, oracle, workloads, cuda):
     """wkv7/mod.rs:294-328: shape [1,16,1,4], U[0,1) inputs, loss = sum(y), tolerance 1e-2 absolute."""
     six = workloads.uniform_inputs((1, 16, 1, 4), seed=3)
