@@ -230,3 +230,35 @@ def test_wkv7_train_forward_saves(oracle, workloads):
     np.testing.assert_allclose(snaps[:, :, 0], s_half, rtol=1e-13, atol=1e-13)
     np.testing.assert_allclose(sa[:, 0], np.einsum("bhij,bhj->bhi", f["s0"].astype(np.float64),
                                                    f["a"][:, 0].astype(np.float64)), rtol=1e-13, atol=1e-13)
+
+
+def test_oracle_reproduces_golden_of_the_other_operators(oracle):
+    """The committed fixtures of mix6 / addcmul5 / token_shift_diff, the two time-mixer epilogues,
+    the channel mixer and the training path: drift of the oracle shows up here, on CPU."""
+    g = _load("mix_ops.npz")
+    mus = [m for m in g["mus"]]
+    np.testing.assert_allclose(oracle.mix6(g["x"], mus), g["mix6"], rtol=1e-13, atol=1e-13)
+    np.testing.assert_allclose(oracle.addcmul(g["x"], g["diff"], mus[:5]), g["addcmul5"], rtol=1e-13, atol=1e-13)
+    tsd, st = oracle.token_shift_diff(g["x"], g["state"], g["ids"])
+    assert np.array_equal(tsd, g["tsd"]) and np.array_equal(st, g["tsd_state"])
+    g = _load("time_mixer_epilogues.npz")
+    e = {k[3:]: v for k, v in g.items() if k.startswith("in_")}
+    wp = oracle.weight_prepare(e["key_precursor"], e["learning_rate_lora"], e["weight_decay_lora"], e["key_removal"],
+                               e["key_replacement"], 2, e["value_precursor"], e["value_from_first_cell"],
+                               e["value_residual_lora"])
+    for k, v in wp.items():
+        np.testing.assert_allclose(v, g["wp_" + k], rtol=1e-13, atol=1e-13, err_msg=k)
+    gr = oracle.gated_readout(e["wkv7_output"], e["receptance"], e["replacement_key"], e["value"], e["gate"],
+                              e["group_norm_gamma"], e["group_norm_beta"], e["receptance_key_bonus"], 2)
+    np.testing.assert_allclose(gr, g["gated_readout"], rtol=1e-13, atol=1e-13)
+    g = _load("channel_mixer.npz")
+    np.testing.assert_allclose(oracle.channel_mixer(g["x"], g["key_scale"], g["key_weight"], g["value_weight"]),
+                               g["out"], rtol=1e-13, atol=1e-13)
+    for name in ("wkv7_train_ref_shape.npz", "wkv7_train_n64.npz"):
+        g = _load(name)
+        y, s_out, snaps, sa = oracle.wkv7_train(*[g[n] for n in "rwkvab"], s0=g["s0"], chunk_len=16)
+        for got, key in ((y, "y"), (s_out, "s_out"), (snaps, "snapshots"), (sa, "state_replacement")):
+            np.testing.assert_allclose(got, g[key], rtol=1e-12, atol=1e-12, err_msg=key)
+        grads = oracle.wkv7_backward(*[g[n] for n in "rwkvab"], g["dy"], s0=g["s0"], ds_out=g["ds"])
+        for k, v in grads.items():
+            np.testing.assert_allclose(v, g["d" + k], rtol=1e-11, atol=1e-11, err_msg="d" + k)
