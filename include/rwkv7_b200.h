@@ -110,6 +110,13 @@ int64_t rwkv7_kernel_launch_count(void);
  */
 int rwkv7_read_device_status(int device, rwkv7_stream stream);
 
+/* No counterpart in the reference.  Launches one thread that waits, for at most max_polls
+ * polls (1 .. 1000000), on a barrier that nothing signals, records the time-out in the device
+ * status word and returns: the error path of every bounded wait in this library, exercised
+ * without hanging or faulting anything.  rwkv7_read_device_status then returns
+ * RWKV7_ERR_TIMEOUT once, and the device stays usable. */
+int rwkv7_selftest_bounded_wait(int device, int64_t max_polls, rwkv7_stream stream);
+
 /* ------------------------------------------------------------------ WKV7 -- */
 /*
  * Per (b,h), state S[i][j] (i value row, j key column), t = 0..T-1:

@@ -143,6 +143,13 @@ def read_device_status(device: int = 0) -> int:
     return int(lib().rwkv7_read_device_status(ctypes.c_int(device), stream))
 
 
+def selftest_bounded_wait(device: int = 0, max_polls: int = 1000) -> None:
+    """Runs the library's bounded-wait error path once (``rwkv7_selftest_bounded_wait``); the
+    time-out is then reported by :func:`read_device_status`."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    _check(lib().rwkv7_selftest_bounded_wait(ctypes.c_int(device), ctypes.c_int64(max_polls), stream))
+
+
 # ---------------------------------------------------------------------- WKV7 --
 
 

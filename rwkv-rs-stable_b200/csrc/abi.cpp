@@ -268,6 +268,17 @@ int rwkv7_read_device_status(int device, rwkv7_stream stream) {
     return RWKV7_OK;
 }
 
+int rwkv7_selftest_bounded_wait(int device, int64_t max_polls, rwkv7_stream stream) {
+    clear_error();
+    if (max_polls < 1 || max_polls > 1000000)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: max_polls must be in [1, 1000000], got %lld", (long long)max_polls);
+    DeviceGuard guard(device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    if (int e = launch_bounded_wait_selftest(device, (unsigned)max_polls, (cudaStream_t)stream))
+        return cuda_fail("bounded-wait self-test launch", e);
+    return RWKV7_OK;
+}
+
 size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype) {
     (void)dtype;
     if (g_wkv7_path.load() == RWKV7_WKV7_SEQUENTIAL) return 0;

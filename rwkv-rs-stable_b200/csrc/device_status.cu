@@ -6,6 +6,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "sm100_umma.cuh"
 
 namespace rwkv7 {
 
@@ -34,6 +35,25 @@ int device_status_ptr(int device, int **out) {
     }
     *out = g_status_ptr[device];
     return 0;
+}
+
+// Exercises the error path every kernel in this library takes when a bounded wait expires:
+// one thread waits, for at most `max_polls` polls, on an mbarrier that nothing will ever arrive
+// on, then records the time-out in the status word and returns.  The wait cannot hang (it is
+// the same bounded loop the kernels use) and nothing faults; the context stays usable.
+__global__ void bounded_wait_selftest_kernel(int *status, unsigned max_polls) {
+    __shared__ __align__(8) uint64_t bar;
+    sm100::mbar_init(&bar, 1);
+    sm100::mbar_fence_init();
+    if (!sm100::mbar_wait(&bar, 0, max_polls)) atomicExch(status, (int)kDevTimeout);
+}
+
+int launch_bounded_wait_selftest(int device, unsigned max_polls, cudaStream_t stream) {
+    int *status = nullptr;
+    if (int e = device_status_ptr(device, &status)) return e;
+    bounded_wait_selftest_kernel<<<1, 1, 0, stream>>>(status, max_polls);
+    count_launch();
+    return (int)cudaGetLastError();
 }
 
 }  // namespace rwkv7

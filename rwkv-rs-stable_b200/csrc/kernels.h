@@ -14,6 +14,8 @@ namespace rwkv7 {
 enum DeviceStatus : int { kDevOk = 0, kDevTimeout = 1, kDevBadIndex = 2, kDevInternal = 3 };
 // Address of the per-device status word, resolved once per device.
 int device_status_ptr(int device, int **out);
+// One bounded wait on a barrier nobody signals: records kDevTimeout and returns (test hook).
+int launch_bounded_wait_selftest(int device, unsigned max_polls, cudaStream_t stream);
 // Process-wide count of kernel launches (rwkv7_kernel_launch_count).
 void count_launch(int n = 1);
 int64_t launch_count();

@@ -31,6 +31,25 @@ def shard_ranges(B: int, H: int, world: int) -> list[tuple[slice, slice]]:
     raise ValueError(f"cannot split B={B}, H={H} into {world} rectangular batch x head shards")
 
 
+def gather_outputs(y_local: torch.Tensor, B: int, H: int, group=None) -> torch.Tensor:
+    """All-gathers the per-rank y shards (``[B_loc, T, H_loc, N]``, cut as :func:`shard_ranges`
+    cuts them) into the full ``[B, T, H, N]`` tensor on every rank.  Only for consumers that
+    need the whole tensor; the WKV7 path itself never calls it.  A batch split is one
+    all-gather into place; a head split gathers ``[world, B_loc, T, H_loc, N]`` and scatters
+    the head blocks into their slots with one strided copy per rank."""
+    world = dist.get_world_size(group)
+    ranges = shard_ranges(B, H, world)
+    T, N = y_local.shape[1], y_local.shape[3]
+    gathered = torch.empty((world,) + tuple(y_local.shape), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(gathered.view(-1, *y_local.shape[1:]), y_local.contiguous(), group=group)
+    if ranges[0][1] == slice(0, H):      # whole-batch shards: the gather already is [B, T, H, N]
+        return gathered.view(B, T, H, N)
+    full = torch.empty((B, T, H, N), dtype=y_local.dtype, device=y_local.device)
+    for r, (bs, hs) in enumerate(ranges):
+        full[bs, :, hs] = gathered[r]
+    return full
+
+
 def vocab_shard(V: int, rank: int, world: int) -> tuple[int, int]:
     """``[lo, hi)`` rows of the LM-head weight owned by ``rank`` (near-equal, contiguous)."""
     base, rem = divmod(V, world)

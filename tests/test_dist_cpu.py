@@ -53,6 +53,41 @@ def _worker(rank, world, port, root, result):
         dist.destroy_process_group()
 
 
+def _gather_worker(rank, world, port, root, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import sys
+    sys.path.insert(0, root)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from rwkv_rs_stable_b200 import dist as rdist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ok = True
+        for B, H in ((4, 3), (1, 6), (3, 4)):       # batch split, head split, head split with B > 1
+            full = torch.arange(B * 5 * H * 2, dtype=torch.float32).reshape(B, 5, H, 2)
+            bs, hs = rdist.shard_ranges(B, H, world)[rank]
+            got = rdist.gather_outputs(full[bs, :, hs].contiguous(), B, H)
+            ok = ok and torch.equal(got, full)
+        result[rank] = 1 if ok else 0
+    finally:
+        dist.destroy_process_group()
+
+
+def test_output_gather_two_ranks():
+    """C1: every rank ends with the full [B,T,H,N] output, for batch and for head splits."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ctx = mp.get_context("spawn")
+    result = ctx.Array("i", [0, 0])
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, root, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert list(result) == [1, 1]
+
+
 def test_vocab_sharded_combine_two_ranks():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ctx = mp.get_context("spawn")

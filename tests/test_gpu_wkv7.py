@@ -276,3 +276,20 @@ def test_config1_prefix_against_oracle(pkg, oracle, workloads, cuda):
     parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
     parity.assert_close_f32(s, s_ref, 1e-3, "state")
     print("parity", parity.stats(y, y_ref), parity.headline(s, s_ref))
+
+
+def test_expired_bounded_wait_is_reported_and_the_device_stays_usable(pkg, workloads, cuda):
+    """Every device-side wait in the library is bounded; when one expires the kernel records a
+    time-out and returns.  The self-test waits (briefly) on a barrier that nothing signals: the
+    status word must report the time-out once, and the next real call must work."""
+    assert pkg.read_device_status(0) == 0
+    pkg.selftest_bounded_wait(0, max_polls=200)
+    assert pkg.read_device_status(0) == 12          # RWKV7_ERR_TIMEOUT
+    assert "Timeout" in pkg.lib().rwkv7_last_error_message().decode()
+    assert pkg.read_device_status(0) == 0           # reading clears the word
+    inp = workloads.wkv7_inputs(1, 64, 2, 64, seed=2, dtype=torch.bfloat16, device=cuda)
+    out = pkg.wkv7_pretrain_custom(pkg.Wkv7PretrainForwardInputs(*[inp[n] for n in "rwkvab"]))
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all() and pkg.read_device_status(0) == 0
+    with pytest.raises(pkg.KernelInputsError):
+        pkg.selftest_bounded_wait(0, max_polls=0)
