@@ -99,6 +99,13 @@ const char *rwkv7_last_error_message(void);
 /* Process-wide override of the WKV7 kernel choice (tests and benchmarks). */
 int rwkv7_set_wkv7_path(int path);
 int rwkv7_get_wkv7_path(void);
+
+/* The chunked prefill kernel gives a chain to a thread-block cluster of 2 or 4 CTAs when there
+ * are at most half / a quarter as many (b,h) chains as SMs (small-batch prefill): the CTAs take
+ * the chunks in turn, prepare everything that does not depend on the state ahead of time and
+ * pass only the state through distributed shared memory.  0 restores that automatic choice;
+ * 1, 2 or 4 force a cluster size (for tests and measurements).  Process-wide. */
+int rwkv7_set_wkv7_cluster(int cluster_size);
 /* Number of kernels this library has launched in this process (all devices,
  * all threads).  Benchmarks read it before and after a timed region. */
 int64_t rwkv7_kernel_launch_count(void);

@@ -128,6 +128,11 @@ def set_wkv7_path(path: int) -> None:
     _check(lib().rwkv7_set_wkv7_path(ctypes.c_int(path)))
 
 
+def set_wkv7_cluster(cluster_size: int) -> None:
+    """0 = automatic (by the number of chains), else the cluster size (1, 2, 4) of the chunked kernel."""
+    _check(lib().rwkv7_set_wkv7_cluster(ctypes.c_int(cluster_size)))
+
+
 def get_wkv7_path() -> int:
     return int(lib().rwkv7_get_wkv7_path())
 

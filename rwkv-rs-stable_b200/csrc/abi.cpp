@@ -249,6 +249,13 @@ int rwkv7_set_wkv7_path(int path) {
 
 int rwkv7_get_wkv7_path(void) { return g_wkv7_path.load(); }
 
+int rwkv7_set_wkv7_cluster(int cluster_size) {
+    if (cluster_size != 0 && cluster_size != 1 && cluster_size != 2 && cluster_size != 4)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: cluster size must be 0 (automatic), 1, 2 or 4, got %d", cluster_size);
+    wkv7_set_cluster_override(cluster_size);
+    return RWKV7_OK;
+}
+
 int64_t rwkv7_kernel_launch_count(void) { return launch_count(); }
 
 int rwkv7_read_device_status(int device, rwkv7_stream stream) {

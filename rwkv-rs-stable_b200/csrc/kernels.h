@@ -63,6 +63,10 @@ bool wkv7_chunked_supported(const Wkv7Args &p);
 int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream);
 
+// Cluster size of the chunked kernel: 0 = by the number of chains (default), else 1, 2 or 4.
+int wkv7_cluster_override();
+void wkv7_set_cluster_override(int k);
+
 // Training forward on the tensor cores (N == 64, bf16, chunk_len 16): the chunked kernel also
 // writing snapshots and state_replacement; same workspace as launch_wkv7_chunked.
 int launch_wkv7_chunked_saved(const Wkv7Args &p, void *workspace, float *snapshots, void *state_replacement,

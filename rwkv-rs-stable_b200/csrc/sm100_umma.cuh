@@ -126,6 +126,66 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, u
     return false;
 }
 
+// ---- thread-block clusters: distributed shared memory -------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void st_cluster_u4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+// Asynchronous 16-byte store into another CTA's shared memory that reports its bytes to an
+// mbarrier of that CTA when it lands: the sender neither waits nor fences.
+__device__ __forceinline__ void st_async_cluster_u4(uint32_t addr, uint4 v, uint32_t remote_bar_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(remote_bar_addr)
+                 : "memory");
+}
+// Bulk copy from this CTA's shared memory into another CTA's (addresses and size multiples of 16
+// bytes); the bytes are reported to an mbarrier of the destination CTA as they land.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t remote_dst, const void *local_src, uint32_t bytes,
+                                                 uint32_t remote_bar_addr) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(remote_dst), "r"(smem_u32(local_src)), "r"(bytes), "r"(remote_bar_addr)
+                 : "memory");
+}
+// Arrive on an mbarrier of another CTA of the cluster; orders this thread's earlier (remote) writes before it.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+}
+// Bounded wait on a local mbarrier that CTAs of the cluster arrive on (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, uint32_t max_polls = 2000000u) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < max_polls; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

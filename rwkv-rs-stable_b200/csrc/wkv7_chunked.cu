@@ -36,6 +36,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "kernels.h"
@@ -184,7 +185,15 @@ __device__ __forceinline__ void mma_ts_block(uint32_t d_tmem, uint32_t a_tmem, u
 // 16th token (snapshots [B,H,T/16,N,N], fp32) and state_replacement = U (sa_t = S_{t-1} a_t).  The
 // state update dS is then accumulated per 16-token block in four TMEM regions; the state after
 // token 16m-1 is diag(exp(c_{16m-1})) (Z0 + the first m blocks).
-template <bool SAVE>
+//
+// K > 1: a thread-block cluster of K CTAs shares one chain.  CTA rho owns the chunks
+// c = rho (mod K) with all their tiles; everything that does not depend on the incoming state
+// (phase A, G, the masks, the block inverses, the products with V) runs ahead, and only the state
+// travels: after its chunk a CTA writes the new state into the shared memory of the next CTA
+// (the tf32 operand tile, plus the bf16-rounded residual so that the fp32 state is rebuilt to
+// 2^-20) and arrives on that CTA's mbarrier.  For workloads with fewer chains than SMs this takes
+// the state-independent two thirds of a chunk off the serial path.
+template <bool SAVE, int K>
 __global__ void __launch_bounds__(kThreads, 1)
 wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     __nv_bfloat16 *__restrict__ y, float *s_out, int *__restrict__ flags,
@@ -205,6 +214,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
     uint64_t *bar_dep = bar_tma + 3;   // used by the MMA-issuing thread alone, between dependent MMAs
+    uint64_t *bar_state = bar_tma + 4; // K > 1: the previous CTA of the cluster has delivered the state
+    unsigned char *lo_buf = tXU + 2048;   // K > 1: [64][64] bf16 residual of the delivered state (8 KB)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc + 16);
     float *exp_cl = reinterpret_cast<float *>(smem + kOffMisc + 64);   // [2][64] exp(c_L), by chunk parity
     int *unsafe = reinterpret_cast<int *>(exp_cl + 128);
@@ -212,7 +223,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quarter = warp & 3;   // TMEM lane quarter this warp may read
     const int cgrp = warp >> 2;     // column group among the four warps of a quarter
-    const int bh = blockIdx.x;
+    static_assert(!(SAVE && K > 1), "the cluster variant does not write the training tensors");
+    const int rank = K > 1 ? (int)cluster_ctarank() : 0;
+    const int bh = blockIdx.x / K;
     const int bi = bh / H, h = bh % H;
     const int nchunks = (Tlen + kL - 1) / kL;
 
@@ -220,6 +233,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         mbar_init(bar_tma, 1);
         mbar_init(bar_mma, 1);
         mbar_init(bar_dep, 1);
+        mbar_init(bar_state, 1);   // armed by this CTA with the byte count of a delivered state
         mbar_fence_init();
         *unsafe = 0;
 #pragma unroll
@@ -231,6 +245,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    if constexpr (K > 1) cluster_sync_all();   // every CTA's barriers exist before anyone writes to a peer
 
     auto issue_tma = [&](int chunk) {
         mbar_expect_tx(bar_tma, kRawBytes);
@@ -238,12 +253,12 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
 #pragma unroll
         for (int i = 0; i < 6; ++i) tma_load_2d(raw + i * (kL * kN * 2), &maps.m[i], h * kN, row, bar_tma);
     };
-    if (tid == 0) issue_tma(0);
+    if (tid == 0 && rank < nchunks) issue_tma(rank);
 
     // fp32 state: the thread at TMEM lane i (< 64), column group g holds S[i][16g .. 16g+15].
     const int zj = quarter * 32 + lane;  // value row i, meaningful for quarter < 2
     float Z[16];
-    if (quarter < 2) {
+    if (quarter < 2 && rank == 0) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
             float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -264,20 +279,25 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                    dS = desc_kmajor(smem_u32(tS), 64, 0), dVT = desc_kmajor(smem_u32(tVT), 64, 0),
                    dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0);
     constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
-    uint32_t mma_phase = 0, dep_phase = 0;
+    uint32_t mma_phase = 0, dep_phase = 0, state_phase = 0;
     // TMEM columns of the dS accumulator of token block b (the last one reuses G's, dead by then)
     auto ds_col = [](int b) -> uint32_t { return !SAVE ? kColDS : (b == 3 ? kColG : kColDS + 64u * (uint32_t)b); };
     float *exp_sub = reinterpret_cast<float *>(tXU + 2048);   // [3][64] exp(c_15), exp(c_31), exp(c_47); SAVE only
     bool failed = false;
     int tma_issued = 1, tma_consumed = 0;  // tile batches requested / received
 
-    for (int chunk = 0; chunk < nchunks; ++chunk) {
+    int iter = 0;   // chunks this CTA has started
+    for (int chunk = rank; chunk < nchunks; chunk += K, ++iter) {
         const int valid = min(kL, Tlen - chunk * kL);
+        if constexpr (K > 1) {
+            // tf32 tile (16 KB) + bf16 residual (8 KB) will arrive from the previous CTA
+            if (tid == 0 && chunk > 0) mbar_expect_tx(bar_state, kN * kN * 6);
+        }
         // ---------------- wait for this chunk's six input tiles
         PHASE(0);
         // A wait that expires sets a sticky flag; every thread sees it after the next
         // CTA barrier and leaves the loop there, so no extra barrier is spent on it.
-        if (!mbar_wait(bar_tma, (uint32_t)(chunk & 1))) atomicOr(unsafe, 2);
+        if (!mbar_wait(bar_tma, (uint32_t)(iter & 1))) atomicOr(unsafe, 2);
         ++tma_consumed;
         // ---------------- phase A: decay prefix sums and scaled operands
         PHASE(1);
@@ -318,7 +338,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 if (g < tg) base += x;
             }
             if (tg == 7) {
-                exp_cl[(chunk & 1) * 64 + j] = __expf(total);
+                exp_cl[(iter & 1) * 64 + j] = __expf(total);
                 if (total < -kMaxLogDecay) atomicOr(unsafe, 1);
             }
             // Row t0 + u of a 128-row tile: t0 is a multiple of 8, so the swizzle term is u.
@@ -356,7 +376,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         }
         fence_proxy_async();
         __syncthreads();  // operands visible to the tensor core; raw tiles and group sums are dead
-        if (*unsafe) { failed = true; break; }
+        // A cluster keeps going on a decay flag (its chain is recomputed afterwards anyway): a CTA
+        // that left here would keep its successors waiting for a state.
+        if (K > 1 ? (*unsafe & 2) : *unsafe) { failed = true; break; }
         // ---------------- M1: G = [At;Rt] [Bh;Kh]^T
         PHASE(3);
         if (tid == 0) {
@@ -365,8 +387,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             umma_commit(bar_mma);
             // State path, part 1: value-major products (M = value index i, 64 valid lanes) that
             // need only this chunk's scaled operands.  They run while G is read back below.
-            mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
-            mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
+            if constexpr (K == 1) {
+                mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
+                mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
+            }
             if constexpr (!SAVE) mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
@@ -427,19 +451,20 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        if (*unsafe) { failed = true; break; }
+        if (K > 1 ? (*unsafe & 2) : *unsafe) { failed = true; break; }
         // ---------------- state path, part 2: the products with the masked A_ak, A_rk just
         // staged; they run on the tensor core while the diagonal blocks are inverted below.
         if (tid == 0) {
             tc_fence_after();
-            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, true);             // X^T += V^T A_ak^T
-            mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, true);    // Y^T += V^T A_rk^T
+            // (K > 1: the state has not arrived yet, these products start the accumulators)
+            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, K == 1);             // X^T (+)= V^T A_ak^T
+            mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, K == 1);    // Y^T (+)= V^T A_rk^T
             if constexpr (SAVE) {
 #pragma unroll
                 for (int b = 0; b < kL / kBlk; ++b)   // dS_b = V^T Kh over the tokens of block b (G is dead now)
                     mma_kpair<64, 128, 64>(tmem + ds_col(b), dVT, dZT + kLower, 2 * b);
             }
-            umma_commit(bar_dep);
+            if constexpr (K == 1) umma_commit(bar_dep);   // K > 1: one commit after the products with the state
         }
         // ---------------- U = (I - A_ab)^-1 X is solved block-wise with 16-token blocks:
         // only the diagonal blocks T_bb = (I - A_bb)^-1 are formed here (forward substitution
@@ -467,9 +492,29 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         }
         fence_proxy_async();
         __syncthreads();  // scratch matrices are dead: the raw-tile region may be refilled
-        if (chunk + 1 < nchunks) {
-            if (tid == 32) issue_tma(chunk + 1);   // not the thread that issues the MMAs
+        if (chunk + K < nchunks) {
+            if (tid == 32) issue_tma(chunk + K);   // not the thread that issues the MMAs
             ++tma_issued;
+        }
+        if constexpr (K > 1) {
+            // ---------------- the state arrives from the previous CTA of the cluster (the very
+            // first chunk of the chain starts from the initial state, staged above by rank 0)
+            PHASE(2);
+            if (chunk > 0) {
+                if (!mbar_wait_cluster(bar_state, state_phase)) atomicOr(unsafe, 2);
+                state_phase ^= 1;
+                if (quarter < 2) {   // fp32 state = delivered tf32 tile + bf16 residual
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const float4 hi = *reinterpret_cast<const float4 *>(tS + tile_off_f32(64, zj, cgrp * 16 + 4 * q4));
+                        const uint2 lo = *reinterpret_cast<const uint2 *>(lo_buf + (zj * kN + cgrp * 16 + 4 * q4) * 2);
+                        Z[4 * q4 + 0] = hi.x + __uint_as_float(lo.x << 16);
+                        Z[4 * q4 + 1] = hi.y + __uint_as_float(lo.x & 0xffff0000u);
+                        Z[4 * q4 + 2] = hi.z + __uint_as_float(lo.y << 16);
+                        Z[4 * q4 + 3] = hi.w + __uint_as_float(lo.y & 0xffff0000u);
+                    }
+                }
+            }
         }
         // ---------------- state path, part 3: the triangular solve and what depends on U.
         // X^T and U^T stay in TMEM and feed later MMAs as their A operand.  An MMA that
@@ -489,6 +534,13 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 mma_ts_block<64>(tmem + kColYT, tmem + kColUT + b * kBlk, dBK, 64, b * kBlk, kBlk / 8, true);   // A_rb
                 mma_ts_block<64>(tmem + ds_col(b), tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, kBlk / 8, true);    // Bh
             };
+            if constexpr (K > 1) {
+                // (the state tile was written by a bulk copy, i.e. through the async proxy the tensor
+                // core reads it with: no proxy fence is needed here)
+                mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, true);               // X^T += S At^T
+                dep_commit();   // completes after the products with V issued earlier, too
+                mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, true);      // Y^T += S Rt^T (not needed by the solve)
+            }
             dep_wait();   // parts 1 and 2 have finished: X^T is complete
             // U^T = X^T (I - A_ab)^-T by block forward substitution over the token blocks b:
             // X_b^T += U_{<b}^T A_{b,<b}^T, then U_b^T = X_b^T T_bb^T.
@@ -556,7 +608,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             uint32_t yv[16];
             tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
             tmem_ld_wait();
-            const float4 *g4 = reinterpret_cast<const float4 *>(exp_cl + (chunk & 1) * 64 + cgrp * 16);
+            const float4 *g4 = reinterpret_cast<const float4 *>(exp_cl + (iter & 1) * 64 + cgrp * 16);
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
                 const float4 g = g4[q4];
@@ -564,9 +616,40 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 Z[4 * q4 + 1] = g.y * (Z[4 * q4 + 1] + __uint_as_float(v[4 * q4 + 1]));
                 Z[4 * q4 + 2] = g.z * (Z[4 * q4 + 2] + __uint_as_float(v[4 * q4 + 2]));
                 Z[4 * q4 + 3] = g.w * (Z[4 * q4 + 3] + __uint_as_float(v[4 * q4 + 3]));
-                st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,   // operand of the next chunk
-                         make_float4(round_tf32(Z[4 * q4]), round_tf32(Z[4 * q4 + 1]), round_tf32(Z[4 * q4 + 2]),
-                                     round_tf32(Z[4 * q4 + 3])));
+                if constexpr (K == 1)
+                    st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,   // operand of the next chunk
+                             make_float4(round_tf32(Z[4 * q4]), round_tf32(Z[4 * q4 + 1]), round_tf32(Z[4 * q4 + 2]),
+                                         round_tf32(Z[4 * q4 + 3])));
+            }
+            if constexpr (K > 1) {
+                // The state leaves as the tf32 operand tile plus the residual Z - tf32(Z) in bf16, staged
+                // in this CTA's own (now idle) state tile and residual buffer and shipped below by two
+                // bulk copies.  Nobody writes into these buffers before the copies have been consumed:
+                // the state for this CTA's next chunk is produced by a chain of CTAs that starts at the
+                // consumer of these very copies.
+                unsigned lo[8];
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    float hi[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) hi[e] = round_tf32(Z[4 * q4 + e]);
+                    st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4, make_float4(hi[0], hi[1], hi[2], hi[3]));
+                    const __nv_bfloat162 l01 = __floats2bfloat162_rn(Z[4 * q4] - hi[0], Z[4 * q4 + 1] - hi[1]);
+                    const __nv_bfloat162 l23 = __floats2bfloat162_rn(Z[4 * q4 + 2] - hi[2], Z[4 * q4 + 3] - hi[3]);
+                    lo[2 * q4] = *reinterpret_cast<const unsigned *>(&l01);
+                    lo[2 * q4 + 1] = *reinterpret_cast<const unsigned *>(&l23);
+                }
+                uint4 *lo_dst = reinterpret_cast<uint4 *>(lo_buf + (zj * kN + cgrp * 16) * 2);
+                lo_dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                lo_dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                fence_proxy_async();   // the bulk copies read these buffers through the async proxy
+                asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight warps that hold the state
+                if (tid == 0 && chunk + 1 < nchunks) {
+                    const uint32_t peer = (uint32_t)((rank + 1) % K);
+                    const uint32_t peer_bar = map_to_cta(smem_u32(bar_state), peer);
+                    bulk_copy_to_cta(map_to_cta(smem_u32(tS), peer), tS, kN * kN * 4, peer_bar);
+                    bulk_copy_to_cta(map_to_cta(smem_u32(lo_buf), peer), lo_buf, kN * kN * 2, peer_bar);
+                }
             }
             if constexpr (SAVE) {
                 if (valid == kL) {   // the state after the chunk's last token is its fourth snapshot
@@ -596,8 +679,12 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     if (failed && tma_issued > tma_consumed) mbar_wait(bar_tma, (uint32_t)(tma_consumed & 1));
     const bool bad_decay = (*unsafe & 1) != 0;
     if (failed && !bad_decay && tid == 0) atomicExch(status, (int)kDevTimeout);
-    if (tid == 0) flags[bh] = bad_decay ? 1 : 0;
-    if (!failed && s_out != nullptr && quarter < 2) {
+    if constexpr (K == 1) {
+        if (tid == 0) flags[bh] = bad_decay ? 1 : 0;
+    } else {
+        if (tid == 0 && bad_decay) atomicOr(&flags[bh], 1);   // zeroed by the host before the launch
+    }
+    if (!failed && s_out != nullptr && quarter < 2 && (nchunks - 1) % K == rank) {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
             *reinterpret_cast<float4 *>(s_out + ((size_t)bh * kN + zj) * kN + cgrp * 16 + 4 * q4) =
@@ -606,6 +693,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+    // No CTA of a cluster may exit while a peer can still write into its shared memory.
+    if constexpr (K > 1) cluster_sync_all();
 }
 
 // ---- host side --------------------------------------------------------------------
@@ -690,6 +779,11 @@ bool wkv7_chunked_supported(const Wkv7Args &p) {
            aligned(p.b) && aligned(p.y) && p.B * p.T < (int64_t(1) << 31);
 }
 
+// 0 = choose by the number of chains, else the cluster size to use (1, 2 or 4).
+std::atomic<int> g_cluster_override{0};
+int wkv7_cluster_override() { return g_cluster_override.load(); }
+void wkv7_set_cluster_override(int k) { g_cluster_override.store(k); }
+
 int launch_wkv7_sequential_flagged_saved(const Wkv7Args &p, const int *flags, float *snapshots,
                                          void *state_replacement, int chunk_len, cudaStream_t stream);
 
@@ -712,20 +806,46 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
     int *status = nullptr;
     if (int e = device_status_ptr(p.device, &status)) return e;
     const bool save = snapshots != nullptr;
-    cudaError_t e = save ? cudaFuncSetAttribute(wkv7_chunked_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)kSmemBytes)
-                         : cudaFuncSetAttribute(wkv7_chunked_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                (int)kSmemBytes);
-    if (e != cudaSuccess) return (int)e;
     int *flags = static_cast<int *>(workspace);
-    if (save)
-        wkv7_chunked_kernel<true><<<(unsigned)(p.B * p.H), kThreads, kSmemBytes, stream>>>(
-            maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags, (int)p.T, (int)p.H, status, snapshots,
-            reinterpret_cast<__nv_bfloat16 *>(state_replacement));
-    else
-        wkv7_chunked_kernel<false><<<(unsigned)(p.B * p.H), kThreads, kSmemBytes, stream>>>(
-            maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags, (int)p.T, (int)p.H, status, nullptr,
-            nullptr);
+    const int64_t chains = p.B * p.H;
+    // Few chains: a cluster of CTAs per chain (needs at least one chunk per CTA to pay).
+    int cluster = 1;
+    if (!save) {
+        const int forced = wkv7_cluster_override();
+        const int64_t nchunks = (p.T + kL - 1) / kL;
+        if (forced > 0) cluster = forced;
+        else if (chains * 4 <= p.num_sms && nchunks >= 8) cluster = 4;
+        else if (chains * 2 <= p.num_sms && nchunks >= 4) cluster = 2;
+    }
+    cudaError_t e;
+    auto launch = [&](auto kern, int k) -> cudaError_t {
+        cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (err != cudaSuccess) return err;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(chains * k));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)k;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = k > 1 ? 1 : 0;
+        return cudaLaunchKernelEx(&cfg, kern, maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags,
+                                  (int)p.T, (int)p.H, status, snapshots,
+                                  reinterpret_cast<__nv_bfloat16 *>(state_replacement));
+    };
+    if (cluster > 1) {
+        e = cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)chains, stream);   // CTAs of a cluster only ever set a flag
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (save) e = launch(wkv7_chunked_kernel<true, 1>, 1);
+    else if (cluster == 4) e = launch(wkv7_chunked_kernel<false, 4>, 4);
+    else if (cluster == 2) e = launch(wkv7_chunked_kernel<false, 2>, 2);
+    else e = launch(wkv7_chunked_kernel<false, 1>, 1);
+    if (e != cudaSuccess) return (int)e;
     count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;

@@ -293,3 +293,44 @@ def test_expired_bounded_wait_is_reported_and_the_device_stays_usable(pkg, workl
     assert torch.isfinite(out.float()).all() and pkg.read_device_status(0) == 0
     with pytest.raises(pkg.KernelInputsError):
         pkg.selftest_bounded_wait(0, max_polls=0)
+
+
+@pytest.mark.parametrize("cluster", [2, 4])
+@pytest.mark.parametrize("shape,state", [((1, 512, 2, 64), "normal"), ((2, 200, 3, 64), None), ((1, 64, 1, 64), "normal"),
+                                         ((1, 1024, 4, 64), "normal")])
+def test_cluster_pipeline_matches_single_cta(pkg, oracle, workloads, cuda, shape, state, cluster):
+    """Small-batch prefill: a cluster of CTAs per chain passing the state through distributed shared
+    memory.  Same arithmetic as the one-CTA kernel except that the fp32 state crosses CTAs as a tf32
+    tile plus a bf16 residual (2^-20 relative): results agree with the single-CTA kernel far inside
+    the 1e-3 parity bound, and with the oracle within it.  T = 200 ends in a partial chunk; T = 64 has
+    fewer chunks than CTAs in the cluster."""
+    inp = workloads.wkv7_inputs(*shape, seed=33, dtype=torch.bfloat16, state=state)
+    y_ref, s_ref = _oracle(oracle, inp)
+    if state is None:
+        inp["s0"] = torch.zeros(shape[0], shape[2], 64, 64)
+    one_y, one_s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+    pkg.set_wkv7_cluster(cluster)
+    try:
+        y, s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+    finally:
+        pkg.set_wkv7_cluster(0)
+    assert pkg.read_device_status(0) == 0
+    parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s, s_ref, 1e-3, "state")
+    assert parity.headline(s, one_s) <= 2e-5
+
+
+def test_cluster_pipeline_falls_back_outside_decay_range(pkg, oracle, workloads, cuda):
+    inp = workloads.wkv7_inputs(2, 256, 2, 64, seed=34, dtype=torch.bfloat16, state="normal")
+    w = inp["w"].float()
+    w[0] = torch.rand_like(w[0]) + 0.5
+    inp["w"] = w.to(torch.bfloat16)
+    y_ref, s_ref = _oracle(oracle, inp)
+    pkg.set_wkv7_cluster(2)
+    try:
+        y, s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+    finally:
+        pkg.set_wkv7_cluster(0)
+    assert pkg.read_device_status(0) == 0
+    parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s, s_ref, 1e-3, "state")
