@@ -370,7 +370,9 @@ class Wkv7HostStatepass:
     its kernel and its device-to-host copies, so the copy of one slice overlaps
     the kernel and the copy-back of the slices before it.  (b,h) chains are
     independent, so slicing the batch changes no arithmetic: results are bitwise
-    those of one call on the whole batch.
+    those of one call on the whole batch whenever both run the same variant of the
+    kernel (a slice with at most half as many chains as the GPU has SMs takes the
+    cluster variant, whose state hand-off differs in the last bits).
 
     ``host_state_in`` may be None (S0 = 0).  Device staging buffers for
     ``n_streams`` slices are allocated once, here; ``__call__`` allocates nothing.
