@@ -121,7 +121,7 @@ def cpu_baseline(oracle, workloads, torch, budget_s: float = 12.0):
     """Times the fp32 CPU oracle (the restatement of the reference's CPU path) on a
     bounded sample of configuration 1: all T = 4096 tokens of as many (b,h) chains
     as fit the time budget, one chain per host thread at a time."""
-    threads = oracle.num_threads()
+    threads = oracle.use_all_cores()
     probe = workloads.wkv7_inputs(1, 256, threads, 64, seed=1, dtype=torch.bfloat16)
     f = [probe[n].float().numpy() for n in "rwkvab"]
     oracle.wkv7(*f, None, precision="f32")
@@ -160,7 +160,7 @@ def run_reference(args):
     oracle.build()
     entry.load_package()
     from rwkv_rs_stable_b200 import workloads
-    threads = oracle.num_threads()
+    threads = oracle.use_all_cores()
     # One step = all T tokens of `threads` chains (a bounded sample of the 96 chains).
     inp = workloads.wkv7_inputs(1, CFG1["T"], threads, 64, seed=1, dtype=torch.bfloat16)
     f = [inp[n].float().numpy() for n in "rwkvab"]

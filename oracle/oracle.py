@@ -44,6 +44,13 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Sets the OpenMP thread count to the cores this process may run on (launchers such as
+    torchrun export OMP_NUM_THREADS=1); returns the count in force."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return int(lib().oracle_set_num_threads(ctypes.c_int(cores)))
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 

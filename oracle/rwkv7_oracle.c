@@ -57,6 +57,18 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* A launcher may have set OMP_NUM_THREADS=1 for its workers (torchrun does); the timed CPU
+ * baseline asks for the host's cores explicitly.  Returns the count now in force. */
+int oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------ wkv7 -- */
 
 /*
