@@ -784,6 +784,37 @@ std::atomic<int> g_cluster_override{0};
 int wkv7_cluster_override() { return g_cluster_override.load(); }
 void wkv7_set_cluster_override(int k) { g_cluster_override.store(k); }
 
+// How many clusters of `k` CTAs of the (one CTA per SM) chunked kernel can be resident on `device`;
+// queried once per device and cluster size.
+static int max_resident_clusters(int device, int k) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static int cached[kMaxDevices][5] = {};
+    if (device < 0 || device >= kMaxDevices || (k != 2 && k != 4)) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[device][k] == 0) {
+        auto kern = k == 4 ? (const void *)wkv7_chunked_kernel<false, 4> : (const void *)wkv7_chunked_kernel<false, 2>;
+        int n = 0;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(k * 64));
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = kSmemBytes;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)k;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) n = 0;
+        }
+        (void)cudaGetLastError();
+        cached[device][k] = n > 0 ? n : -1;
+    }
+    return cached[device][k] > 0 ? cached[device][k] : 0;
+}
+
 int launch_wkv7_sequential_flagged_saved(const Wkv7Args &p, const int *flags, float *snapshots,
                                          void *state_replacement, int chunk_len, cudaStream_t stream);
 
@@ -813,9 +844,11 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
     if (!save) {
         const int forced = wkv7_cluster_override();
         const int64_t nchunks = (p.T + kL - 1) / kL;
+        // A cluster must fit one GPC, so fewer clusters are resident than SMs / K (on a 148-SM B200:
+        // 74 of two, 33 of four): all chains must be resident at once or the launch runs in waves.
         if (forced > 0) cluster = forced;
-        else if (chains * 4 <= p.num_sms && nchunks >= 8) cluster = 4;
-        else if (chains * 2 <= p.num_sms && nchunks >= 4) cluster = 2;
+        else if (nchunks >= 8 && chains <= max_resident_clusters(p.device, 4)) cluster = 4;
+        else if (nchunks >= 4 && chains <= max_resident_clusters(p.device, 2)) cluster = 2;
     }
     cudaError_t e;
     auto launch = [&](auto kern, int k) -> cudaError_t {
