@@ -487,16 +487,18 @@ def main():
         seq_bytes = B * T * H * N * 2
         snap_bytes = B * H * (T // 16) * N * N * 4
         fwd_ms = timed(lambda: pkg.wkv7_forward_saved(tin, None, want_state=True))
-        bwd_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None))
+        bws = torch.empty(pkg.wkv7_backward_workspace_bytes(B, T, H, N), dtype=torch.uint8, device=dev)
+        bwd_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None, workspace=bws))
+        bwd_seq_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None, parallel=False), reps=2)
         fwd_bytes = 8 * seq_bytes + snap_bytes + B * H * STATE_BYTES             # 6 in, y and sa out, snapshots, S_T
         bwd_bytes = 14 * seq_bytes + snap_bytes + B * H * STATE_BYTES            # 6 in, sa, dy, 6 grads, snapshots, dS0
         train = {"workload": f"B={B} T={T} H={H} N={N} bf16, chunk_len 16",
                  "forward_saved_ms": fwd_ms, "forward_saved_gb_per_s": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                  "forward_saved_frac_of_hbm_peak": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak_gbs,
-                 "backward_ms": bwd_ms, "backward_gb_per_s": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
+                 "backward_ms": bwd_ms, "backward_token_by_token_ms": bwd_seq_ms, "backward_gb_per_s": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
                  "backward_frac_of_hbm_peak": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak_gbs,
                  "forward_algorithmic_bytes": fwd_bytes, "backward_algorithmic_bytes": bwd_bytes}
-        del saved, dy
+        del saved, dy, bws
 
     # ---- channel mixer at the configuration-2 layer shape (two tensor-core projections) ---
     channel_mixer = None

@@ -252,6 +252,29 @@ int rwkv7_fused_wkv7_backward(const rwkv7_tensor *initial_state, const rwkv7_ten
                               rwkv7_tensor *const sequence_grads[6],
                               rwkv7_tensor *initial_state_grad, rwkv7_stream stream);
 
+/*
+ * The same gradients in time-parallel form; no counterpart in the reference, whose backward
+ * kernel takes T dependent steps per (b,h) chain.  The recurrence of the state gradient is a
+ * forward WKV7 recurrence over the reversed sequence (decay w_t, removal key b_t, replacement
+ * a_t, value dy_t, key r_t d_t + (r_t.b_t) a_t, starting from next_state_grad), so it runs on
+ * the tensor-core prefill kernel; its saved tensors then let every 16-token chunk be finished
+ * independently of all others.  Taken for BF16 tensors with N = 64, chunk_len 16 and T >= 64;
+ * any other shape is handled exactly like rwkv7_fused_wkv7_backward and needs no workspace.
+ * workspace: rwkv7_wkv7_backward_workspace_bytes(B,T,H,N) bytes, 256-byte aligned, borrowed
+ * until the enqueued work has finished (0 is returned for shapes that need none).
+ */
+size_t rwkv7_wkv7_backward_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+int rwkv7_fused_wkv7_backward_parallel(const rwkv7_tensor *initial_state, const rwkv7_tensor *receptance,
+                                       const rwkv7_tensor *weight_decay, const rwkv7_tensor *replacement_key,
+                                       const rwkv7_tensor *value,
+                                       const rwkv7_tensor *removal_key_normalized,
+                                       const rwkv7_tensor *replacement, const rwkv7_tensor *snapshots,
+                                       const rwkv7_tensor *state_replacement, int64_t chunk_len,
+                                       const rwkv7_tensor *output_grad, const rwkv7_tensor *next_state_grad,
+                                       rwkv7_tensor *const sequence_grads[6],
+                                       rwkv7_tensor *initial_state_grad, void *workspace,
+                                       size_t workspace_bytes, rwkv7_stream stream);
+
 /* ------------------------------------------------------------------ mix6 -- */
 /* Replaces Mix6Backend::fused_mix6 (mix6/mod.rs:25-28, impl :42-73; kernel
  * mix6/kernel.rs:25-57): prev = x[b,t-1,:] (0 at t == 0);

@@ -88,6 +88,8 @@ def lib() -> ctypes.CDLL:
         L.rwkv7_lm_head_ce_workspace_bytes.argtypes = [ctypes.c_int64] * 3
         L.rwkv7_channel_mixer_workspace_bytes.restype = ctypes.c_size_t
         L.rwkv7_channel_mixer_workspace_bytes.argtypes = [ctypes.c_int64] * 4
+        L.rwkv7_wkv7_backward_workspace_bytes.restype = ctypes.c_size_t
+        L.rwkv7_wkv7_backward_workspace_bytes.argtypes = [ctypes.c_int64] * 4
         _lib = L
     return _lib
 
@@ -318,11 +320,22 @@ def wkv7_forward_saved(inputs: Wkv7PretrainForwardInputs, initial_state: Optiona
     return Wkv7SavedForward(output=y, next_state=s_out, snapshots=snaps, state_replacement=sa)
 
 
+def wkv7_backward_workspace_bytes(B: int, T: int, H: int, N: int) -> int:
+    """``rwkv7_wkv7_backward_workspace_bytes``: workspace of the time-parallel backward (0 when the shape
+    takes the token-by-token kernel)."""
+    return int(lib().rwkv7_wkv7_backward_workspace_bytes(ctypes.c_int64(B), ctypes.c_int64(T), ctypes.c_int64(H),
+                                                         ctypes.c_int64(N)))
+
+
 def wkv7_backward(inputs: Wkv7PretrainForwardInputs, saved: Wkv7SavedForward, output_grad: torch.Tensor,
                   next_state_grad: Optional[torch.Tensor] = None, *, initial_state: Optional[torch.Tensor] = None,
-                  want_state_grad: bool = True):
-    """``rwkv7_fused_wkv7_backward``: returns ``(six sequence gradients in input order,
-    initial_state_grad or None)`` (``Wkv7BackwardPrimitiveOutputs``, ``wkv7/backward.rs:567-575``)."""
+                  want_state_grad: bool = True, parallel: bool = True, workspace: Optional[torch.Tensor] = None):
+    """``rwkv7_fused_wkv7_backward_parallel`` (``parallel=True``: the gradient recurrence as a tensor-core
+    forward pass over the reversed sequence, the rest per 16-token chunk; shapes it does not cover fall
+    through to the token-by-token kernel) or ``rwkv7_fused_wkv7_backward``.  Returns ``(six sequence
+    gradients in input order, initial_state_grad or None)`` (``Wkv7BackwardPrimitiveOutputs``,
+    ``wkv7/backward.rs:567-575``).  ``workspace``: a uint8 tensor of ``wkv7_backward_workspace_bytes``;
+    allocated here when omitted."""
     r = inputs.receptance
     B, T, H, N = r.shape
     grads = [torch.empty_like(r) for _ in range(6)]
@@ -332,6 +345,14 @@ def wkv7_backward(inputs: Wkv7PretrainForwardInputs, saved: Wkv7SavedForward, ou
     descs = [describe(initial_state)] + [describe(t) for t in inputs.six()] + [describe(saved.snapshots),
                                                                             describe(saved.state_replacement)]
     dyd, dsd, ds0d = describe(output_grad.contiguous()), describe(next_state_grad), describe(ds0)
+    if parallel and r.dtype == torch.bfloat16:
+        need = wkv7_backward_workspace_bytes(B, T, H, N)
+        if workspace is None:
+            workspace = torch.empty(max(need, 1), dtype=torch.uint8, device=r.device)
+        _check(lib().rwkv7_fused_wkv7_backward_parallel(
+            *[_ref(d) for d in descs], ctypes.c_int64(inputs.chunk_len), _ref(dyd), _ref(dsd), arr, _ref(ds0d),
+            ctypes.c_void_p(workspace.data_ptr()), ctypes.c_size_t(workspace.numel()), _stream(r)))
+        return grads, ds0
     _check(lib().rwkv7_fused_wkv7_backward(*[_ref(d) for d in descs], ctypes.c_int64(inputs.chunk_len), _ref(dyd),
                                            _ref(dsd), arr, _ref(ds0d), _stream(r)))
     return grads, ds0

@@ -415,12 +415,48 @@ int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *s0, const rwkv7_tensor *r
     return RWKV7_OK;
 }
 
+size_t rwkv7_wkv7_backward_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
+    if (B <= 0 || T <= 0 || H <= 0) return 0;
+    return wkv7_backward_parallel_workspace_bytes(B, T, H, N);
+}
+
+static int wkv7_backward_impl(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, const rwkv7_tensor *w,
+                              const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                              const rwkv7_tensor *b, const rwkv7_tensor *snapshots, const rwkv7_tensor *state_replacement,
+                              int64_t chunk_len, const rwkv7_tensor *output_grad,
+                              const rwkv7_tensor *next_state_grad, rwkv7_tensor *const sequence_grads[6],
+                              rwkv7_tensor *initial_state_grad, bool parallel, void *workspace, size_t workspace_bytes,
+                              rwkv7_stream stream);
+
 int rwkv7_fused_wkv7_backward(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, const rwkv7_tensor *w,
                               const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
                               const rwkv7_tensor *b, const rwkv7_tensor *snapshots, const rwkv7_tensor *state_replacement,
                               int64_t chunk_len, const rwkv7_tensor *output_grad,
                               const rwkv7_tensor *next_state_grad, rwkv7_tensor *const sequence_grads[6],
                               rwkv7_tensor *initial_state_grad, rwkv7_stream stream) {
+    return wkv7_backward_impl(s0, r_t, w, k, v, a, b, snapshots, state_replacement, chunk_len, output_grad,
+                              next_state_grad, sequence_grads, initial_state_grad, false, nullptr, 0, stream);
+}
+
+int rwkv7_fused_wkv7_backward_parallel(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, const rwkv7_tensor *w,
+                                       const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                                       const rwkv7_tensor *b, const rwkv7_tensor *snapshots,
+                                       const rwkv7_tensor *state_replacement, int64_t chunk_len,
+                                       const rwkv7_tensor *output_grad, const rwkv7_tensor *next_state_grad,
+                                       rwkv7_tensor *const sequence_grads[6], rwkv7_tensor *initial_state_grad,
+                                       void *workspace, size_t workspace_bytes, rwkv7_stream stream) {
+    return wkv7_backward_impl(s0, r_t, w, k, v, a, b, snapshots, state_replacement, chunk_len, output_grad,
+                              next_state_grad, sequence_grads, initial_state_grad, true, workspace, workspace_bytes,
+                              stream);
+}
+
+static int wkv7_backward_impl(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, const rwkv7_tensor *w,
+                              const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
+                              const rwkv7_tensor *b, const rwkv7_tensor *snapshots, const rwkv7_tensor *state_replacement,
+                              int64_t chunk_len, const rwkv7_tensor *output_grad,
+                              const rwkv7_tensor *next_state_grad, rwkv7_tensor *const sequence_grads[6],
+                              rwkv7_tensor *initial_state_grad, bool parallel, void *workspace, size_t workspace_bytes,
+                              rwkv7_stream stream) {
     clear_error();
     const rwkv7_tensor *six_t[6] = {r_t, w, k, v, a, b};
     TensorInfo six[6];
@@ -461,6 +497,20 @@ int rwkv7_fused_wkv7_backward(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, c
                                            "head size N=%lld exceeds 64", (long long)p.N);
     DeviceGuard guard(r_t->device);
     if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    if (parallel && wkv7_backward_parallel_supported(p)) {
+        // (shapes outside the time-parallel form take the token-by-token kernel below)
+        const size_t need = wkv7_backward_parallel_workspace_bytes(p.B, p.T, p.H, p.N);
+        if (workspace == nullptr || workspace_bytes < need)
+            return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: wkv7 backward needs %zu workspace bytes, got %zu",
+                        need, workspace == nullptr ? (size_t)0 : workspace_bytes);
+        if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+            return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: the backward workspace must be 256-byte aligned");
+        int sms = 0;
+        RWKV7_TRY(num_sms(r_t->device, &sms));
+        if (int e = launch_wkv7_backward_parallel(p, workspace, r_t->device, sms, (cudaStream_t)stream))
+            return cuda_fail("wkv7 backward (time-parallel) launch", e);
+        return RWKV7_OK;
+    }
     if (int e = launch_wkv7_backward(p, (cudaStream_t)stream)) return cuda_fail("wkv7 backward launch", e);
     return RWKV7_OK;
 }

@@ -57,6 +57,14 @@ struct Wkv7BackwardArgs {
 };
 int launch_wkv7_backward(const Wkv7BackwardArgs &p, cudaStream_t stream);
 
+// Time-parallel backward (N == 64, bf16, chunk_len 16, T >= 64): the gradient recurrence runs as a
+// forward pass of the tensor-core prefill kernel over the reversed sequence, everything else per
+// 16-token chunk.  Needs wkv7_backward_parallel_workspace_bytes of workspace.
+bool wkv7_backward_parallel_supported(const Wkv7BackwardArgs &p);
+size_t wkv7_backward_parallel_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+int launch_wkv7_backward_parallel(const Wkv7BackwardArgs &p, void *workspace, int device, int num_sms,
+                                  cudaStream_t stream);
+
 // Chunked tensor-core prefill (N == 64): tcgen05 MMAs with TMEM accumulators.
 size_t wkv7_chunked_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 bool wkv7_chunked_supported(const Wkv7Args &p);

@@ -107,6 +107,57 @@ def test_backward_against_oracle(pkg, oracle, workloads, cuda, shape, state, dty
     _grads_close(ds0, ref["s0"], tol, "ds0")
 
 
+@pytest.mark.parametrize("shape,state,state_grad", [((1, 64, 2, 64), True, True), ((1, 80, 2, 64), True, False),
+                                                    ((2, 256, 3, 64), False, True), ((1, 1040, 1, 64), True, True)])
+def test_time_parallel_backward(pkg, oracle, workloads, cuda, shape, state, state_grad):
+    """bf16, N = 64, chunk_len 16, T >= 64: the gradient recurrence runs as a tensor-core forward pass over
+    the reversed sequence and every 16-token chunk is finished on its own.  Checked against the fp64 oracle
+    (1e-2 of each gradient's largest magnitude, the bound of the bf16 token-by-token kernel) and against
+    that kernel; T = 80 and 1040 leave the prefill kernel a partial 64-token chunk."""
+    B, T, H, N = shape
+    inp = workloads.wkv7_inputs(*shape, seed=47, dtype=torch.bfloat16, state="normal" if state else None)
+    gen = torch.Generator().manual_seed(11)
+    dy = torch.randn(B, T, H, N, generator=gen).to(torch.bfloat16)
+    ds = torch.randn(B, H, N, N, generator=gen) if state_grad else None
+    f = {n: inp[n].float().numpy() for n in inp}
+    ref = oracle.wkv7_backward(*[f[n] for n in "rwkvab"], dy.float().numpy(), s0=f.get("s0"),
+                               ds_out=None if ds is None else ds.numpy())
+    g = {n: t.to(cuda) for n, t in inp.items()}
+    inputs = pkg.Wkv7PretrainForwardInputs(*[g[n] for n in "rwkvab"])
+    saved = pkg.wkv7_forward_saved(inputs, g.get("s0"), want_state=True)
+    need = pkg.wkv7_backward_workspace_bytes(B, T, H, N)
+    assert need > 0
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+    dsg = None if ds is None else ds.to(cuda)
+    grads, ds0 = pkg.wkv7_backward(inputs, saved, dy.to(cuda), dsg, initial_state=g.get("s0"), workspace=ws)
+    seq_grads, seq_ds0 = pkg.wkv7_backward(inputs, saved, dy.to(cuda), dsg, initial_state=g.get("s0"), parallel=False)
+    torch.cuda.synchronize()
+    assert pkg.read_device_status(0) == 0
+    for name, got, seq in zip("rwkvab", grads, seq_grads):
+        _grads_close(got, ref[name], 1e-2, f"d{name}")
+        _grads_close(got, seq.float().cpu().numpy().astype(np.float64), 1e-2, f"d{name} against the token-by-token kernel")
+    _grads_close(ds0, ref["s0"], 1e-2, "ds0")
+    with pytest.raises(pkg.KernelInputsError) as e:
+        pkg.wkv7_backward(inputs, saved, dy.to(cuda), dsg, initial_state=g.get("s0"), workspace=ws[: need // 2])
+    assert e.value.kind == "WorkspaceTooSmall"
+
+
+def test_time_parallel_backward_small_decay(pkg, oracle, workloads, cuda):
+    """Decays far below the range the chunked kernel scales safely (the reference's U[0,1) test inputs at
+    N = 64): the reversed run falls back to the sequential scan for those chains; gradients still match."""
+    B, T, H, N = 1, 64, 2, 64
+    gen = torch.Generator().manual_seed(12)
+    six = [(torch.rand(B, T, H, N, generator=gen) * (0.2 if i in (4, 5) else 1.0)).to(torch.bfloat16) for i in range(6)]
+    dy = torch.randn(B, T, H, N, generator=gen).to(torch.bfloat16)
+    ref = oracle.wkv7_backward(*[t.float().numpy() for t in six], dy.float().numpy())
+    inputs = pkg.Wkv7PretrainForwardInputs(*[t.to(cuda) for t in six])
+    saved = pkg.wkv7_forward_saved(inputs, None, want_state=True)
+    grads, _ = pkg.wkv7_backward(inputs, saved, dy.to(cuda), None)
+    torch.cuda.synchronize()
+    for name, got in zip("rwkvab", grads):
+        _grads_close(got, ref[name], 1e-2, f"d{name}")
+
+
 def test_autograd_wrapper_with_state(pkg, oracle, workloads, cuda):
     inp = workloads.wkv7_inputs(1, 32, 2, 64, seed=44, state="normal")
     leaves = {n: inp[n].to(cuda).requires_grad_(True) for n in list("rwkvab") + ["s0"]}
