@@ -98,16 +98,41 @@ struct LocalArgs {
 enum { RU = 0, RV, RDY, RDSA, kRowVecs };          // vectors indexed by the value row i
 enum { CD = 0, CR, CK, CA, CB, CEW, kColVecs };    // vectors indexed by the key column j
 enum { ODR = 0, ODA, ODK, ODB, ODW, kOutVecs };
-constexpr int kRowPitch = 72;   // floats per row vector: the upper 32 rows start 4 floats later (bank spread)
-__device__ __forceinline__ int row_slot(int i) { return i + ((i >> 5) << 2); }
 
-constexpr size_t kLocalSmemFloats = (size_t)kRowVecs * kC * kRowPitch + (size_t)(kColVecs + kOutVecs) * kC * kN + 2 * kN;
+constexpr size_t kLocalSmemFloats = (size_t)(kRowVecs + kColVecs + kOutVecs) * kC * kN + 2 * kN;
 constexpr int kLocalThreads = 256;
 
+// Sums `acc` (two kinds x four columns) over the eight row groups of a warp (lane bits 2..4) so that
+// every lane ends up with one total: kind = lane bit 4, column = 2 * bit 3 + bit 2.
+__device__ __forceinline__ float reduce_scatter_rows(const float (&acc)[2][4], int lane) {
+    float h4[4];
+    const bool k1 = lane & 16;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const float send = k1 ? acc[0][c] : acc[1][c];
+        h4[c] = (k1 ? acc[1][c] : acc[0][c]) + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+    float h2[2];
+    const bool c2 = lane & 8;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        const float send = c2 ? h4[c] : h4[2 + c];
+        h2[c] = (c2 ? h4[2 + c] : h4[c]) + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    const bool c1 = lane & 4;
+    const float send = c1 ? h2[0] : h2[1];
+    return (c1 ? h2[1] : h2[0]) + __shfl_xor_sync(0xffffffffu, send, 4);
+}
+
+// 256 threads: warps 0..3 replay S forwards, warps 4..7 replay Gh backwards.  Within a pass a warp
+// owns 16 key columns and a thread a block of 8 value rows x 4 key columns of the matrix
+// (lane = column group + 4 * row group): a row-indexed vector element is then shared by four
+// columns and a column-indexed one by eight rows, which keeps the shared-memory traffic (the bound
+// of a one-column-per-thread layout) at a quarter.
 __global__ void __launch_bounds__(kLocalThreads, 3) wkv7_bwd_local_kernel(LocalArgs p) {
     extern __shared__ __align__(16) float sm[];
-    float *rowv = sm;                                     // [4][16][72]
-    float *colv = rowv + kRowVecs * kC * kRowPitch;       // [6][16][64]
+    float *rowv = sm;                                     // [4][16][64]
+    float *colv = rowv + kRowVecs * kC * kN;              // [6][16][64]
     float *outv = colv + kColVecs * kC * kN;              // [5][16][64]
     float *phi_end = outv + kOutVecs * kC * kN;           // [64]
     float *dv_last = phi_end + kN;                        // [64]  next_state_grad k_{T-1}
@@ -118,19 +143,30 @@ __global__ void __launch_bounds__(kLocalThreads, 3) wkv7_bwd_local_kernel(LocalA
     const int bi = bh / p.H, h = bh % p.H;
     const bool last_chunk = q == nq - 1;
 
-    // ---- this thread's matrix column: S-pass warps 0..3, G-pass warps 4..7
+    // ---- this thread's block of its pass's matrix
     const bool g_pass = warp >= 4;
-    const int j = (warp & 3) * 16 + (lane & 15);   // key column
-    const int rh = lane >> 4;                      // row half
-    const float *msrc;
-    if (!g_pass) msrc = q == 0 ? p.initial_state + (p.initial_state ? (size_t)bh * kN * kN : 0)
-                               : p.snapshots + ((size_t)bh * nq + (q - 1)) * kN * kN;
-    else msrc = last_chunk ? p.next_state_grad + (p.next_state_grad ? (size_t)bh * kN * kN : 0)
-                           : p.grad_snapshots + ((size_t)bh * nq + (nq - q - 2)) * kN * kN;
-    const bool mzero = !g_pass ? (q == 0 && p.initial_state == nullptr) : (last_chunk && p.next_state_grad == nullptr);
-    float M[32];
+    const int j0 = (warp & 3) * 16 + (lane & 3) * 4;   // first key column
+    const int i0 = (lane >> 2) * 8;                    // first value row
+    const float *s_src = (q == 0) ? p.initial_state : p.snapshots;
+    const size_t s_off = (q == 0) ? (size_t)bh * kN * kN : ((size_t)bh * nq + (q - 1)) * kN * kN;
+    const float *g_src = last_chunk ? p.next_state_grad : p.grad_snapshots;
+    const size_t g_off = last_chunk ? (size_t)bh * kN * kN : ((size_t)bh * nq + (nq - q - 2)) * kN * kN;
+    const float *msrc = g_pass ? g_src : s_src;
+    const size_t moff = g_pass ? g_off : s_off;
+    // Rows are held in pairs, M[rp][c] = (row 2 rp, row 2 rp + 1) of column c: the replays below use the
+    // packed fp32 instructions of sm_100 (two FMAs per issue slot), and a pair of consecutive
+    // elements of a row-indexed vector is what a 16-byte shared-memory load delivers.
+    float2 M[4][4];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) M[i] = mzero ? 0.f : msrc[(size_t)(32 * rh + i) * kN + j];
+    for (int rp = 0; rp < 4; ++rp) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f), y = x;
+        if (msrc != nullptr) {
+            x = *reinterpret_cast<const float4 *>(msrc + moff + (size_t)(i0 + 2 * rp) * kN + j0);
+            y = *reinterpret_cast<const float4 *>(msrc + moff + (size_t)(i0 + 2 * rp + 1) * kN + j0);
+        }
+        M[rp][0] = make_float2(x.x, y.x); M[rp][1] = make_float2(x.y, y.y);
+        M[rp][2] = make_float2(x.z, y.z); M[rp][3] = make_float2(x.w, y.w);
+    }
 
     // ---- prologue: the chunk's vectors, 16 lanes per token, four channels per lane
     const int tt = tid >> 4, c4 = tid & 15;
@@ -153,7 +189,7 @@ __global__ void __launch_bounds__(kLocalThreads, 3) wkv7_bwd_local_kernel(LocalA
         const float4 dv4 = make_float4(__expf(-ew.x), __expf(-ew.y), __expf(-ew.z), __expf(-ew.w));
         auto colp = [&](int x) { return reinterpret_cast<float4 *>(colv + (x * kC + tt) * kN + 4 * c4); };
         *colp(CD) = dv4; *colp(CR) = rv; *colp(CK) = kv; *colp(CA) = av; *colp(CB) = bv; *colp(CEW) = ew;
-        auto rowp = [&](int x) { return reinterpret_cast<float4 *>(rowv + (x * kC + tt) * kRowPitch + row_slot(4 * c4)); };
+        auto rowp = [&](int x) { return reinterpret_cast<float4 *>(rowv + (x * kC + tt) * kN + 4 * c4); };
         *rowp(RU) = uv; *rowp(RV) = vv; *rowp(RDY) = dyv;
         *rowp(RDSA) = make_float4(sav.x + dyv.x * rb, sav.y + dyv.y * rb, sav.z + dyv.z * rb, sav.w + dyv.w * rb);
         dvv = make_float4(ghk.x + dyv.x * rk, ghk.y + dyv.y * rk, ghk.z + dyv.z * rk, ghk.w + dyv.w * rk);
@@ -161,108 +197,142 @@ __global__ void __launch_bounds__(kLocalThreads, 3) wkv7_bwd_local_kernel(LocalA
     if (tid < kN) dv_last[tid] = 0.f;
     __syncthreads();
 
-    const float *rbase = rowv + row_slot(32 * rh);
+    // rows i0 + 4 half .. + 3 of a row-indexed vector, as two row pairs
+    auto row4 = [&](int x, int t, int half, float2 (&o)[2]) {
+        const float4 f = *reinterpret_cast<const float4 *>(rowv + (x * kC + t) * kN + i0 + 4 * half);
+        o[0] = make_float2(f.x, f.y); o[1] = make_float2(f.z, f.w);
+    };
+    // columns j0 .. j0 + 3 of a column-indexed vector, each duplicated for the two rows of a pair
+    auto col4 = [&](int x, int t, float2 (&o)[4]) {
+        const float4 f = *reinterpret_cast<const float4 *>(colv + (x * kC + t) * kN + j0);
+        o[0] = make_float2(f.x, f.x); o[1] = make_float2(f.y, f.y); o[2] = make_float2(f.z, f.z); o[3] = make_float2(f.w, f.w);
+    };
+    // where this lane's total of a reduce_scatter_rows lands
+    const int out_kind = (lane >> 4) & 1;
+    const int out_j = j0 + 2 * ((lane >> 3) & 1) + ((lane >> 2) & 1);
+
     if (!g_pass) {
         // ---- S-pass, forwards: da_t = S_{t-1}^T dsa_t, then the step, then dr_t = S_t^T dy_t
 #pragma unroll 1
         for (int t = 0; t < kC; ++t) {
-            const float dj = colv[(CD * kC + t) * kN + j], bj = colv[(CB * kC + t) * kN + j], kj = colv[(CK * kC + t) * kN + j];
-            float acc_a = 0.f, acc_r = 0.f;
+            float2 d[4], bb[4], kk[4];
+            col4(CD, t, d); col4(CB, t, bb); col4(CK, t, kk);
+            float2 acc_a[4] = {}, acc_r[4] = {};
 #pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                const float4 ds = *reinterpret_cast<const float4 *>(rbase + (RDSA * kC + t) * kRowPitch + 4 * m);
-                const float4 u4 = *reinterpret_cast<const float4 *>(rbase + (RU * kC + t) * kRowPitch + 4 * m);
-                const float4 v4 = *reinterpret_cast<const float4 *>(rbase + (RV * kC + t) * kRowPitch + 4 * m);
-                const float4 y4 = *reinterpret_cast<const float4 *>(rbase + (RDY * kC + t) * kRowPitch + 4 * m);
-                const float dsv[4] = {ds.x, ds.y, ds.z, ds.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w},
-                            vv[4] = {v4.x, v4.y, v4.z, v4.w}, yy[4] = {y4.x, y4.y, y4.z, y4.w};
+            for (int half = 0; half < 2; ++half) {
+                float2 ds[2], uu[2], vv[2], yy[2];
+                row4(RDSA, t, half, ds); row4(RU, t, half, uu); row4(RV, t, half, vv); row4(RDY, t, half, yy);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float s = M[4 * m + e];
-                    acc_a = fmaf(s, dsv[e], acc_a);
-                    s = fmaf(s, dj, fmaf(uu[e], bj, vv[e] * kj));
-                    acc_r = fmaf(s, yy[e], acc_r);
-                    M[4 * m + e] = s;
-                }
+                for (int pr = 0; pr < 2; ++pr)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float2 s2 = M[2 * half + pr][c];
+                        acc_a[c] = __ffma2_rn(s2, ds[pr], acc_a[c]);
+                        s2 = __ffma2_rn(s2, d[c], __ffma2_rn(uu[pr], bb[c], __fmul2_rn(vv[pr], kk[c])));
+                        acc_r[c] = __ffma2_rn(s2, yy[pr], acc_r[c]);
+                        M[2 * half + pr][c] = s2;
+                    }
             }
-            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 16);
-            acc_r += __shfl_xor_sync(0xffffffffu, acc_r, 16);
-            if (rh == 0) outv[(ODA * kC + t) * kN + j] = acc_a;
-            else outv[(ODR * kC + t) * kN + j] = acc_r;
+            float acc[2][4];   // [0]: da, [1]: dr
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { acc[0][c] = acc_a[c].x + acc_a[c].y; acc[1][c] = acc_r[c].x + acc_r[c].y; }
+            const float total = reduce_scatter_rows(acc, lane);
+            outv[((out_kind ? ODR : ODA) * kC + t) * kN + out_j] = total;
         }
         // phi at the chunk's end: colsum(Gh_end . S_end)
-        const float *gsrc = last_chunk ? p.next_state_grad + (p.next_state_grad ? (size_t)bh * kN * kN : 0)
-                                       : p.grad_snapshots + ((size_t)bh * nq + (nq - q - 2)) * kN * kN;
-        float phi = 0.f;
-        if (!(last_chunk && p.next_state_grad == nullptr)) {
+        float phi[4] = {0.f, 0.f, 0.f, 0.f};
+        if (g_src != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) phi = fmaf(gsrc[(size_t)(32 * rh + i) * kN + j], M[i], phi);
+            for (int r = 0; r < 8; ++r) {
+                const float4 g = *reinterpret_cast<const float4 *>(g_src + g_off + (size_t)(i0 + r) * kN + j0);
+                const float gg[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) phi[c] = fmaf(gg[c], (r & 1) ? M[r >> 1][c].y : M[r >> 1][c].x, phi[c]);
+            }
         }
-        phi += __shfl_xor_sync(0xffffffffu, phi, 16);
-        if (rh == 0) phi_end[j] = phi;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) phi[c] += __shfl_xor_sync(0xffffffffu, phi[c], o);
+        }
+        if ((lane >> 2) == 0) *reinterpret_cast<float4 *>(phi_end + j0) = make_float4(phi[0], phi[1], phi[2], phi[3]);
     } else {
         // ---- G-pass, backwards: G_t = Gh_t + dy_t r_t^T, dk_t, db_t, then Gh_{t-1}
         if (last_chunk && p.next_state_grad != nullptr) {
             // the last token's dv also needs next_state_grad k_{T-1} (no later token produces it)
-            const float kj = colv[(CK * kC + kC - 1) * kN + j];
+            float2 kk[4];
+            col4(CK, kC - 1, kk);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float x = sum16(M[i] * kj);
-                if ((lane & 15) == 0) atomicAdd(&dv_last[32 * rh + i], x);
+            for (int r = 0; r < 8; ++r) {
+                float x = 0.f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) x = fmaf((r & 1) ? M[r >> 1][c].y : M[r >> 1][c].x, kk[c].x, x);
+                x += __shfl_xor_sync(0xffffffffu, x, 1);
+                x += __shfl_xor_sync(0xffffffffu, x, 2);
+                if ((lane & 3) == 0) atomicAdd(&dv_last[i0 + r], x);
             }
         }
 #pragma unroll 1
         for (int t = kC - 1; t >= 0; --t) {
-            const float dj = colv[(CD * kC + t) * kN + j], rj = colv[(CR * kC + t) * kN + j], aj = colv[(CA * kC + t) * kN + j];
-            float acc_k = 0.f, acc_b = 0.f;
+            float2 d[4], rr[4], aa[4];
+            col4(CD, t, d); col4(CR, t, rr); col4(CA, t, aa);
+            float2 acc_k[4] = {}, acc_b[4] = {};
 #pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                const float4 ds = *reinterpret_cast<const float4 *>(rbase + (RDSA * kC + t) * kRowPitch + 4 * m);
-                const float4 u4 = *reinterpret_cast<const float4 *>(rbase + (RU * kC + t) * kRowPitch + 4 * m);
-                const float4 v4 = *reinterpret_cast<const float4 *>(rbase + (RV * kC + t) * kRowPitch + 4 * m);
-                const float4 y4 = *reinterpret_cast<const float4 *>(rbase + (RDY * kC + t) * kRowPitch + 4 * m);
-                const float dsv[4] = {ds.x, ds.y, ds.z, ds.w}, uu[4] = {u4.x, u4.y, u4.z, u4.w},
-                            vv[4] = {v4.x, v4.y, v4.z, v4.w}, yy[4] = {y4.x, y4.y, y4.z, y4.w};
+            for (int half = 0; half < 2; ++half) {
+                float2 ds[2], uu[2], vv[2], yy[2];
+                row4(RDSA, t, half, ds); row4(RU, t, half, uu); row4(RV, t, half, vv); row4(RDY, t, half, yy);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float g = fmaf(yy[e], rj, M[4 * m + e]);
-                    acc_k = fmaf(g, vv[e], acc_k);
-                    acc_b = fmaf(g, uu[e], acc_b);
-                    M[4 * m + e] = fmaf(g, dj, dsv[e] * aj);
-                }
+                for (int pr = 0; pr < 2; ++pr)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float2 g2 = __ffma2_rn(yy[pr], rr[c], M[2 * half + pr][c]);
+                        acc_k[c] = __ffma2_rn(g2, vv[pr], acc_k[c]);
+                        acc_b[c] = __ffma2_rn(g2, uu[pr], acc_b[c]);
+                        M[2 * half + pr][c] = __ffma2_rn(g2, d[c], __fmul2_rn(ds[pr], aa[c]));
+                    }
             }
-            acc_k += __shfl_xor_sync(0xffffffffu, acc_k, 16);
-            acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 16);
-            if (rh == 0) outv[(ODK * kC + t) * kN + j] = acc_k;
-            else outv[(ODB * kC + t) * kN + j] = acc_b;
+            float acc[2][4];   // [0]: dk, [1]: db
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { acc[0][c] = acc_k[c].x + acc_k[c].y; acc[1][c] = acc_b[c].x + acc_b[c].y; }
+            const float total = reduce_scatter_rows(acc, lane);
+            outv[((out_kind ? ODB : ODK) * kC + t) * kN + out_j] = total;
         }
     }
     __syncthreads();
 
-    // ---- decay gradient: d_t dd_t from phi, one channel per thread
-    if (tid < kN) {
-        float phi = phi_end[tid];
-#pragma unroll 1
-        for (int t = kC - 1; t >= 0; --t) {
-            const int o = t * kN + tid;
-            const float ddd = phi - colv[CB * kC * kN + o] * outv[ODB * kC * kN + o] - colv[CK * kC * kN + o] * outv[ODK * kC * kN + o] +
-                              colv[CR * kC * kN + o] * outv[ODR * kC * kN + o];
-            outv[ODW * kC * kN + o] = -colv[CEW * kC * kN + o] * ddd;
-            phi = fmaf(colv[CA * kC * kN + o], outv[ODA * kC * kN + o], ddd);
-        }
-    }
-    __syncthreads();
-
-    // ---- gradients of (token tt, channels 4 c4 ..) leave as bf16
+    // ---- decay gradient.  With x_t = b_t db_t + k_t dk_t - r_t dr_t and z_t = x_t - a_t da_t the two
+    // identities give phi_{t-1} = phi_t - z_t, so d_t dd_t = phi_end - sum_{s>t} z_s - x_t: a suffix sum
+    // over the chunk, taken by every (token, four channels) thread for itself.
     auto st4 = [&](__nv_bfloat16 *base, float4 x) {
         *reinterpret_cast<uint2 *>(base + tok * kN + 4 * c4) = float4_to_bf16x4(x);
     };
-    auto outp = [&](int x) { return *reinterpret_cast<const float4 *>(outv + (x * kC + tt) * kN + 4 * c4); };
-    st4(p.dr, outp(ODR));
-    st4(p.dw, outp(ODW));
-    st4(p.dk, outp(ODK));
-    st4(p.da, outp(ODA));
-    st4(p.db, outp(ODB));
+    auto outp = [&](int x, int t) { return reinterpret_cast<float4 *>(outv + (x * kC + t) * kN + 4 * c4); };
+    auto colq = [&](int x) { return *reinterpret_cast<const float4 *>(colv + (x * kC + tt) * kN + 4 * c4); };
+    float4 xs;
+    {
+        const float4 gr = *outp(ODR, tt), ga = *outp(ODA, tt), gk = *outp(ODK, tt), gb = *outp(ODB, tt);
+        const float4 rv = colq(CR), kv = colq(CK), av = colq(CA), bv = colq(CB);
+        xs = make_float4(bv.x * gb.x + kv.x * gk.x - rv.x * gr.x, bv.y * gb.y + kv.y * gk.y - rv.y * gr.y,
+                         bv.z * gb.z + kv.z * gk.z - rv.z * gr.z, bv.w * gb.w + kv.w * gk.w - rv.w * gr.w);
+        *outp(ODW, tt) = make_float4(xs.x - av.x * ga.x, xs.y - av.y * ga.y, xs.z - av.z * ga.z, xs.w - av.w * ga.w);
+        st4(p.dr, gr);
+        st4(p.dk, gk);
+        st4(p.da, ga);
+        st4(p.db, gb);
+    }
+    __syncthreads();
+    {
+        float4 ph = *reinterpret_cast<const float4 *>(phi_end + 4 * c4);
+#pragma unroll
+        for (int s2 = kC - 1; s2 > 0; --s2) {
+            if (s2 > tt) {
+                const float4 z = *outp(ODW, s2);
+                ph.x -= z.x; ph.y -= z.y; ph.z -= z.z; ph.w -= z.w;
+            }
+        }
+        const float4 ew = colq(CEW);
+        st4(p.dw, make_float4(-ew.x * (ph.x - xs.x), -ew.y * (ph.y - xs.y), -ew.z * (ph.z - xs.z), -ew.w * (ph.w - xs.w)));
+    }
     if (last_chunk && tt == kC - 1) {
         const float4 x = *reinterpret_cast<const float4 *>(dv_last + 4 * c4);
         dvv = make_float4(dvv.x + x.x, dvv.y + x.y, dvv.z + x.z, dvv.w + x.w);
