@@ -123,6 +123,60 @@ inline void wkv7_statepass_custom(const Wkv7StatepassForwardInputs &in, Wkv7Stat
                                             ws.data, ws.bytes, stream));
 }
 
+// ---- training: the tensors the autodiff nodes keep, and the backward pass ---------------------
+// What launch_wkv7_*_forward returns under autodiff (wkv7/forward.rs:290-302) and what
+// Wkv7BackwardState keeps (wkv7/backward.rs:549-559).
+struct Wkv7SavedForward {
+    TensorView output, next_state;             // next_state may be empty (pretrain, statetune)
+    TensorView snapshots, state_replacement;   // F32 [B,H,T/chunk_len,N,N]; [B,T,H,N] like the inputs
+};
+
+// Forward pass of an autodiff node; initial_state may be empty (pretrain: S0 = 0).
+inline void wkv7_forward_saved(const Wkv7StatepassForwardInputs &in, Wkv7SavedForward &out, Workspace ws = {},
+                               rwkv7_stream stream = nullptr) {
+    const auto &s = in.sequence;
+    check_status(rwkv7_fused_wkv7_forward_saved(
+        in.initial_state.t.data ? in.initial_state.c() : nullptr, s.receptance.c(), s.weight_decay.c(),
+        s.replacement_key.c(), s.value.c(), s.removal_key_normalized.c(), s.replacement.c(), s.chunk_len,
+        out.output.m(), out.next_state.t.data ? out.next_state.m() : nullptr, out.snapshots.m(),
+        out.state_replacement.m(), ws.data, ws.bytes, stream));
+}
+
+// Wkv7BackwardPrimitiveOutputs (wkv7/backward.rs:567-575); initial_state_grad may be empty.
+struct Wkv7BackwardOutputs {
+    TensorView receptance_grad, weight_decay_grad, replacement_key_grad, value_grad, removal_key_normalized_grad,
+        replacement_grad, initial_state_grad;
+};
+
+inline size_t wkv7_backward_workspace_bytes(const Wkv7PretrainForwardInputs &in) {
+    const rwkv7_tensor &r = in.receptance.t;
+    return r.ndim == 4 ? rwkv7_wkv7_backward_workspace_bytes(r.shape[0], r.shape[1], r.shape[2], r.shape[3]) : 0;
+}
+
+// launch_wkv7_backward (wkv7/backward.rs:583-703).  in.initial_state is the state the forward started from
+// (empty = zero); next_state_grad may be empty (zero).  With a workspace of wkv7_backward_workspace_bytes the
+// time-parallel form is used where it applies; without one, the token-by-token kernel.
+inline void wkv7_backward(const Wkv7StatepassForwardInputs &in, const Wkv7SavedForward &saved,
+                          const TensorView &output_grad, const TensorView &next_state_grad, Wkv7BackwardOutputs &out,
+                          Workspace ws = {}, rwkv7_stream stream = nullptr) {
+    const auto &s = in.sequence;
+    rwkv7_tensor *grads[6] = {out.receptance_grad.m(), out.weight_decay_grad.m(), out.replacement_key_grad.m(),
+                              out.value_grad.m(), out.removal_key_normalized_grad.m(), out.replacement_grad.m()};
+    const rwkv7_tensor *s0 = in.initial_state.t.data ? in.initial_state.c() : nullptr;
+    const rwkv7_tensor *dst = next_state_grad.t.data ? next_state_grad.c() : nullptr;
+    rwkv7_tensor *ds0 = out.initial_state_grad.t.data ? out.initial_state_grad.m() : nullptr;
+    if (ws.data != nullptr)
+        check_status(rwkv7_fused_wkv7_backward_parallel(
+            s0, s.receptance.c(), s.weight_decay.c(), s.replacement_key.c(), s.value.c(), s.removal_key_normalized.c(),
+            s.replacement.c(), saved.snapshots.c(), saved.state_replacement.c(), s.chunk_len, output_grad.c(), dst,
+            grads, ds0, ws.data, ws.bytes, stream));
+    else
+        check_status(rwkv7_fused_wkv7_backward(
+            s0, s.receptance.c(), s.weight_decay.c(), s.replacement_key.c(), s.value.c(), s.removal_key_normalized.c(),
+            s.replacement.c(), saved.snapshots.c(), saved.state_replacement.c(), s.chunk_len, output_grad.c(), dst,
+            grads, ds0, stream));
+}
+
 // mix6/io.rs:20-46, 110-124: scales and outputs in the order receptance, weight_decay, key, value,
 // learning_rate, gate.
 struct Mix6ForwardInputs {

@@ -83,6 +83,22 @@ int main() {
         expect_error("token_shift_diff shape_mismatch_panics", "ShapeMismatch", "embedded_token_shift",
                      [&] { token_shift_diff_custom(x, state, ids, diff); });
     }
+    {   // training: snapshots of the wrong shape, and a backward workspace that is too small
+        Wkv7StatepassForwardInputs in{TensorView(), seq({1, 32, 1, 8})};
+        Wkv7SavedForward saved{f32({1, 32, 1, 8}), TensorView(), f32({1, 1, 3, 8, 8}), f32({1, 32, 1, 8})};
+        expect_error("wkv7 forward_saved snapshots shape", "ShapeMismatch", "snapshots",
+                     [&] { wkv7_forward_saved(in, saved); });
+        saved.snapshots = f32({1, 1, 2, 8, 8});
+        auto dy = f32({1, 32, 1, 8});
+        Wkv7BackwardOutputs out{f32({1, 32, 1, 8}), f32({1, 32, 1, 8}), f32({1, 32, 1, 8}), f32({1, 32, 1, 4}),
+                                f32({1, 32, 1, 8}), f32({1, 32, 1, 8}), TensorView()};
+        expect_error("wkv7 backward value_grad shape", "ShapeMismatch", "value_grad",
+                     [&] { wkv7_backward(in, saved, dy, TensorView(), out); });
+        if (wkv7_backward_workspace_bytes(seq({2, 128, 2, 64})) == 0 || wkv7_backward_workspace_bytes(in.sequence) != 0) {
+            std::printf("FAIL backward workspace size\n");
+            ++failures;
+        }
+    }
     std::printf("%d failure(s)\n", failures);
     return failures ? 1 : 0;
 }
