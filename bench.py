@@ -289,11 +289,12 @@ def main():
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_value = tokens_per_step / (float(te.item()) / e2e_steps * 1e-3)
     h2d, d2h = e2e_step.bytes_per_call()
-    # Same arithmetic; a batch slice has few enough chains for the cluster variant of the kernel,
-    # which carries the state between CTAs as tf32 + bf16 residual, hence a tolerance, not equality.
+    # A batch slice has few enough chains for the cluster-of-4 variant of the kernel, which applies the
+    # triangular inverse as one precomputed operand (a different, equally accurate rounding path: both
+    # are 2-3e-4 from the fp64 oracle and 1.1-1.6e-4 from each other), hence a tolerance, not equality.
     y_dev, s_dev = y.float().cpu(), s_out.cpu()
     if not ((y_host.float() - y_dev).abs().max() <= 1e-3 * y_dev.abs().max() + 2 ** -8 * y_dev.abs().max()
-            and (s_host - s_dev).abs().max() <= 1e-4 * s_dev.abs().max()):
+            and (s_host - s_dev).abs().max() <= 5e-4 * s_dev.abs().max()):
         raise SystemExit("end-to-end result differs from the device-resident call")
 
     # ---- decode: one layer-step of configuration 3 (B=1024, H=40), state in place --

@@ -90,6 +90,11 @@ static_assert(kOffAm + 64 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch 
 
 // TMEM columns.
 constexpr uint32_t kColG = 0, kColXT = 128, kColUT = 192, kColYT = 256, kColDS = 320, kTmemCols = 512;
+constexpr uint32_t kColTX = 384, kColTT = 448;   // cluster of 4: the solve applied to the identity (never with SAVE)
+// Identity operand tile [64][64] of that product, inside the raw-tile region past the inverse scratch.
+constexpr uint32_t kOffIdent = kOffRaw + 8192;
+static_assert(kOffAm + 64 * kPitch * 4 <= kOffIdent && kOffIdent + 16384 + 8192 <= kOffRaw + kRawBytes,
+              "identity tile (read as a 128-row operand) must stay inside the raw-tile region");
 
 // Optional per-phase cycle counters (development builds only): thread 0 of CTA 0
 // adds the cycles spent since the previous mark to the slot of the phase that
@@ -224,6 +229,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     const int quarter = warp & 3;   // TMEM lane quarter this warp may read
     const int cgrp = warp >> 2;     // column group among the four warps of a quarter
     static_assert(!(SAVE && K > 1), "the cluster variant does not write the training tensors");
+    // Cluster of 4: a CTA has three chunk periods of slack, so it also applies the block solve to the
+    // identity ahead of time.  T = (I - A_ab)^-1 then sits in shared memory as one operand tile and
+    // the state-dependent part of the solve shrinks from eight dependent MMA steps to one.
+    constexpr bool kFullInv = (K == 4);
     const int rank = K > 1 ? (int)cluster_ctarank() : 0;
     const int bh = blockIdx.x / K;
     const int bi = bh / H, h = bh % H;
@@ -490,11 +499,75 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 *reinterpret_cast<float *>(tBK + tile_off_f32(128, 16 * b + t, 16 * b + cc)) = round_tf32(x[t] * kDebias);
             }
         }
+        if constexpr (kFullInv) {
+            if (tid >= 128) {   // identity tile for X^T := I, next to the scratch of the block inverses
+                unsigned char *ident = smem + kOffIdent;
+                for (int idx = tid - 128; idx < kN * kN / 4; idx += kThreads - 128) {
+                    const int row = idx >> 4, c0 = (idx & 15) * 4;
+                    st_tile4(ident, 64, row, c0,
+                             make_float4(row == c0 ? 1.f : 0.f, row == c0 + 1 ? 1.f : 0.f, row == c0 + 2 ? 1.f : 0.f,
+                                         row == c0 + 3 ? 1.f : 0.f));
+                }
+            }
+        }
         fence_proxy_async();
         __syncthreads();  // scratch matrices are dead: the raw-tile region may be refilled
-        if (chunk + K < nchunks) {
-            if (tid == 32) issue_tma(chunk + K);   // not the thread that issues the MMAs
-            ++tma_issued;
+        if constexpr (!kFullInv) {
+            if (chunk + K < nchunks) {
+                if (tid == 32) issue_tma(chunk + K);   // not the thread that issues the MMAs
+                ++tma_issued;
+            }
+        } else {
+            // ---------------- T^T = I (I - A_ab)^-T by the same block substitution, before the state is
+            // needed; the raw-tile region is refilled once the identity tile has been read.
+            if (tid == 0) {
+                auto dep_commit = [&]() { umma_commit(bar_dep); };
+                auto dep_wait = [&]() {
+                    if (!mbar_wait_spin(bar_dep, dep_phase)) atomicOr(unsafe, 2);
+                    dep_phase ^= 1;
+                    tc_fence_after();
+                };
+                tc_fence_after();
+                const uint64_t dI = desc_kmajor(smem_u32(smem + kOffIdent), 64, 0);
+                mma_k64<64, 64, 64>(tmem + kColTX, dI, dI, false);
+                dep_commit();
+                dep_wait();
+                if (chunk + K < nchunks) issue_tma(chunk + K);
+#pragma unroll
+                for (int b = 0; b < kL / kBlk; ++b) {
+                    if (b > 0) {
+                        mma_ts_block<kBlk>(tmem + kColTX + b * kBlk, tmem + kColTT, dBK, b * kBlk, 0, b * kBlk / 8, true);
+                        dep_commit();
+                        dep_wait();
+                    }
+                    mma_ts_block<kBlk>(tmem + kColTT + b * kBlk, tmem + kColTX + b * kBlk, dBK, b * kBlk, b * kBlk,
+                                       kBlk / 8, false);
+                    if (b + 1 < kL / kBlk) {
+                        dep_commit();
+                        dep_wait();
+                    }
+                }
+                umma_commit(bar_mma);
+            }
+            if (chunk + K < nchunks) ++tma_issued;
+            __syncwarp();
+            if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
+            mma_phase ^= 1;
+            tc_fence_after();
+            // T^T (lane s, column t) -> rows t of the [T;A_rb] tile, replacing A_ab and the block inverses.
+            // No debias factor here: the identity is exact as a TMEM operand, so the factor carried by
+            // the block inverses and by A_ab has come through once, which is what U^T = X^T T^T needs.
+            if (quarter < 2) {
+                uint32_t tv[16];
+                tmem_ld16(tmem + lane_base + kColTT + cgrp * 16, tv);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    st_tile(tBK, 128, cgrp * 16 + e, zj, round_tf32(__uint_as_float(tv[e])));
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            __syncthreads();
         }
         if constexpr (K > 1) {
             // ---------------- the state arrives from the previous CTA of the cluster (the very
@@ -542,10 +615,17 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, true);      // Y^T += S Rt^T (not needed by the solve)
             }
             dep_wait();   // parts 1 and 2 have finished: X^T is complete
+            if constexpr (kFullInv) {
+                mma_k64_ts<128, 64>(tmem + kColUT, tmem + kColXT, dBK, false);            // U^T = X^T T^T
+                dep_commit();
+                dep_wait();
+                mma_k64_ts<128, 64>(tmem + kColYT, tmem + kColUT, dBK + kLower, true);    // Y^T += U^T A_rb^T
+                mma_k64_ts<128, 64>(tmem + kColDS, tmem + kColUT, dZT, true);             // dS  += U^T Bh
+            }
             // U^T = X^T (I - A_ab)^-T by block forward substitution over the token blocks b:
             // X_b^T += U_{<b}^T A_{b,<b}^T, then U_b^T = X_b^T T_bb^T.
 #pragma unroll
-            for (int b = 0; b < kL / kBlk; ++b) {
+            for (int b = 0; b < (kFullInv ? 0 : kL / kBlk); ++b) {
                 if (b > 0) {
                     mma_ts_block<kBlk>(tmem + kColXT + b * kBlk, tmem + kColUT, dBK, b * kBlk, 0, b * kBlk / 8, true);
                     dep_commit();
@@ -557,7 +637,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 dep_commit();
                 dep_wait();
             }
-            leaves(kL / kBlk - 1);
+            if constexpr (!kFullInv) leaves(kL / kBlk - 1);
             umma_commit(bar_mma);
         }
         // The other lanes of the issuing warp must not poll the barrier below while lane 0 is

@@ -300,24 +300,29 @@ def test_expired_bounded_wait_is_reported_and_the_device_stays_usable(pkg, workl
                                          ((1, 1024, 4, 64), "normal")])
 def test_cluster_pipeline_matches_single_cta(pkg, oracle, workloads, cuda, shape, state, cluster):
     """Small-batch prefill: a cluster of CTAs per chain passing the state through distributed shared
-    memory.  Same arithmetic as the one-CTA kernel except that the fp32 state crosses CTAs as a tf32
-    tile plus a bf16 residual (2^-20 relative): results agree with the single-CTA kernel far inside
-    the 1e-3 parity bound, and with the oracle within it.  T = 200 ends in a partial chunk; T = 64 has
-    fewer chunks than CTAs in the cluster."""
+    memory.  A cluster of 2 does the arithmetic of the one-CTA kernel except for the order in which two
+    products meet in their accumulator and the way the fp32 state crosses CTAs (a tf32 tile plus a bf16
+    residual, 2^-20 relative): it agrees with the one-CTA kernel to a few 1e-5 of the largest state entry
+    (measured 0.7-3.7e-5).  A cluster of 4 also forms the whole inverse of the
+    triangular system ahead of time (the block solve applied to the identity) and applies it in one
+    product: a different, equally accurate rounding path (measured against the oracle: 1.9-3.1e-4 of
+    the largest state entry for both), so it agrees with the one-CTA kernel to a few 1e-4 only.
+    T = 200 ends in a partial chunk; T = 64 has fewer chunks than CTAs in the cluster."""
     inp = workloads.wkv7_inputs(*shape, seed=33, dtype=torch.bfloat16, state=state)
     y_ref, s_ref = _oracle(oracle, inp)
     if state is None:
         inp["s0"] = torch.zeros(shape[0], shape[2], 64, 64)
-    one_y, one_s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
-    pkg.set_wkv7_cluster(cluster)
     try:
+        pkg.set_wkv7_cluster(1)   # (left to itself the launcher would pick a cluster for these few chains)
+        one_y, one_s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+        pkg.set_wkv7_cluster(cluster)
         y, s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
     finally:
         pkg.set_wkv7_cluster(0)
     assert pkg.read_device_status(0) == 0
     parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
     parity.assert_close_f32(s, s_ref, 1e-3, "state")
-    assert parity.headline(s, one_s) <= 2e-5
+    assert parity.headline(s, one_s) <= (1e-4 if cluster == 2 else 4e-4)
 
 
 def test_cluster_pipeline_falls_back_outside_decay_range(pkg, oracle, workloads, cuda):
