@@ -218,6 +218,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     float *grp_tot = reinterpret_cast<float *>(tXU);  // [8][64], phase A only
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
+    uint64_t *bar_y = bar_tma + 2;     // cluster of 4: Y^T is complete (the state leaves before y is stored)
     uint64_t *bar_dep = bar_tma + 3;   // used by the MMA-issuing thread alone, between dependent MMAs
     uint64_t *bar_state = bar_tma + 4; // K > 1: the previous CTA of the cluster has delivered the state
     unsigned char *lo_buf = tXU + 2048;   // K > 1: [64][64] bf16 residual of the delivered state (8 KB)
@@ -241,6 +242,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     if (tid == 0) {
         mbar_init(bar_tma, 1);
         mbar_init(bar_mma, 1);
+        mbar_init(bar_y, 1);
         mbar_init(bar_dep, 1);
         mbar_init(bar_state, 1);   // armed by this CTA with the byte count of a delivered state
         mbar_fence_init();
@@ -288,7 +290,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                    dS = desc_kmajor(smem_u32(tS), 64, 0), dVT = desc_kmajor(smem_u32(tVT), 64, 0),
                    dAKRK = desc_kmajor(smem_u32(tAKRK), 128, 0);
     constexpr uint64_t kLower = (64 * 128) >> 4;   // rows 64..127 of a stacked 128-row tile
-    uint32_t mma_phase = 0, dep_phase = 0, state_phase = 0;
+    uint32_t mma_phase = 0, dep_phase = 0, state_phase = 0, y_phase = 0;
     // TMEM columns of the dS accumulator of token block b (the last one reuses G's, dead by then)
     auto ds_col = [](int b) -> uint32_t { return !SAVE ? kColDS : (b == 3 ? kColG : kColDS + 64u * (uint32_t)b); };
     float *exp_sub = reinterpret_cast<float *>(tXU + 2048);   // [3][64] exp(c_15), exp(c_31), exp(c_47); SAVE only
@@ -520,6 +522,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         } else {
             // ---------------- T^T = I (I - A_ab)^-T by the same block substitution, before the state is
             // needed; the raw-tile region is refilled once the identity tile has been read.
+            PHASE(7);
             if (tid == 0) {
                 auto dep_commit = [&]() { umma_commit(bar_dep); };
                 auto dep_wait = [&]() {
@@ -554,6 +557,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
             mma_phase ^= 1;
             tc_fence_after();
+            PHASE(8);
             // T^T (lane s, column t) -> rows t of the [T;A_rb] tile, replacing A_ab and the block inverses.
             // No debias factor here: the identity is exact as a TMEM operand, so the factor carried by
             // the block inverses and by A_ab has come through once, which is what U^T = X^T T^T needs.
@@ -619,8 +623,11 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 mma_k64_ts<128, 64>(tmem + kColUT, tmem + kColXT, dBK, false);            // U^T = X^T T^T
                 dep_commit();
                 dep_wait();
-                mma_k64_ts<128, 64>(tmem + kColYT, tmem + kColUT, dBK + kLower, true);    // Y^T += U^T A_rb^T
+                // the state update first: the next CTA waits for it, nobody waits for y
                 mma_k64_ts<128, 64>(tmem + kColDS, tmem + kColUT, dZT, true);             // dS  += U^T Bh
+                umma_commit(bar_mma);
+                mma_k64_ts<128, 64>(tmem + kColYT, tmem + kColUT, dBK + kLower, true);    // Y^T += U^T A_rb^T
+                umma_commit(bar_y);
             }
             // U^T = X^T (I - A_ab)^-T by block forward substitution over the token blocks b:
             // X_b^T += U_{<b}^T A_{b,<b}^T, then U_b^T = X_b^T T_bb^T.
@@ -637,8 +644,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 dep_commit();
                 dep_wait();
             }
-            if constexpr (!kFullInv) leaves(kL / kBlk - 1);
-            umma_commit(bar_mma);
+            if constexpr (!kFullInv) {
+                leaves(kL / kBlk - 1);
+                umma_commit(bar_mma);
+            }
         }
         // The other lanes of the issuing warp must not poll the barrier below while lane 0 is
         // still issuing: a suspended poll would stall lane 0's own waits between dependent MMAs.
@@ -686,7 +695,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 tmem_ld16(tmem + lane_base + kColDS + cgrp * 16, v);
             }
             uint32_t yv[16];
-            tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
+            if constexpr (!kFullInv) tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
             tmem_ld_wait();
             const float4 *g4 = reinterpret_cast<const float4 *>(exp_cl + (iter & 1) * 64 + cgrp * 16);
 #pragma unroll
@@ -739,12 +748,20 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                         *reinterpret_cast<float4 *>(sn + 4 * q4) = make_float4(Z[4 * q4], Z[4 * q4 + 1], Z[4 * q4 + 2], Z[4 * q4 + 3]);
                 }
             }
+            if constexpr (kFullInv) {   // Y^T was issued after the state update and completes here
+                PHASE(9);
+                if (!mbar_wait(bar_y, y_phase)) atomicOr(unsafe, 2);
+                tc_fence_after();
+                tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
+                tmem_ld_wait();
+            }
             // y[t][i]: this thread holds value channel i = zj for tokens 16*cgrp .. +15
             __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + cgrp * 16) * H + h) * kN + zj;
 #pragma unroll
             for (int e = 0; e < 16; ++e)
                 if (cgrp * 16 + e < valid) dst[(size_t)e * H * kN] = __float2bfloat16_rn(__uint_as_float(yv[e]));
         }
+        if constexpr (kFullInv) y_phase ^= 1;
         // No CTA barrier here: the next chunk's phase A touches neither TMEM nor any
         // buffer this hop reads (exp(c_L) is kept per chunk parity), and its own
         // barriers come before the next MMA that overwrites the accumulators read above.
