@@ -659,6 +659,28 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         PHASE(11);
         if (quarter < 2) {
             uint32_t v[16];
+            // SAVE: a snapshot leaves through a staging tile (the state operand tile, dead by now) so
+            // that the 256 threads of this hop write whole rows: a thread owns 64 bytes of one row,
+            // and stored from there a warp would touch 32 cache lines per instruction.  The 16-byte
+            // column index is XOR-ed with the row so that both directions are (almost) conflict-free.
+            float *stage = reinterpret_cast<float *>(tS);
+            const int hop_tid = (((warp >> 2) * 2 + quarter) << 5) + lane;   // 0..255 over the eight warps of this hop
+            auto stage_put = [&](const float (&x)[16]) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    *reinterpret_cast<float4 *>(stage + zj * kN + (((cgrp * 4 + q4) ^ (zj & 15)) << 2)) =
+                        make_float4(x[4 * q4], x[4 * q4 + 1], x[4 * q4 + 2], x[4 * q4 + 3]);
+            };
+            auto stage_flush = [&](float *dst) {   // dst: the [64][64] snapshot of this chain
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int f = k4 * 256 + hop_tid, row = f >> 4, c = f & 15;
+                    *reinterpret_cast<float4 *>(dst + row * kN + 4 * c) =
+                        *reinterpret_cast<const float4 *>(stage + row * kN + ((c ^ (row & 15)) << 2));
+                }
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+            };
             if constexpr (SAVE) {
                 // v accumulates the blocks; after block m the state after token 16m+15 is known
                 const size_t nsnap = (size_t)Tlen / 16;
@@ -672,16 +694,17 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                         v[e] = m == 0 ? w[e] : __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(w[e]));
                     if (m < 3 && 16 * (m + 1) <= valid) {
                         const float4 *e4 = reinterpret_cast<const float4 *>(exp_sub + m * 64 + cgrp * 16);
-                        float *dst = snapshots + (((size_t)bh * nsnap + (size_t)chunk * 4 + m) * kN + zj) * kN + cgrp * 16;
+                        float sv[16];
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
                             const float4 g = e4[q4];
-                            *reinterpret_cast<float4 *>(dst + 4 * q4) =
-                                make_float4(g.x * (Z[4 * q4 + 0] + __uint_as_float(v[4 * q4 + 0])),
-                                            g.y * (Z[4 * q4 + 1] + __uint_as_float(v[4 * q4 + 1])),
-                                            g.z * (Z[4 * q4 + 2] + __uint_as_float(v[4 * q4 + 2])),
-                                            g.w * (Z[4 * q4 + 3] + __uint_as_float(v[4 * q4 + 3])));
+                            sv[4 * q4 + 0] = g.x * (Z[4 * q4 + 0] + __uint_as_float(v[4 * q4 + 0]));
+                            sv[4 * q4 + 1] = g.y * (Z[4 * q4 + 1] + __uint_as_float(v[4 * q4 + 1]));
+                            sv[4 * q4 + 2] = g.z * (Z[4 * q4 + 2] + __uint_as_float(v[4 * q4 + 2]));
+                            sv[4 * q4 + 3] = g.w * (Z[4 * q4 + 3] + __uint_as_float(v[4 * q4 + 3]));
                         }
+                        stage_put(sv);
+                        stage_flush(snapshots + ((size_t)bh * nsnap + (size_t)chunk * 4 + m) * kN * kN);
                     }
                 }
                 uint32_t uv[16];   // U^T: this thread's value channel for tokens 16*cgrp .. +15
@@ -705,8 +728,19 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 Z[4 * q4 + 1] = g.y * (Z[4 * q4 + 1] + __uint_as_float(v[4 * q4 + 1]));
                 Z[4 * q4 + 2] = g.z * (Z[4 * q4 + 2] + __uint_as_float(v[4 * q4 + 2]));
                 Z[4 * q4 + 3] = g.w * (Z[4 * q4 + 3] + __uint_as_float(v[4 * q4 + 3]));
-                if constexpr (K == 1)
+                if constexpr (K == 1 && !SAVE)
                     st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,   // operand of the next chunk
+                             make_float4(round_tf32(Z[4 * q4]), round_tf32(Z[4 * q4 + 1]), round_tf32(Z[4 * q4 + 2]),
+                                         round_tf32(Z[4 * q4 + 3])));
+            }
+            if constexpr (SAVE) {
+                if (valid == kL) {   // the state after the chunk's last token is its fourth snapshot
+                    stage_put(Z);
+                    stage_flush(snapshots + ((size_t)bh * ((size_t)Tlen / 16) + (size_t)chunk * 4 + 3) * kN * kN);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)   // only now may the staging tile become the operand of the next chunk
+                    st_tile4(tS, 64, zj, cgrp * 16 + 4 * q4,
                              make_float4(round_tf32(Z[4 * q4]), round_tf32(Z[4 * q4 + 1]), round_tf32(Z[4 * q4 + 2]),
                                          round_tf32(Z[4 * q4 + 3])));
             }
@@ -738,14 +772,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     const uint32_t peer_bar = map_to_cta(smem_u32(bar_state), peer);
                     bulk_copy_to_cta(map_to_cta(smem_u32(tS), peer), tS, kN * kN * 4, peer_bar);
                     bulk_copy_to_cta(map_to_cta(smem_u32(lo_buf), peer), lo_buf, kN * kN * 2, peer_bar);
-                }
-            }
-            if constexpr (SAVE) {
-                if (valid == kL) {   // the state after the chunk's last token is its fourth snapshot
-                    float *sn = snapshots + (((size_t)bh * ((size_t)Tlen / 16) + (size_t)chunk * 4 + 3) * kN + zj) * kN + cgrp * 16;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4)
-                        *reinterpret_cast<float4 *>(sn + 4 * q4) = make_float4(Z[4 * q4], Z[4 * q4 + 1], Z[4 * q4 + 2], Z[4 * q4 + 3]);
                 }
             }
             if constexpr (kFullInv) {   // Y^T was issued after the state update and completes here
