@@ -89,7 +89,10 @@ constexpr uint32_t kOffAm = kOffRaw;                          // diagonal blocks
 static_assert(kOffAm + 64 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
 
 // TMEM columns.
-constexpr uint32_t kColG = 0, kColXT = 128, kColUT = 192, kColYT = 256, kColDS = 320, kTmemCols = 512;
+// X^T and Y^T are neighbours: products whose second operands are the two halves of one 128-row tile
+// (S [At;Rt]^T, V^T [A_ak;A_rk]^T) then fill both with one N = 128 MMA per K-step instead of two N = 64.
+constexpr uint32_t kColG = 0, kColXT = 128, kColYT = 192, kColUT = 256, kColDS = 320, kTmemCols = 512;
+static_assert(kColYT == kColXT + 64, "X^T and Y^T must be adjacent accumulators");
 constexpr uint32_t kColTX = 384, kColTT = 448;   // cluster of 4: the solve applied to the identity (never with SAVE)
 // Identity operand tile [64][64] of that product, inside the raw-tile region past the inverse scratch.
 constexpr uint32_t kOffIdent = kOffRaw + 8192;
@@ -399,8 +402,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             // State path, part 1: value-major products (M = value index i, 64 valid lanes) that
             // need only this chunk's scaled operands.  They run while G is read back below.
             if constexpr (K == 1) {
-                mma_k64<64, 128, 64>(tmem + kColXT, dS, dAR, false);               // X^T  = S At^T
-                mma_k64<64, 128, 64>(tmem + kColYT, dS, dAR + kLower, false);      // Y^T  = S Rt^T
+                mma_k64<64, 128, 128>(tmem + kColXT, dS, dAR, false);              // [X^T | Y^T] = S [At;Rt]^T
             }
             if constexpr (!SAVE) mma_k64<64, 128, 64>(tmem + kColDS, dVT, dZT + kLower, false);     // dS   = V^T Kh
         }
@@ -468,8 +470,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         if (tid == 0) {
             tc_fence_after();
             // (K > 1: the state has not arrived yet, these products start the accumulators)
-            mma_k64<64, 128, 64>(tmem + kColXT, dVT, dAKRK, K == 1);             // X^T (+)= V^T A_ak^T
-            mma_k64<64, 128, 64>(tmem + kColYT, dVT, dAKRK + kLower, K == 1);    // Y^T (+)= V^T A_rk^T
+            mma_k64<64, 128, 128>(tmem + kColXT, dVT, dAKRK, K == 1);            // [X^T | Y^T] (+)= V^T [A_ak;A_rk]^T
             if constexpr (SAVE) {
 #pragma unroll
                 for (int b = 0; b < kL / kBlk; ++b)   // dS_b = V^T Kh over the tokens of block b (G is dead now)
