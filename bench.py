@@ -297,6 +297,88 @@ def main():
             and (s_host - s_dev).abs().max() <= 5e-4 * s_dev.abs().max()):
         raise SystemExit("end-to-end result differs from the device-resident call")
 
+    # ---- the same prefill kernel at the other configurations' per-GPU shapes --------------
+    # (Runs before the tensor-core legs: right after the LM-head leg the SM clock is still held down by the
+    # power cap for some tens of milliseconds, which a latency-bound kernel feels one to one.)
+    prefill_other = None
+    if not args.no_prefill_other and rank == 0 and not args.small:
+        peak_gbs, _ = measured_peaks()
+        prefill_other = {}
+        for name, (Bo, To, Ho) in (("cfg2_layer_1gpu", (16, 8192, 32)), ("cfg4_layer_shard_of_8", (4, 65536, 8)),
+                                   ("single_sequence_cfg2_model", (1, 8192, 32))):
+            oin = workloads.wkv7_inputs(Bo, To, Ho, 64, seed=11, dtype=torch.bfloat16, device=dev)
+            oseq = pkg.Wkv7PretrainForwardInputs(*[oin[n] for n in "rwkvab"])
+            os0 = torch.zeros(Bo, Ho, 64, 64, device=dev)
+            oy, oso = torch.empty_like(oin["r"]), torch.empty_like(os0)
+            ows_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bo, To, Ho, 64, pkg.BF16))
+            ows = torch.empty(max(ows_bytes, 1), dtype=torch.uint8, device=dev)
+            ocall = pkg.Wkv7StatepassCall(os0, oseq, oy, oso, ows)
+            for _ in range(2):
+                ocall()
+            torch.cuda.synchronize()
+            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            o0.record()
+            for _ in range(3):
+                ocall()
+            o1.record()
+            torch.cuda.synchronize()
+            oms = o0.elapsed_time(o1) / 3
+            obytes = Bo * To * Ho * BYTES_PER_TOKEN_HEAD + Bo * Ho * STATE_BYTES
+            # few chains: the library gives each chain a cluster of CTAs; time the one-CTA kernel beside it
+            one_cta_ms = None
+            if Bo * Ho * 2 <= 148:
+                pkg.set_wkv7_cluster(1)
+                ocall()
+                torch.cuda.synchronize()
+                o0.record()
+                for _ in range(3):
+                    ocall()
+                o1.record()
+                torch.cuda.synchronize()
+                one_cta_ms = o0.elapsed_time(o1) / 3
+                pkg.set_wkv7_cluster(0)
+            prefill_other[name] = {"shape": f"B={Bo} T={To} H={Ho} N=64 bf16 ({Bo * Ho} chains)", "ms": oms,
+                                   "ms_one_cta_per_chain": one_cta_ms,
+                                   "tokens_per_s": Bo * To / (oms * 1e-3), "gb_per_s": obytes / (oms * 1e-3) / 1e9,
+                                   "frac_of_hbm_peak": obytes / (oms * 1e-3) / 1e9 / peak_gbs,
+                                   "algorithmic_bytes": obytes}
+            del oin, oseq, os0, oy, oso, ows, ocall
+
+    # ---- training forward (with saved tensors) and backward at configuration 1 ------------
+    train = None
+    if not args.no_train and rank == 0:
+        peak_gbs, _ = measured_peaks()
+        tin = pkg.Wkv7PretrainForwardInputs(*six)
+        saved = pkg.wkv7_forward_saved(tin, None, want_state=True)
+        dy = torch.randn_like(six[0])
+
+        def timed(fn, reps=3):
+            fn()
+            torch.cuda.synchronize()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(reps):
+                fn()
+            b_.record()
+            torch.cuda.synchronize()
+            return a_.elapsed_time(b_) / reps
+
+        seq_bytes = B * T * H * N * 2
+        snap_bytes = B * H * (T // 16) * N * N * 4
+        fwd_ms = timed(lambda: pkg.wkv7_forward_saved(tin, None, want_state=True))
+        bws = torch.empty(pkg.wkv7_backward_workspace_bytes(B, T, H, N), dtype=torch.uint8, device=dev)
+        bwd_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None, workspace=bws))
+        bwd_seq_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None, parallel=False), reps=2)
+        fwd_bytes = 8 * seq_bytes + snap_bytes + B * H * STATE_BYTES             # 6 in, y and sa out, snapshots, S_T
+        bwd_bytes = 14 * seq_bytes + snap_bytes + B * H * STATE_BYTES            # 6 in, sa, dy, 6 grads, snapshots, dS0
+        train = {"workload": f"B={B} T={T} H={H} N={N} bf16, chunk_len 16",
+                 "forward_saved_ms": fwd_ms, "forward_saved_gb_per_s": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
+                 "forward_saved_frac_of_hbm_peak": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak_gbs,
+                 "backward_ms": bwd_ms, "backward_token_by_token_ms": bwd_seq_ms, "backward_gb_per_s": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
+                 "backward_frac_of_hbm_peak": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak_gbs,
+                 "forward_algorithmic_bytes": fwd_bytes, "backward_algorithmic_bytes": bwd_bytes}
+        del saved, dy, bws
+
     # ---- decode: one layer-step of configuration 3 (B=1024, H=40), state in place --
     decode = None
     if not args.no_decode and rank == 0:
@@ -420,86 +502,6 @@ def main():
                    "frac_of_bf16_peak": flops / (lms * 1e-3) / 1e12 / (tf_peak * world),
                    "mean_loss": float(loss.mean().item())}
         del xl, w_shard, tl
-
-    # ---- the same prefill kernel at the other configurations' per-GPU shapes --------------
-    prefill_other = None
-    if not args.no_prefill_other and rank == 0 and not args.small:
-        peak_gbs, _ = measured_peaks()
-        prefill_other = {}
-        for name, (Bo, To, Ho) in (("cfg2_layer_1gpu", (16, 8192, 32)), ("cfg4_layer_shard_of_8", (4, 65536, 8)),
-                                   ("single_sequence_cfg2_model", (1, 8192, 32))):
-            oin = workloads.wkv7_inputs(Bo, To, Ho, 64, seed=11, dtype=torch.bfloat16, device=dev)
-            oseq = pkg.Wkv7PretrainForwardInputs(*[oin[n] for n in "rwkvab"])
-            os0 = torch.zeros(Bo, Ho, 64, 64, device=dev)
-            oy, oso = torch.empty_like(oin["r"]), torch.empty_like(os0)
-            ows_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bo, To, Ho, 64, pkg.BF16))
-            ows = torch.empty(max(ows_bytes, 1), dtype=torch.uint8, device=dev)
-            ocall = pkg.Wkv7StatepassCall(os0, oseq, oy, oso, ows)
-            for _ in range(2):
-                ocall()
-            torch.cuda.synchronize()
-            o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            o0.record()
-            for _ in range(3):
-                ocall()
-            o1.record()
-            torch.cuda.synchronize()
-            oms = o0.elapsed_time(o1) / 3
-            obytes = Bo * To * Ho * BYTES_PER_TOKEN_HEAD + Bo * Ho * STATE_BYTES
-            # few chains: the library gives each chain a cluster of CTAs; time the one-CTA kernel beside it
-            one_cta_ms = None
-            if Bo * Ho * 2 <= 148:
-                pkg.set_wkv7_cluster(1)
-                ocall()
-                torch.cuda.synchronize()
-                o0.record()
-                for _ in range(3):
-                    ocall()
-                o1.record()
-                torch.cuda.synchronize()
-                one_cta_ms = o0.elapsed_time(o1) / 3
-                pkg.set_wkv7_cluster(0)
-            prefill_other[name] = {"shape": f"B={Bo} T={To} H={Ho} N=64 bf16 ({Bo * Ho} chains)", "ms": oms,
-                                   "ms_one_cta_per_chain": one_cta_ms,
-                                   "tokens_per_s": Bo * To / (oms * 1e-3), "gb_per_s": obytes / (oms * 1e-3) / 1e9,
-                                   "frac_of_hbm_peak": obytes / (oms * 1e-3) / 1e9 / peak_gbs,
-                                   "algorithmic_bytes": obytes}
-            del oin, oseq, os0, oy, oso, ows, ocall
-
-    # ---- training forward (with saved tensors) and backward at configuration 1 ------------
-    train = None
-    if not args.no_train and rank == 0:
-        peak_gbs, _ = measured_peaks()
-        tin = pkg.Wkv7PretrainForwardInputs(*six)
-        saved = pkg.wkv7_forward_saved(tin, None, want_state=True)
-        dy = torch.randn_like(six[0])
-
-        def timed(fn, reps=3):
-            fn()
-            torch.cuda.synchronize()
-            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a_.record()
-            for _ in range(reps):
-                fn()
-            b_.record()
-            torch.cuda.synchronize()
-            return a_.elapsed_time(b_) / reps
-
-        seq_bytes = B * T * H * N * 2
-        snap_bytes = B * H * (T // 16) * N * N * 4
-        fwd_ms = timed(lambda: pkg.wkv7_forward_saved(tin, None, want_state=True))
-        bws = torch.empty(pkg.wkv7_backward_workspace_bytes(B, T, H, N), dtype=torch.uint8, device=dev)
-        bwd_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None, workspace=bws))
-        bwd_seq_ms = timed(lambda: pkg.wkv7_backward(tin, saved, dy, None, parallel=False), reps=2)
-        fwd_bytes = 8 * seq_bytes + snap_bytes + B * H * STATE_BYTES             # 6 in, y and sa out, snapshots, S_T
-        bwd_bytes = 14 * seq_bytes + snap_bytes + B * H * STATE_BYTES            # 6 in, sa, dy, 6 grads, snapshots, dS0
-        train = {"workload": f"B={B} T={T} H={H} N={N} bf16, chunk_len 16",
-                 "forward_saved_ms": fwd_ms, "forward_saved_gb_per_s": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
-                 "forward_saved_frac_of_hbm_peak": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak_gbs,
-                 "backward_ms": bwd_ms, "backward_token_by_token_ms": bwd_seq_ms, "backward_gb_per_s": bwd_bytes / (bwd_ms * 1e-3) / 1e9,
-                 "backward_frac_of_hbm_peak": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / peak_gbs,
-                 "forward_algorithmic_bytes": fwd_bytes, "backward_algorithmic_bytes": bwd_bytes}
-        del saved, dy, bws
 
     # ---- channel mixer at the configuration-2 layer shape (two tensor-core projections) ---
     channel_mixer = None
