@@ -75,7 +75,7 @@ static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of an sm_1
 // fp32 scratch of the triangular solve: the diagonal 16 x 16 blocks of A_ab, inside the
 // raw-tile region (free between phase A and the next TMA request).
 #ifndef RWKV7_SOLVE_BLOCK
-#define RWKV7_SOLVE_BLOCK 16
+#define RWKV7_SOLVE_BLOCK 32
 #endif
 #ifndef RWKV7_TRUNC_DEBIAS
 #define RWKV7_TRUNC_DEBIAS 3.4e-4f
@@ -85,9 +85,15 @@ constexpr int kBlk = RWKV7_SOLVE_BLOCK;   // token block of the triangular solve
 // average about 0.7 * 2^-11 of its magnitude.  The shared-memory operand of such an MMA
 // is scaled up by the same factor before it is rounded, which removes the bias.
 constexpr float kDebias = 1.f + RWKV7_TRUNC_DEBIAS;
-constexpr int kPitch = 20;   // floats per scratch row (conflict-free 16-byte stores)
-constexpr uint32_t kOffAm = kOffRaw;                          // diagonal blocks of A_ab [64][20]
-static_assert(kOffAm + 64 * kPitch * 4 <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
+static_assert(kBlk == 16 || kBlk == 32, "solve block of 16 or 32 tokens");
+constexpr int kPitch = 20;    // floats per row of a 16-column scratch matrix (conflict-free 16-byte stores)
+constexpr int kPitchA = 36;   // floats per row of the A_ab scratch: the row's diagonal 16 x 16 block, then (odd
+                              // 16-token blocks) its block left of the diagonal
+constexpr uint32_t kOffAm = kOffRaw;                          // fp32 blocks of A_ab           [64][36]
+constexpr uint32_t kOffTm = kOffAm + 64 * kPitchA * 4;        // fp32 16 x 16 block inverses   [64][20]
+constexpr uint32_t kOffWm = kOffTm + 64 * kPitch * 4;         // A_10 T_00 of the two pairs    [32][20]
+constexpr uint32_t kScratchEnd = kOffWm + 32 * kPitch * 4;
+static_assert(kScratchEnd <= kOffRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
 
 // TMEM columns.
 // X^T and Y^T are neighbours: products whose second operands are the two halves of one 128-row tile
@@ -96,8 +102,8 @@ constexpr uint32_t kColG = 0, kColXT = 128, kColYT = 192, kColUT = 256, kColDS =
 static_assert(kColYT == kColXT + 64, "X^T and Y^T must be adjacent accumulators");
 constexpr uint32_t kColTX = 384, kColTT = 448;   // cluster of 4: the solve applied to the identity (never with SAVE)
 // Identity operand tile [64][64] of that product, inside the raw-tile region past the inverse scratch.
-constexpr uint32_t kOffIdent = kOffRaw + 8192;
-static_assert(kOffAm + 64 * kPitch * 4 <= kOffIdent && kOffIdent + 16384 + 8192 <= kOffRaw + kRawBytes,
+constexpr uint32_t kOffIdent = kOffRaw + 17408;
+static_assert(kScratchEnd <= kOffIdent && kOffIdent % 1024 == 0 && kOffIdent + 16384 + 8192 <= kOffRaw + kRawBytes,
               "identity tile (read as a 128-row operand) must stay inside the raw-tile region");
 
 // Optional per-phase cycle counters (development builds only): thread 0 of CTA 0
@@ -220,6 +226,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     unsigned char *raw = smem + kOffRaw, *tAR = smem + kOffAR, *tBK = smem + kOffBK, *tZT = smem + kOffZT,
                   *tS = smem + kOffS, *tVT = smem + kOffVT, *tAKRK = smem + kOffAKRK, *tXU = smem + kOffXU;
     float *Am = reinterpret_cast<float *>(smem + kOffAm);
+    float *Tm = reinterpret_cast<float *>(smem + kOffTm);
+    float *Wm = reinterpret_cast<float *>(smem + kOffWm);
     float *grp_tot = reinterpret_cast<float *>(tXU);  // [8][64], phase A only
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
@@ -445,9 +453,15 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     const bool hi = rb & 1;
 #pragma unroll
                     for (int e4 = 0; e4 < 4; ++e4)
-                        *reinterpret_cast<uint4 *>(Am + t * kPitch + e4 * 4) =
+                        *reinterpret_cast<uint4 *>(Am + t * kPitchA + e4 * 4) =
                             make_uint4(hi ? v[16 + e4 * 4] : v[e4 * 4], hi ? v[17 + e4 * 4] : v[e4 * 4 + 1],
                                        hi ? v[18 + e4 * 4] : v[e4 * 4 + 2], hi ? v[19 + e4 * 4] : v[e4 * 4 + 3]);
+                    if (kBlk == 32 && hi) {   // A_10: this row against the even block of its pair
+#pragma unroll
+                        for (int e4 = 0; e4 < 4; ++e4)
+                            *reinterpret_cast<uint4 *>(Am + t * kPitchA + 16 + e4 * 4) =
+                                make_uint4(v[e4 * 4], v[e4 * 4 + 1], v[e4 * 4 + 2], v[e4 * 4 + 3]);
+                    }
                 }
             } else {
                 unsigned char *dst = (cgrp < 2) ? tBK : tAKRK;   // A_rb under T, or [A_ak;A_rk]
@@ -478,26 +492,27 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             mma_k64<64, 128, 128>(tmem + kColXT, dVT, dAKRK, K == 1);            // [X^T | Y^T] (+)= V^T [A_ak;A_rk]^T
             if constexpr (SAVE) {
 #pragma unroll
-                for (int b = 0; b < kL / kBlk; ++b)   // dS_b = V^T Kh over the tokens of block b (G is dead now)
+                for (int b = 0; b < kL / 16; ++b)   // dS_b = V^T Kh over the 16 tokens of block b (G is dead now)
                     mma_kpair<64, 128, 64>(tmem + ds_col(b), dVT, dZT + kLower, 2 * b);
             }
             if constexpr (K == 1) umma_commit(bar_dep);   // K > 1: one commit after the products with the state
         }
-        // ---------------- U = (I - A_ab)^-1 X is solved block-wise with 16-token blocks:
-        // only the diagonal blocks T_bb = (I - A_bb)^-1 are formed here (forward substitution
-        // in fp32, one column per thread); the coupling between blocks is part of the MMA
-        // chain below.
+        // ---------------- U = (I - A_ab)^-1 X is solved block-wise: only the diagonal blocks
+        // T_bb = (I - A_bb)^-1 are formed here, the coupling between blocks is part of the MMA
+        // chain below.  16 x 16 blocks by forward substitution in fp32 (one column per thread);
+        // with 32-token solve blocks two of them are then joined by all threads,
+        // [[T_00, 0], [T_11 A_10 T_00, T_11]], which halves the dependent steps of the chain.
         PHASE(5);
         if (tid >= 64 && tid < 128) {   // warps 2 and 3: warp 0 is busy issuing
             const int b = (tid - 64) >> 4, cc = tid & 15;
-            const float *Ab = Am + (16 * b) * kPitch;
+            const float *Ab = Am + (16 * b) * kPitchA;
             float x[16];
 #pragma unroll
             for (int t = 0; t < 16; ++t) {
                 float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
                 for (int s4 = 0; s4 < (t + 3) / 4; ++s4) {
-                    const float4 a4 = *reinterpret_cast<const float4 *>(Ab + t * kPitch + 4 * s4);
+                    const float4 a4 = *reinterpret_cast<const float4 *>(Ab + t * kPitchA + 4 * s4);
                     if (4 * s4 + 0 < t) acc0 = fmaf(a4.x, x[4 * s4 + 0], acc0);
                     if (4 * s4 + 1 < t) acc1 = fmaf(a4.y, x[4 * s4 + 1], acc1);
                     if (4 * s4 + 2 < t) acc0 = fmaf(a4.z, x[4 * s4 + 2], acc0);
@@ -505,6 +520,41 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 }
                 x[t] = (t == cc) ? 1.f : ((t > cc) ? acc0 + acc1 : 0.f);
                 *reinterpret_cast<float *>(tBK + tile_off_f32(128, 16 * b + t, 16 * b + cc)) = round_tf32(x[t] * kDebias);
+                if constexpr (kBlk == 32) Tm[(16 * b + t) * kPitch + cc] = x[t];
+            }
+        }
+        if constexpr (kBlk == 32) {
+            // T_10 = T_11 (A_10 T_00) for the two pairs of blocks, one element per thread and product
+            const int pr = tid >> 8, t = (tid >> 4) & 15, c = tid & 15;
+            __syncthreads();
+            {
+                const float *arow = Am + (32 * pr + 16 + t) * kPitchA + 16;   // A_10[t][.]
+                const float *tcol = Tm + (32 * pr) * kPitch + c;              // T_00[.][c]
+                float w = 0.f;
+#pragma unroll
+                for (int s4 = 0; s4 < 4; ++s4) {
+                    const float4 a4 = *reinterpret_cast<const float4 *>(arow + 4 * s4);
+                    w = fmaf(a4.x, tcol[(4 * s4 + 0) * kPitch], w);
+                    w = fmaf(a4.y, tcol[(4 * s4 + 1) * kPitch], w);
+                    w = fmaf(a4.z, tcol[(4 * s4 + 2) * kPitch], w);
+                    w = fmaf(a4.w, tcol[(4 * s4 + 3) * kPitch], w);
+                }
+                Wm[(16 * pr + t) * kPitch + c] = w;
+            }
+            __syncthreads();
+            {
+                const float *trow = Tm + (32 * pr + 16 + t) * kPitch;   // T_11[t][.] (zero right of the diagonal)
+                const float *wcol = Wm + (16 * pr) * kPitch + c;
+                float z = 0.f;
+#pragma unroll
+                for (int s4 = 0; s4 < 4; ++s4) {
+                    const float4 a4 = *reinterpret_cast<const float4 *>(trow + 4 * s4);
+                    z = fmaf(a4.x, wcol[(4 * s4 + 0) * kPitch], z);
+                    z = fmaf(a4.y, wcol[(4 * s4 + 1) * kPitch], z);
+                    z = fmaf(a4.z, wcol[(4 * s4 + 2) * kPitch], z);
+                    z = fmaf(a4.w, wcol[(4 * s4 + 3) * kPitch], z);
+                }
+                *reinterpret_cast<float *>(tBK + tile_off_f32(128, 32 * pr + 16 + t, 32 * pr + c)) = round_tf32(z * kDebias);
             }
         }
         if constexpr (kFullInv) {
@@ -615,7 +665,12 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             };
             auto leaves = [&](int b) {   // what U_b^T contributes to Y^T and dS
                 mma_ts_block<64>(tmem + kColYT, tmem + kColUT + b * kBlk, dBK, 64, b * kBlk, kBlk / 8, true);   // A_rb
-                mma_ts_block<64>(tmem + ds_col(b), tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, kBlk / 8, true);    // Bh
+                if constexpr (SAVE && kBlk == 32) {   // the snapshots need the update per 16 tokens
+                    mma_ts_block<64>(tmem + ds_col(2 * b), tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, 2, true);
+                    mma_ts_block<64>(tmem + ds_col(2 * b + 1), tmem + kColUT + b * kBlk + 16, dZT, 0, b * kBlk + 16, 2, true);
+                } else {
+                    mma_ts_block<64>(tmem + ds_col(b), tmem + kColUT + b * kBlk, dZT, 0, b * kBlk, kBlk / 8, true);    // Bh
+                }
             };
             if constexpr (K > 1) {
                 // (the state tile was written by a bulk copy, i.e. through the async proxy the tensor
