@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     __nv_bfloat16 *__restrict__ y, float *s_out, int *__restrict__ flags,
                     int Tlen, int H, int *status, float *__restrict__ snapshots,
-                    __nv_bfloat16 *__restrict__ state_repl) {
+                    __nv_bfloat16 *__restrict__ state_repl, int chain0) {
     // Every pointer is derived from the array itself so that the accesses stay in
     // the shared address space; the 1024-byte alignment the swizzled tiles need is
     // what the runtime provides and is verified before anything else happens.
@@ -248,7 +248,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     // the state-dependent part of the solve shrinks from eight dependent MMA steps to one.
     constexpr bool kFullInv = (K == 4);
     const int rank = K > 1 ? (int)cluster_ctarank() : 0;
-    const int bh = blockIdx.x / K;
+    const int bh = chain0 + blockIdx.x / K;   // a launch covers the chains chain0 .. chain0 + gridDim.x / K - 1
     const int bi = bh / H, h = bh % H;
     const int nchunks = (Tlen + kL - 1) / kL;
 
@@ -968,6 +968,19 @@ std::atomic<int> g_cluster_override{0};
 int wkv7_cluster_override() { return g_cluster_override.load(); }
 void wkv7_set_cluster_override(int k) { g_cluster_override.store(k); }
 
+// Number of SMs of `device` (0 if the query fails); queried once per device.
+static int sm_count(int device) {
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> cached[kMaxDevices];
+    if (device < 0 || device >= kMaxDevices) return 0;
+    int n = cached[device].load();
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) n = -1;
+        cached[device].store(n > 0 ? n : -1);
+    }
+    return n > 0 ? n : 0;
+}
+
 // How many clusters of `k` CTAs of the (one CTA per SM) chunked kernel can be resident on `device`;
 // queried once per device and cluster size.
 static int max_resident_clusters(int device, int k) {
@@ -1038,22 +1051,40 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
     int *flags = static_cast<int *>(workspace);
     const int64_t chains = p.B * p.H;
     // Few chains: a cluster of CTAs per chain (needs at least one chunk per CTA to pay).
+    // A cluster must fit one GPC, so fewer clusters are resident than SMs / K (on a 148-SM B200:
+    // 74 of two, 33 of four): all chains of a cluster launch must be resident at once or it runs in waves.
+    const int64_t nchunks = (p.T + kL - 1) / kL;
+    auto cluster_for = [&](int64_t n) -> int {
+        if (nchunks >= 8 && n <= max_resident_clusters(p.device, 4)) return 4;
+        if (nchunks >= 4 && n <= max_resident_clusters(p.device, 2)) return 2;
+        return 1;
+    };
+    // Launch plan: `head` chains with one CTA each, then `chains - head` chains with `cluster` CTAs each.
+    // More chains than SMs run in waves of one CTA per SM; when the last wave would leave at least half
+    // of the SMs idle, its chains form a second launch with a cluster per chain, which ends sooner.
     int cluster = 1;
+    int64_t head = 0;
     if (!save) {
         const int forced = wkv7_cluster_override();
-        const int64_t nchunks = (p.T + kL - 1) / kL;
-        // A cluster must fit one GPC, so fewer clusters are resident than SMs / K (on a 148-SM B200:
-        // 74 of two, 33 of four): all chains must be resident at once or the launch runs in waves.
         if (forced > 0) cluster = forced;
-        else if (nchunks >= 8 && chains <= max_resident_clusters(p.device, 4)) cluster = 4;
-        else if (nchunks >= 4 && chains <= max_resident_clusters(p.device, 2)) cluster = 2;
+        else {
+            cluster = cluster_for(chains);
+            const int sms = sm_count(p.device);
+            if (cluster == 1 && sms > 0 && chains > sms && chains % sms != 0) {
+                const int tail = cluster_for(chains % sms);
+                if (tail > 1) {
+                    cluster = tail;
+                    head = chains - chains % sms;
+                }
+            }
+        }
     }
     cudaError_t e;
-    auto launch = [&](auto kern, int k) -> cudaError_t {
+    auto launch = [&](auto kern, int k, int64_t first, int64_t count) -> cudaError_t {
         cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (err != cudaSuccess) return err;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(chains * k));
+        cfg.gridDim = dim3((unsigned)(count * k));
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = kSmemBytes;
         cfg.stream = stream;
@@ -1064,20 +1095,25 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = k > 1 ? 1 : 0;
-        return cudaLaunchKernelEx(&cfg, kern, maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags,
-                                  (int)p.T, (int)p.H, status, snapshots,
-                                  reinterpret_cast<__nv_bfloat16 *>(state_replacement));
+        err = cudaLaunchKernelEx(&cfg, kern, maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags,
+                                 (int)p.T, (int)p.H, status, snapshots,
+                                 reinterpret_cast<__nv_bfloat16 *>(state_replacement), (int)first);
+        if (err == cudaSuccess) count_launch();
+        return err;
     };
-    if (cluster > 1) {
-        e = cudaMemsetAsync(flags, 0, sizeof(int) * (size_t)chains, stream);   // CTAs of a cluster only ever set a flag
+    if (cluster > 1) {   // CTAs of a cluster only ever set a flag
+        e = cudaMemsetAsync(flags + head, 0, sizeof(int) * (size_t)(chains - head), stream);
         if (e != cudaSuccess) return (int)e;
     }
-    if (save) e = launch(wkv7_chunked_kernel<true, 1>, 1);
-    else if (cluster == 4) e = launch(wkv7_chunked_kernel<false, 4>, 4);
-    else if (cluster == 2) e = launch(wkv7_chunked_kernel<false, 2>, 2);
-    else e = launch(wkv7_chunked_kernel<false, 1>, 1);
+    if (save) e = launch(wkv7_chunked_kernel<true, 1>, 1, 0, chains);
+    else {
+        e = head > 0 ? launch(wkv7_chunked_kernel<false, 1>, 1, 0, head) : cudaSuccess;
+        if (e != cudaSuccess) return (int)e;
+        if (cluster == 4) e = launch(wkv7_chunked_kernel<false, 4>, 4, head, chains - head);
+        else if (cluster == 2) e = launch(wkv7_chunked_kernel<false, 2>, 2, head, chains - head);
+        else e = launch(wkv7_chunked_kernel<false, 1>, 1, head, chains - head);
+    }
     if (e != cudaSuccess) return (int)e;
-    count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     // Chains whose decay left the safe range are recomputed token by token; the

@@ -339,3 +339,32 @@ def test_cluster_pipeline_falls_back_outside_decay_range(pkg, oracle, workloads,
     assert pkg.read_device_status(0) == 0
     parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
     parity.assert_close_f32(s, s_ref, 1e-3, "state")
+
+
+@pytest.mark.parametrize("T,extra", [(256, 3), (512, 2)])
+def test_last_wave_runs_as_clusters(pkg, oracle, workloads, cuda, T, extra):
+    """More chains than SMs: the chains of the last, mostly empty wave are launched separately with a
+    cluster of CTAs each (2 at T = 256, 4 at T = 512).  Every chain must come out as from the plain
+    one-CTA launch, including one chain in each launch whose decay leaves the safe range and is
+    recomputed by the sequential scan."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    H = sms + extra
+    inp = workloads.wkv7_inputs(1, T, H, 64, seed=35, dtype=torch.bfloat16, state="normal")
+    w = inp["w"].float()
+    for h in (1, H - 1):   # one chain of the first launch, one of the second
+        w[:, :, h] = torch.rand_like(w[:, :, h]) + 0.5
+    inp["w"] = w.to(torch.bfloat16)
+    y_ref, s_ref = _oracle(oracle, inp)
+    try:
+        pkg.set_wkv7_cluster(1)
+        one_y, one_s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+    finally:
+        pkg.set_wkv7_cluster(0)
+    before = pkg.kernel_launch_count()
+    y, s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+    assert pkg.kernel_launch_count() - before == 3   # two chunked launches and the flag check
+    assert pkg.read_device_status(0) == 0
+    parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s, s_ref, 1e-3, "state")
+    assert np.array_equal(s[:, :sms], one_s[:, :sms])   # the first launch is the one-CTA kernel itself
+    assert parity.headline(s[:, sms:], one_s[:, sms:]) <= 4e-4
