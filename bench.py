@@ -198,6 +198,7 @@ def main():
     ap.add_argument("--no-train", action="store_true")
     ap.add_argument("--no-prefill-other", action="store_true")
     ap.add_argument("--no-lm-head", action="store_true")
+    ap.add_argument("--no-forward", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
     args = ap.parse_args()
@@ -455,6 +456,52 @@ def main():
         streaming["gated_readout"] = timeit(lambda: pkg.gated_readout_epilogue(*gr, Hs), 6 * 2 * elems)
         del ep, wp, gr
 
+    # ---- whole prefill forward of the configuration-2 model (secondary figure) ------------
+    # 24 cells of C = 2048 (32 heads), vocabulary 65 536, B = 16 sequences of T = 8192 random token
+    # ids, random-init bf16 weights, fused LM-head cross entropy on the shifted targets.  Every
+    # hot-path operator goes through the C ABI; the dense projections and LoRA products are cuBLAS
+    # matmuls, layer norms and residuals torch ops (rwkv-rs-stable_b200/cell_forward.py).  With N
+    # GPUs the batch is split over the ranks (replicated weights, no collective in the forward).
+    forward = None
+    if not args.no_forward and (16 % world == 0):
+        from rwkv_rs_stable_b200 import cell_forward as cf
+        Lf, Cf, Hf, Ff, Vf, Bf, Tf = (2, 512, 8, 2048, 4096, 2, 1024) if args.small else (24, 2048, 32, 8192, 65536, 16, 8192)
+        Bl = max(Bf // world, 1)
+        with torch.no_grad():
+            cells = [cf.random_cell(i, Cf, Hf, Ff, device=dev, seed=9) for i in range(Lf)]
+            gf = torch.Generator(device=dev)
+            gf.manual_seed(99 + rank)
+            emb = (torch.randn((Vf, Cf), generator=gf, device=dev) * 0.02).to(torch.bfloat16)
+            headw = (torch.randn((Vf, Cf), generator=gf, device=dev) * 0.02).to(torch.bfloat16)
+            fln = (torch.ones(Cf, device=dev, dtype=torch.bfloat16), torch.zeros(Cf, device=dev, dtype=torch.bfloat16))
+            ids = torch.randint(0, Vf, (Bl, Tf), generator=gf, device=dev)
+            cmws = torch.empty(int(pkg.lib().rwkv7_channel_mixer_workspace_bytes(Bl, Tf, Cf, Ff)) or 1,
+                               dtype=torch.uint8, device=dev)
+            floss = cf.prefill_forward(pkg, cells, emb, headw, fln, ids, Hf, cmws)   # warm-up
+            sync_all()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n_fw = 2
+            launches_before = pkg.kernel_launch_count()
+            f0.record()
+            for _ in range(n_fw):
+                floss = cf.prefill_forward(pkg, cells, emb, headw, fln, ids, Hf, cmws)
+            f1.record()
+            sync_all()
+            fw_launches = (pkg.kernel_launch_count() - launches_before) // n_fw
+        tf_ms = torch.tensor([f0.elapsed_time(f1) / n_fw], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tf_ms, op=dist.ReduceOp.MAX)
+        fms = float(tf_ms.item())
+        forward = {"workload": f"L={Lf} C={Cf} H={Hf} F={Ff} V={Vf}, B={Bf} T={Tf} random token ids, bf16 random-init "
+                               "weights, LM-head cross entropy on shifted targets",
+                   "sharding": "none" if world == 1 else f"batch over {world} GPUs ({Bl} sequences each), weights replicated",
+                   "scaling": "strong", "ms": fms, "tokens_per_s": Bl * world * Tf / (fms * 1e-3),
+                   "library_kernel_launches_per_forward": int(fw_launches),
+                   "mean_loss": float(floss.item()),
+                   "dense_projections": "cuBLAS (torch.matmul), outside the hot path"}
+        del cells, emb, headw, ids, cmws, floss
+        torch.cuda.empty_cache()
+
     # ---- fused LM-head cross entropy at the configuration-2 shape (tensor-core-bound) -----
     # One GPU: the whole vocabulary.  N GPUs: the vocabulary is sharded over the ranks (strong
     # scaling of one LM head), every rank computes the partial triples of its shard, the triples
@@ -567,6 +614,7 @@ def main():
         "channel_mixer": channel_mixer,
         "train": train,
         "prefill_other_configs": prefill_other,
+        "cfg2_forward": forward,
     }
     if not args.no_cpu_baseline:
         oracle = entry.load_oracle()

@@ -235,7 +235,7 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     uint64_t *bar_dep = bar_tma + 3;   // used by the MMA-issuing thread alone, between dependent MMAs
     uint64_t *bar_state = bar_tma + 4; // K > 1: the previous CTA of the cluster has delivered the state
     unsigned char *lo_buf = tXU + 2048;   // K > 1: [64][64] bf16 residual of the delivered state (8 KB)
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc + 16);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kOffMisc + 48);   // past the five barriers
     float *exp_cl = reinterpret_cast<float *>(smem + kOffMisc + 64);   // [2][64] exp(c_L), by chunk parity
     int *unsafe = reinterpret_cast<int *>(exp_cl + 128);
 
