@@ -92,8 +92,10 @@ def _lora(x: torch.Tensor, w, act=None) -> torch.Tensor:
     h = x @ w[0]
     if act is not None:
         h = act(h)
-    y = h @ w[1]
-    return y if w[2] is None else y + w[2]
+    if w[2] is None:
+        return h @ w[1]
+    # bias + h w_b in one library call (the bias enters the product's epilogue)
+    return torch.addmm(w[2], h.reshape(-1, h.shape[-1]), w[1]).view(*h.shape[:-1], w[1].shape[1])
 
 
 def cell_forward(pkg, w: CellWeights, x: torch.Tensor, value_from_first_cell: Optional[torch.Tensor],
@@ -130,7 +132,7 @@ def cell_forward(pkg, w: CellWeights, x: torch.Tensor, value_from_first_cell: Op
     out = pkg.gated_readout_epilogue(y.view(B, T, C), receptance, wp.replacement_key, value, gate,
                                      w.group_norm[0], w.group_norm[1], w.receptance_key_bonus, H)
     del y, gate, wp, seq, receptance
-    x = x + out @ w.w_output.t()
+    x = torch.addmm(x.view(-1, C), out.view(-1, C), w.w_output.t()).view(B, T, C)   # residual inside the projection
     del out
     xn = F.layer_norm(x, (C,), w.ln2[0], w.ln2[1])
     x = x + pkg.channel_mixer_custom(xn, w.cm_key_scale, w.cm_key_weight, w.cm_value_weight, workspace=cm_workspace)

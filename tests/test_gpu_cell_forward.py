@@ -26,8 +26,8 @@ def _lora(x, w, act=None):
     h = _bf(x @ _d(w[0]))
     if act is not None:
         h = _bf(act(h))
-    y = _bf(h @ _d(w[1]))
-    return y if w[2] is None else _bf(y + _d(w[2]))
+    y = h @ _d(w[1])
+    return _bf(y if w[2] is None else y + _d(w[2]))   # the bias is added inside the product
 
 
 def _cell_restated(oracle, w, x, v_first, cell_id, H):
@@ -60,7 +60,7 @@ def _cell_restated(oracle, w, x, v_first, cell_id, H):
     out = _bf(oracle.gated_readout(*[t.numpy() for t in (y, receptance, wp["replacement_key"], value, gate,
                                                          _d(w.group_norm[0]), _d(w.group_norm[1]),
                                                          _d(w.receptance_key_bonus))], H))
-    x = _bf(x + _bf(out @ _d(w.w_output).t()))
+    x = _bf(x + out @ _d(w.w_output).t())   # the residual is added inside the projection
     xn = _bf(F.layer_norm(x, (C,), _d(w.ln2[0]), _d(w.ln2[1])))
     cm = _bf(oracle.channel_mixer(xn.numpy(), _d(w.cm_key_scale).numpy(), _d(w.cm_key_weight).numpy(),
                                   _d(w.cm_value_weight).numpy()))
