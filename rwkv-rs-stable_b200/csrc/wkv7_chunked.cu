@@ -127,6 +127,7 @@ __device__ long long g_phase_clocks[16];
 struct TmaMaps {
     CUtensorMap m[6];  // r, w, k, v, a, b as [B*T, H*N] bf16, box 64 x 64
     CUtensorMap snap;  // SAVE: snapshots as [B*H*(T/16)*64, 64] fp32, box 64 rows x 32 columns, 128-byte swizzle
+    CUtensorMap y;     // output as [B*T, H*N] bf16, box 64 x 64 (one CTA per chain: y leaves by tensor stores)
 };
 
 enum { TR = 0, TW = 1, TK = 2, TV = 3, TA = 4, TB = 5 };
@@ -229,6 +230,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     float *Tm = reinterpret_cast<float *>(smem + kOffTm);
     float *Wm = reinterpret_cast<float *>(smem + kOffWm);
     float *grp_tot = reinterpret_cast<float *>(tXU);  // [8][64], phase A only
+    // One CTA per chain: a chunk's y tile [t][i] (bf16, 8 KB) is staged here and stored by one bulk tensor
+    // copy; stored by the threads themselves (a thread holds 16 tokens of one channel, 2 bytes each) the
+    // 128 store instructions of a chunk took 830 cycles of the hop.
+    unsigned char *y_stage = tXU + 4096;
     uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kOffMisc);
     uint64_t *bar_mma = bar_tma + 1;
     uint64_t *bar_y = bar_tma + 2;     // cluster of 4: Y^T is complete (the state leaves before y is stored)
@@ -398,8 +403,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 st_tile4(tVT, 64, j, t0 + 4 * q4, make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]));
             }
         }
-        if constexpr (SAVE) {
-            if (tid == 0) bulk_wait_group_read<0>();   // the last snapshots have left the [A_ak;A_rk] tile
+        if constexpr (SAVE || K == 1) {
+            // the last snapshots have left the [A_ak;A_rk] tile, the last y tile its staging area
+            if (tid == 0) bulk_wait_group_read<0>();
         }
         fence_proxy_async();
         __syncthreads();  // operands visible to the tensor core; raw tiles and group sums are dead
@@ -840,10 +846,22 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 tmem_ld_wait();
             }
             // y[t][i]: this thread holds value channel i = zj for tokens 16*cgrp .. +15
-            __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + cgrp * 16) * H + h) * kN + zj;
+            if (K == 1 && valid == kL) {
+                __nv_bfloat16 *st = reinterpret_cast<__nv_bfloat16 *>(y_stage) + (cgrp * 16) * kN + zj;
 #pragma unroll
-            for (int e = 0; e < 16; ++e)
-                if (cgrp * 16 + e < valid) dst[(size_t)e * H * kN] = __float2bfloat16_rn(__uint_as_float(yv[e]));
+                for (int e = 0; e < 16; ++e) st[e * kN] = __float2bfloat16_rn(__uint_as_float(yv[e]));
+                fence_proxy_async();
+                asm volatile("bar.sync 3, 256;" ::: "memory");   // the eight warps of the hop
+                if (tid == 0) {
+                    tma_store_2d(&maps.y, h * kN, bi * Tlen + chunk * kL, y_stage);
+                    bulk_commit_group();
+                }
+            } else {
+                __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + chunk * kL + cgrp * 16) * H + h) * kN + zj;
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    if (cgrp * 16 + e < valid) dst[(size_t)e * H * kN] = __float2bfloat16_rn(__uint_as_float(yv[e]));
+            }
         }
         if constexpr (kFullInv) y_phase ^= 1;
         // No CTA barrier here: the next chunk's phase A touches neither TMEM nor any
@@ -856,8 +874,8 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
 
     // ---------------- epilogue
     PHASE(12);
-    if constexpr (SAVE) {
-        if (tid == 0) bulk_wait_group<0>();   // snapshot copies still in flight read this CTA's shared memory
+    if constexpr (SAVE || K == 1) {
+        if (tid == 0) bulk_wait_group<0>();   // snapshot / y copies still in flight read this CTA's shared memory
     }
     // A tile batch still in flight must land before the CTA gives up its shared memory.
     if (failed && tma_issued > tma_consumed) mbar_wait(bar_tma, (uint32_t)(tma_consumed & 1));
@@ -1028,6 +1046,12 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
     for (int i = 0; i < 6; ++i) {
         CUresult r = encode(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptrs[i]), dims,
                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    }
+    {
+        CUresult r = encode(&maps.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.y, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
     }
