@@ -342,129 +342,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             }
             __syncthreads();
         }
-#ifdef RWKV7_PHASE_A_ROWS
-        {
-            // A thread owns one token (row t) and 8 consecutive channels: every raw tile is read with one
-            // 16-byte load per thread (the tiles arrive 128-byte swizzled, so the 32 rows of a warp do not
-            // collide), the prefix sum over tokens is a warp scan, and the two halves of the chunk meet
-            // through shared memory once.
-            const int cc = warp & 7, half = warp >> 3;       // channels 8cc .. 8cc+7; tokens 32 half + lane
-            const int t = half * 32 + lane;
-            const unsigned char *rrow = raw + t * 128 + ((cc ^ (t & 7)) << 4);
-            auto ld8 = [&](int tensor, float (&o)[8]) {
-                const uint4 u = *reinterpret_cast<const uint4 *>(rrow + tensor * (kL * kN * 2));
-                const unsigned w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    o[2 * i] = __uint_as_float(w4[i] << 16);
-                    o[2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
-                }
-            };
-            float c[8], e[8], ep[8], einv[8];
-            ld8(TW, c);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) c[i] = -__expf(c[i]);
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float up = __shfl_up_sync(0xffffffffu, c[i], off);
-                    if (lane >= off) c[i] += up;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) e[i] = __expf(c[i]);   // exp of the prefix inside this half
-            float *half_sum = grp_tot, *half_exp = grp_tot + 64;   // first half: c_31 and exp(c_31) per channel
-            if (half == 0 && lane == 31) {
-                *reinterpret_cast<float4 *>(half_sum + cc * 8) = make_float4(c[0], c[1], c[2], c[3]);
-                *reinterpret_cast<float4 *>(half_sum + cc * 8 + 4) = make_float4(c[4], c[5], c[6], c[7]);
-                *reinterpret_cast<float4 *>(half_exp + cc * 8) = make_float4(e[0], e[1], e[2], e[3]);
-                *reinterpret_cast<float4 *>(half_exp + cc * 8 + 4) = make_float4(e[4], e[5], e[6], e[7]);
-            }
-            __syncthreads();
-            if (half == 1) {
-                const float4 s0 = *reinterpret_cast<const float4 *>(half_sum + cc * 8);
-                const float4 s1 = *reinterpret_cast<const float4 *>(half_sum + cc * 8 + 4);
-                const float4 x0 = *reinterpret_cast<const float4 *>(half_exp + cc * 8);
-                const float4 x1 = *reinterpret_cast<const float4 *>(half_exp + cc * 8 + 4);
-                const float bs[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                const float bx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    c[i] += bs[i];
-                    e[i] *= bx[i];
-                    ep[i] = bx[i];   // exp(c_31), the predecessor of this half's first token
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) ep[i] = 1.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float up = __shfl_up_sync(0xffffffffu, e[i], 1);
-                if (lane > 0) ep[i] = up;   // exp(c_{t-1})
-                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(einv[i]) : "f"(e[i]));
-            }
-            if (t == kL - 1) {
-                bool bad = false;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    exp_cl[(iter & 1) * 64 + cc * 8 + i] = e[i];
-                    bad |= c[i] < -kMaxLogDecay;
-                }
-                if (bad) atomicOr(unsafe, 1);
-            }
-            if constexpr (SAVE) {
-                if ((t & 15) == 15 && t < kL - 1) {   // exp(c_t) at t = 15, 31, 47
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) exp_sub[(t >> 4) * 64 + cc * 8 + i] = e[i];
-                }
-            }
-            // row t, columns 8cc .. 8cc+7 of a 128-row K-major tile (two 16-byte pieces)
-            const uint32_t nt0 = tile_off_f32(128, t, cc * 8), nt1 = tile_off_f32(128, t, cc * 8 + 4);
-            // transposed: row 8cc + i (its swizzle term is i), column t
-            const uint32_t tr_base = (uint32_t)(t >> 5) * (128u * 128u) + (uint32_t)(cc * 8) * 128u;
-            const uint32_t tr_col = (uint32_t)(t & 31) * 4u;
-            float x[8], o[8];
-            ld8(TA, x);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = round_tf32(x[i] * ep[i]);
-            *reinterpret_cast<float4 *>(tAR + nt0) = make_float4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<float4 *>(tAR + nt1) = make_float4(o[4], o[5], o[6], o[7]);
-            ld8(TR, x);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = round_tf32(x[i] * e[i]);
-            *reinterpret_cast<float4 *>(tAR + 64 * 128 + nt0) = make_float4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<float4 *>(tAR + 64 * 128 + nt1) = make_float4(o[4], o[5], o[6], o[7]);
-            ld8(TB, x);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float bh = x[i] * einv[i];
-                o[i] = round_tf32(bh);
-                // transposed copy: operand of dS += U^T Bh (U^T is read from TMEM, hence the debias factor)
-                *reinterpret_cast<float *>(tZT + tr_base + (uint32_t)i * 128u + (tr_col ^ ((uint32_t)i << 4))) =
-                    round_tf32(bh * kDebias);
-            }
-            *reinterpret_cast<float4 *>(tBK + nt0) = make_float4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<float4 *>(tBK + nt1) = make_float4(o[4], o[5], o[6], o[7]);
-            ld8(TK, x);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                o[i] = round_tf32(x[i] * einv[i]);
-                *reinterpret_cast<float *>(tZT + 64 * 128 + tr_base + (uint32_t)i * 128u + (tr_col ^ ((uint32_t)i << 4))) = o[i];
-            }
-            *reinterpret_cast<float4 *>(tBK + 64 * 128 + nt0) = make_float4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<float4 *>(tBK + 64 * 128 + nt1) = make_float4(o[4], o[5], o[6], o[7]);
-            ld8(TV, x);   // bf16 values are tf32-exact
-            {
-                // V^T is a 64-row tile: panel stride 64 * 128 bytes
-                const uint32_t vt_base = (uint32_t)(t >> 5) * (64u * 128u) + (uint32_t)(cc * 8) * 128u;
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    *reinterpret_cast<float *>(tVT + vt_base + (uint32_t)i * 128u + (tr_col ^ ((uint32_t)i << 4))) = x[i];
-            }
-        }
-#else
         {
             const int j = tid & 63, tg = tid >> 6;  // channel, group of 8 tokens
             const int t0 = tg * 8;
@@ -526,7 +403,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 st_tile4(tVT, 64, j, t0 + 4 * q4, make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]));
             }
         }
-#endif
         if constexpr (SAVE || K == 1) {
             // the last snapshots have left the [A_ak;A_rk] tile, the last y tile its staging area
             if (tid == 0) bulk_wait_group_read<0>();
@@ -1157,12 +1033,6 @@ static int max_resident_clusters(int device, int k) {
 int launch_wkv7_sequential_flagged_saved(const Wkv7Args &p, const int *flags, float *snapshots,
                                          void *state_replacement, int chunk_len, cudaStream_t stream);
 
-#ifdef RWKV7_PHASE_A_ROWS
-constexpr CUtensorMapSwizzle kRawSwizzle = CU_TENSOR_MAP_SWIZZLE_128B;   // phase A reads 16-byte pieces of 32 rows at once
-#else
-constexpr CUtensorMapSwizzle kRawSwizzle = CU_TENSOR_MAP_SWIZZLE_NONE;
-#endif
-
 static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapshots, void *state_replacement,
                                cudaStream_t stream) {
     EncodeTiledFn encode = encode_fn();
@@ -1175,7 +1045,7 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
     const cuuint32_t estr[2] = {1, 1};
     for (int i = 0; i < 6; ++i) {
         CUresult r = encode(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptrs[i]), dims,
-                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, kRawSwizzle,
+                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
     }
