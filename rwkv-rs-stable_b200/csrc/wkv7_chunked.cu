@@ -643,14 +643,22 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 if (!mbar_wait_cluster(bar_state, state_phase)) atomicOr(unsafe, 2);
                 state_phase ^= 1;
                 if (quarter < 2) {   // fp32 state = delivered tf32 tile + bf16 residual
+                    // (residual rows are 128 bytes; their 16-byte pieces are XOR-ed with the row so that the
+                    // 32 rows of a warp do not meet in one bank)
+                    const unsigned char *lo_row = lo_buf + zj * (kN * 2);
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const float4 hi = *reinterpret_cast<const float4 *>(tS + tile_off_f32(64, zj, cgrp * 16 + 4 * q4));
-                        const uint2 lo = *reinterpret_cast<const uint2 *>(lo_buf + (zj * kN + cgrp * 16 + 4 * q4) * 2);
-                        Z[4 * q4 + 0] = hi.x + __uint_as_float(lo.x << 16);
-                        Z[4 * q4 + 1] = hi.y + __uint_as_float(lo.x & 0xffff0000u);
-                        Z[4 * q4 + 2] = hi.z + __uint_as_float(lo.y << 16);
-                        Z[4 * q4 + 3] = hi.w + __uint_as_float(lo.y & 0xffff0000u);
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const uint4 lo = *reinterpret_cast<const uint4 *>(lo_row + (((cgrp * 2 + h2) ^ (zj & 7)) << 4));
+                        const unsigned l4[4] = {lo.x, lo.y, lo.z, lo.w};
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            const int q4 = 2 * h2 + q;
+                            const float4 hi = *reinterpret_cast<const float4 *>(tS + tile_off_f32(64, zj, cgrp * 16 + 4 * q4));
+                            Z[4 * q4 + 0] = hi.x + __uint_as_float(l4[2 * q] << 16);
+                            Z[4 * q4 + 1] = hi.y + __uint_as_float(l4[2 * q] & 0xffff0000u);
+                            Z[4 * q4 + 2] = hi.z + __uint_as_float(l4[2 * q + 1] << 16);
+                            Z[4 * q4 + 3] = hi.w + __uint_as_float(l4[2 * q + 1] & 0xffff0000u);
+                        }
                     }
                 }
             }
@@ -826,9 +834,9 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     lo[2 * q4] = *reinterpret_cast<const unsigned *>(&l01);
                     lo[2 * q4 + 1] = *reinterpret_cast<const unsigned *>(&l23);
                 }
-                uint4 *lo_dst = reinterpret_cast<uint4 *>(lo_buf + (zj * kN + cgrp * 16) * 2);
-                lo_dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                lo_dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                unsigned char *lo_row = lo_buf + zj * (kN * 2);   // 16-byte pieces XOR-ed with the row, as read above
+                *reinterpret_cast<uint4 *>(lo_row + (((cgrp * 2) ^ (zj & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4 *>(lo_row + (((cgrp * 2 + 1) ^ (zj & 7)) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
                 fence_proxy_async();   // the bulk copies read these buffers through the async proxy
                 asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight warps that hold the state
                 if (tid == 0 && chunk + 1 < nchunks) {
