@@ -49,10 +49,10 @@ def bench_config(B, T, H, N, path="auto"):
             "sharding": "batch x head shard per rank, no collective on the data path"}
 
 
-# DRAM bytes of one prefill launch from the ncu capture of the B=4 case (151.9 MB read +
-# 15.2 MB written; y still partly in L2 at kernel end), scaled x2 to B=8: traffic is
+# DRAM bytes of one prefill launch from the ncu capture of this very workload (configuration 1,
+# B=8: 303.6 MB read + 41.8 MB written; part of y is still in L2 when the kernel ends); traffic is
 # proportional to the number of chains.  See profiles/wkv7_chunked_prefill_cfg1.md.
-NCU_TRAFFIC_BYTES_CFG1 = 337.2e6   # ncu dram read+write of the B=4 capture (151.9 + 16.7 MB), scaled to B=8
+NCU_TRAFFIC_BYTES_CFG1 = 345.4e6   # ncu dram__bytes_read.sum + dram__bytes_write.sum, B=8
 
 
 def measured_peaks():
