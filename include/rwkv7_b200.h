@@ -103,8 +103,11 @@ int rwkv7_get_wkv7_path(void);
 /* The chunked prefill kernel gives a chain to a thread-block cluster of 2 or 4 CTAs when there
  * are at most half / a quarter as many (b,h) chains as SMs (small-batch prefill): the CTAs take
  * the chunks in turn, prepare everything that does not depend on the state ahead of time and
- * pass only the state through distributed shared memory.  0 restores that automatic choice;
- * 1, 2 or 4 force a cluster size (for tests and measurements).  Process-wide. */
+ * pass only the state through distributed shared memory.  With more chains than SMs the chains
+ * of a last, at most half-full wave are launched the same way (a second launch on the same
+ * stream).  Results of a chain depend on its cluster size in the last bits (a few 1e-5 to 1e-4 of
+ * the largest entry).  0 restores that automatic choice; 1, 2 or 4 force a cluster size for every
+ * chain (1 makes results independent of how many chains a call holds).  Process-wide. */
 int rwkv7_set_wkv7_cluster(int cluster_size);
 /* Number of kernels this library has launched in this process (all devices,
  * all threads).  Benchmarks read it before and after a timed region. */
