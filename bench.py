@@ -49,10 +49,11 @@ def bench_config(B, T, H, N, path="auto"):
             "sharding": "batch x head shard per rank, no collective on the data path"}
 
 
-# DRAM bytes of one prefill launch from the ncu capture of this very workload (configuration 1,
+# DRAM bytes of one prefill launch from an ncu capture of this very workload (configuration 1,
 # B=8: 303.6 MB read + 41.8 MB written; part of y is still in L2 when the kernel ends); traffic is
-# proportional to the number of chains.  See profiles/wkv7_chunked_prefill_cfg1.md.
+# proportional to the number of chains.  A constant taken from that capture, not measured in the run.
 NCU_TRAFFIC_BYTES_CFG1 = 345.4e6   # ncu dram__bytes_read.sum + dram__bytes_write.sum, B=8
+NCU_TRAFFIC_SOURCE = "ncu capture of the chunked prefill kernel on configuration 1 (constant, scaled by B/8)"
 
 
 def sustained_tflops():
@@ -170,22 +171,23 @@ def run_reference(args):
     entry.load_package()
     from rwkv_rs_stable_b200 import workloads
     threads = oracle.use_all_cores()
-    # One step = all T tokens of `threads` chains (a bounded sample of the 96 chains).
-    inp = workloads.wkv7_inputs(1, CFG1["T"], threads, 64, seed=1, dtype=torch.bfloat16)
+    # One step = the whole configuration-1 workload: all T tokens of all B*H chains, OpenMP over the chains.
+    chains = CFG1["B"] * CFG1["H"]
+    inp = workloads.wkv7_inputs(1, CFG1["T"], chains, 64, seed=1, dtype=torch.bfloat16)
     f = [inp[n].float().numpy() for n in "rwkvab"]
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(args.warmup):
         oracle.wkv7(*f, None, precision="f32")
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, args.steps)
     t0 = time.perf_counter()
     for _ in range(steps):
         oracle.wkv7(*f, None, precision="f32")
     dt = (time.perf_counter() - t0) / steps
-    value = threads * CFG1["T"] / dt / CFG1["H"]
-    sample = (f"{threads} of {CFG1['B'] * CFG1['H']} (b,h) chains x T={CFG1['T']} per step "
-              f"(fp32 oracle port, OpenMP), {steps} steps")
+    value = chains * CFG1["T"] / dt / CFG1["H"]
+    sample = (f"all {chains} (b,h) chains x T={CFG1['T']} per step (fp32 oracle port, OpenMP over chains), "
+              f"{steps} steps after {args.warmup} warm-up steps")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": bench_config(**CFG1),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
@@ -208,6 +210,7 @@ def main():
     ap.add_argument("--no-prefill-other", action="store_true")
     ap.add_argument("--no-lm-head", action="store_true")
     ap.add_argument("--no-forward", action="store_true")
+    ap.add_argument("--no-cfg4", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: B=4 instead of 8 (151 MB of inputs, still larger than L2)")
     args = ap.parse_args()
@@ -306,6 +309,34 @@ def main():
     if not ((y_host.float() - y_dev).abs().max() <= 1e-3 * y_dev.abs().max() + 2 ** -8 * y_dev.abs().max()
             and (s_host - s_dev).abs().max() <= 5e-4 * s_dev.abs().max()):
         raise SystemExit("end-to-end result differs from the device-resident call")
+
+    # ---- bare host-to-device copies of one step's inputs (what bounds `e2e`) ---------------
+    # Every rank copies its six pinned input tensors to the device, nothing else, all ranks at once:
+    # the ceiling of the end-to-end figure above, whose steps move the same bytes plus y and S_T back.
+    host_copy = None
+    if True:
+        hc_steps = 5
+        for d_, h_ in zip(six, pinned):
+            d_.copy_(h_, non_blocking=True)
+        sync_all()
+        h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h0.record()
+        for _ in range(hc_steps):
+            for d_, h_ in zip(six, pinned):
+                d_.copy_(h_, non_blocking=True)
+        h1.record()
+        sync_all()
+        th = torch.tensor([h0.elapsed_time(h1) / hc_steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(th, op=dist.ReduceOp.MAX)
+        copy_gbs = h2d / (float(th.item()) * 1e-3) / 1e9
+        e2e_gbs = h2d / (float(te.item()) / e2e_steps * 1e-3) / 1e9
+        host_copy = {"what": f"{hc_steps} x six pinned input tensors ({h2d} B) host to device per rank, all {world} "
+                             "ranks at once, no kernels; slowest rank",
+                     "h2d_gb_per_s_per_rank": copy_gbs, "h2d_gb_per_s_all_ranks": copy_gbs * world,
+                     "e2e_h2d_gb_per_s_per_rank": e2e_gbs,
+                     "e2e_over_copy_ceiling": e2e_gbs / copy_gbs,
+                     "e2e_bound": "host copies" if e2e_gbs >= 0.8 * copy_gbs else "pipeline"}
 
     # ---- the same prefill kernel at the other configurations' per-GPU shapes --------------
     # (Runs before the tensor-core legs: right after the LM-head leg the SM clock is still held down by the
@@ -645,6 +676,92 @@ def main():
                          "output_abs_mean": float(cout.float().abs().mean().item())}
         del cx, ckw, cvw, cws, cout
 
+    # ---- configuration 4 as a configuration: heads sharded over the ranks -----------------
+    # 7B shape (H = 64 heads of 64, C = 4096), B = 4 sequences of T = 65 536 tokens.  One layer's WKV7
+    # call on this rank's heads (modules/time_mixer/mod.rs:187-198 makes one call per layer over
+    # [B,T,H,N]), the all-gather of the head-split y into [B,T,H,N] on every rank (C1), and the
+    # vocabulary-sharded LM head with the log-sum-exp combine over NCCL (C2) on a bounded number of rows.
+    cfg4 = None
+    if world > 1 and 64 % world == 0 and not args.small and not args.no_cfg4:
+        from rwkv_rs_stable_b200 import dist as rdist4
+        torch.cuda.empty_cache()
+        B4, T4, H4 = 4, 65536, 64
+        bs, hs = rdist4.shard_ranges(B4, H4, world)[rank]
+        Bl4, Hl4 = bs.stop - bs.start, hs.stop - hs.start
+        in4 = workloads.wkv7_inputs(Bl4, T4, Hl4, 64, seed=400 + rank, dtype=torch.bfloat16, device=dev)
+        seq4 = pkg.Wkv7PretrainForwardInputs(*[in4[n] for n in "rwkvab"])
+        s04 = torch.zeros(Bl4, Hl4, 64, 64, device=dev)
+        y4, so4 = torch.empty_like(in4["r"]), torch.empty_like(s04)
+        ws4_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bl4, T4, Hl4, 64, pkg.BF16))
+        ws4 = torch.empty(max(ws4_bytes, 1), dtype=torch.uint8, device=dev)
+        call4 = pkg.Wkv7StatepassCall(s04, seq4, y4, so4, ws4)
+
+        def timed_all(fn, reps):
+            fn()
+            sync_all()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(reps):
+                r_ = fn()
+            b_.record()
+            sync_all()
+            t_ = torch.tensor([a_.elapsed_time(b_) / reps], device=dev, dtype=torch.float64)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            return float(t_.item()), r_
+
+        wkv4_ms, _ = timed_all(call4, 3)
+        gather_ms, full4 = timed_all(lambda: rdist4.gather_outputs(y4, B4, H4), 2)
+        gather_ok = bool(torch.equal(full4[bs, :, hs], y4))
+        # every rank's slot must hold that rank's tensor: compare a checksum of each slot with its owner's
+        sums = torch.stack([full4[b_, :, h_].float().sum() for b_, h_ in rdist4.shard_ranges(B4, H4, world)])
+        own = torch.zeros(world, device=dev)
+        own[rank] = y4.float().sum()
+        dist.all_reduce(own)
+        gather_ok = gather_ok and bool(torch.equal(sums, own))
+        okt = torch.tensor([1.0 if gather_ok else 0.0], device=dev)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        gather_ok = bool(okt.item() == 1.0)
+        y_bytes = B4 * T4 * H4 * 64 * 2
+        del full4, in4, seq4, y4, call4
+        torch.cuda.empty_cache()
+        R4, C4, V4 = 32768, 4096, 65536
+        x4, _, t4 = workloads.lm_head_inputs(R4, C4, 8, seed=4, device=dev)        # same rows on every rank
+        t4 = torch.randint(0, V4, (R4,), generator=torch.Generator(device=dev).manual_seed(44), device=dev)
+        lo4, hi4 = rdist4.vocab_shard(V4, rank, world)
+        g4 = torch.Generator(device=dev)
+        g4.manual_seed(4000 + rank)
+        w4 = (torch.randn((hi4 - lo4, C4), generator=g4, device=dev) * 0.02).to(torch.bfloat16)
+        lm4_ms, (lse4, loss4) = timed_all(lambda: rdist4.lm_head_ce_sharded(pkg, x4, w4, t4, lo4), 3)
+        lm4_flops = 2.0 * R4 * C4 * V4
+        peak4, _ = measured_peaks()
+        tfp4 = 1653.6
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                tfp4 = float(json.load(f)["bf16_tflops"])
+        except Exception:
+            pass
+        wkv4_bytes = B4 * T4 * H4 * BYTES_PER_TOKEN_HEAD + B4 * H4 * STATE_BYTES
+        cfg4 = {"workload": f"cfg4 layer: B={B4} T={T4} H={H4} N=64 bf16, heads sharded over {world} GPUs "
+                            f"({Bl4} x {Hl4} = {Bl4 * Hl4} chains per rank), S0 = 0",
+                "wkv7_ms": wkv4_ms, "wkv7_tokens_per_s": B4 * T4 / (wkv4_ms * 1e-3),
+                "wkv7_gb_per_s": wkv4_bytes / (wkv4_ms * 1e-3) / 1e9,
+                "wkv7_frac_of_hbm_peak": wkv4_bytes / (wkv4_ms * 1e-3) / 1e9 / (peak4 * world),
+                "wkv7_hbm_roof_ms": wkv4_bytes / (peak4 * world * 1e9) * 1e3,
+                "gather": "NCCL all-gather of the head-split y into [B,T,H,N] on every rank + one strided copy per rank",
+                "gather_ms": gather_ms, "gather_bytes_full_tensor": y_bytes,
+                "gather_bus_gb_per_s": y_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9,
+                "gather_checked": gather_ok,
+                "lm_head": f"R={R4} of {B4 * T4} rows, C={C4}, V={V4} sharded {hi4 - lo4} columns per rank, "
+                           "all-gather of [R,3] partials + combine on every rank",
+                "lm_head_ms": lm4_ms, "lm_head_tflops": lm4_flops / (lm4_ms * 1e-3) / 1e12,
+                "lm_head_frac_of_bf16_peak": lm4_flops / (lm4_ms * 1e-3) / 1e12 / (tfp4 * world),
+                "lm_head_frac_of_bf16_sustained_peak": lm4_flops / (lm4_ms * 1e-3) / 1e12 / (sustained_tflops() * world),
+                "lm_head_mean_loss": float(loss4.mean().item())}
+        if not gather_ok:
+            raise SystemExit("cfg4 leg: the gathered y differs from the rank-local shards")
+        del x4, w4, t4, s04, so4, ws4
+        torch.cuda.empty_cache()
+
     if world > 1:
         dist.barrier()
     if rank != 0:
@@ -658,31 +775,68 @@ def main():
     if decode is not None:
         decode["frac_of_hbm_peak"] = decode["state_gb_per_s"] / (peak * world)
         decode["peak"] = f"{world} x {peak} GB/s {peak_kind}"
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES_CFG1 * (B / 8.0) if args.path != "sequential" else None,
+                "traffic_source": NCU_TRAFFIC_SOURCE if args.path != "sequential" else None,
+                "peak_source": peak_kind,
+                "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kernel_ms}
+    if decode is not None:
+        # the metric names two figures: the second one (decode state GB/s against the HBM peak) rides here
+        roofline["decode_gb_per_s"] = decode["state_gb_per_s"]
+        roofline["decode_frac"] = decode["frac_of_hbm_peak"]
+        roofline["decode_ms_per_step"] = decode["ms_per_step"]
+    cpu = None
+    if not args.no_cpu_baseline:
+        oracle = entry.load_oracle()
+        oracle.build()
+        cpu = cpu_baseline(oracle, workloads, torch)
+
+    def pick(obj, *keys):
+        return None if obj is None else {k: obj.get(k) for k in keys}
+
+    # One line; the bulky per-leg objects come first and the compact figures last, so that a reader who
+    # keeps only the end of the line still has every number the metric names.
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate, bf16 I/O", "data": "synthetic",
         "config": bench_config(B, T, H, N, args.path),
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_CFG1 * (B / 8.0) if args.path != "sequential" else None,
-                     "peak_source": peak_kind,
-                     "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kernel_ms},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
-        "decode": decode,
-        "streaming": streaming,
-        "lm_head_ce": lm_head,
-        "channel_mixer": channel_mixer,
-        "train": train,
-        "prefill_other_configs": prefill_other,
         "cfg2_forward": forward,
+        "prefill_other_configs": prefill_other,
+        "train": train,
+        "streaming": streaming,
+        "channel_mixer": channel_mixer,
+        "lm_head_ce": lm_head,
+        "decode": decode,
+        "cfg4": cfg4,
+        "host_copy": host_copy,
+        "clocks": clocks,
+        "gpu_launches": int(launches),
+        "summary": {
+            "prefill_cfg1": {"ms": kernel_ms, "tokens_per_s": value, "frac_of_hbm_peak": achieved / peak},
+            "prefill_other": None if prefill_other is None else
+                {k: {"ms": v["ms"], "frac_of_hbm_peak": v["frac_of_hbm_peak"]} for k, v in prefill_other.items()},
+            "decode": pick(decode, "ms_per_step", "state_gb_per_s", "frac_of_hbm_peak", "tokens_per_s"),
+            "lm_head_ce": pick(lm_head, "ms", "tflops", "frac_of_bf16_peak", "frac_of_bf16_sustained_peak"),
+            "channel_mixer": pick(channel_mixer, "ms", "tflops", "frac_of_bf16_peak", "frac_of_bf16_sustained_peak"),
+            "cfg2_forward": pick(forward, "ms", "tokens_per_s"),
+            "train": pick(train, "forward_saved_ms", "forward_saved_frac_of_hbm_peak", "backward_ms",
+                          "backward_frac_of_hbm_peak"),
+            "streaming_frac_of_hbm_peak": None if streaming is None else
+                {k: v["frac_of_hbm_peak"] for k, v in streaming.items() if isinstance(v, dict)},
+            "cfg4": pick(cfg4, "wkv7_ms", "wkv7_frac_of_hbm_peak", "gather_ms", "lm_head_ms", "lm_head_frac_of_bf16_peak"),
+            "host_copy": pick(host_copy, "h2d_gb_per_s_per_rank", "e2e_h2d_gb_per_s_per_rank", "e2e_bound"),
+        },
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "timing": f"{e2e_steps} passes issued back to back from pinned host buffers, one device-timed "
+                          "interval around all of them, only the last pass joined before the closing event "
+                          "(a throughput figure, not the latency of one pass)"},
+        "roofline": roofline,
     }
-    if not args.no_cpu_baseline:
-        oracle = entry.load_oracle()
-        oracle.build()
-        out["cpu_baseline"] = cpu_baseline(oracle, workloads, torch)
+    if cpu is None:
+        del out["cpu_baseline"]
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -23,8 +23,15 @@
  *    Rust shim does `panic!("{}", rwkv7_last_error_message())` on non-zero.
  *  - All tensors must be contiguous row-major (the reference asserts
  *    `is_contiguous()`, wkv7/mod.rs:56-76).
- *  - The library is re-entrant; it keeps no per-call global state apart from a
- *    thread-local error message and a per-device status word.
+ *  - The compute entry points are re-entrant: a call keeps no state of its own
+ *    beyond a thread-local error message and a per-device status word.  Two
+ *    process-wide switches exist for tests and benchmarks, rwkv7_set_wkv7_path
+ *    and rwkv7_set_wkv7_cluster; they are atomics read once per call, they
+ *    change which kernel a later call on ANY thread takes (and, for the path,
+ *    what rwkv7_wkv7_workspace_bytes reports), and a process that never calls
+ *    them gets the automatic choice everywhere.  Per-device caches (SM count,
+ *    resident-cluster counts, the status word, the address of the fixed scratch
+ *    array) are filled once under a mutex.
  */
 #ifndef RWKV7_B200_H_
 #define RWKV7_B200_H_
@@ -96,7 +103,9 @@ int rwkv7_abi_version(void);
 const char *rwkv7_status_string(int status);
 /* Thread-local text of the last non-zero status returned on this thread. */
 const char *rwkv7_last_error_message(void);
-/* Process-wide override of the WKV7 kernel choice (tests and benchmarks). */
+/* Process-wide override of the WKV7 kernel choice (tests and benchmarks).  It also changes
+ * what rwkv7_wkv7_workspace_bytes reports (the sequential path needs none), so size the
+ * workspace after setting it, and do not flip it while calls are in flight on other threads. */
 int rwkv7_set_wkv7_path(int path);
 int rwkv7_get_wkv7_path(void);
 

@@ -295,7 +295,7 @@ class Wkv7SavedForward:
     """Outputs of the training forward: what the reference's forward kernels return under
     autodiff (``wkv7/forward.rs:368-375``)."""
 
-    output: torch.Tensor
+    output: Optional[torch.Tensor]
     next_state: Optional[torch.Tensor]
     snapshots: torch.Tensor            # [B, H, T/chunk_len, N, N] fp32
     state_replacement: torch.Tensor    # [B, T, H, N]
@@ -366,14 +366,24 @@ class _Wkv7Function(torch.autograd.Function):
     def forward(ctx, r, w, k, v, a, b, s0, chunk_len):
         inputs = Wkv7PretrainForwardInputs(r, w, k, v, a, b, chunk_len=chunk_len)
         saved = wkv7_forward_saved(inputs, s0, want_state=True)
-        ctx.inputs, ctx.saved, ctx.has_state, ctx.s0 = inputs, saved, s0 is not None, s0
-        ctx.mark_non_differentiable(saved.snapshots, saved.state_replacement)
+        # Only what the backward pass reads is kept, and through save_for_backward: the node then
+        # holds no reference to its own outputs (no cycle) and autograd's version counters catch an
+        # in-place change of an input between forward and backward.
+        keep = [r, w, k, v, a, b, saved.snapshots, saved.state_replacement]
+        if s0 is not None:
+            keep.append(s0)
+        ctx.save_for_backward(*keep)
+        ctx.has_state, ctx.chunk_len = s0 is not None, chunk_len
         return saved.output, saved.next_state
 
     @staticmethod
     def backward(ctx, dy, ds):
-        grads, ds0 = wkv7_backward(ctx.inputs, ctx.saved, dy, None if ds is None else ds.contiguous(),
-                                   initial_state=ctx.s0, want_state_grad=ctx.has_state)
+        t = ctx.saved_tensors
+        inputs = Wkv7PretrainForwardInputs(*t[:6], chunk_len=ctx.chunk_len)
+        saved = Wkv7SavedForward(output=None, next_state=None, snapshots=t[6], state_replacement=t[7])
+        s0 = t[8] if ctx.has_state else None
+        grads, ds0 = wkv7_backward(inputs, saved, dy, None if ds is None else ds.contiguous(),
+                                   initial_state=s0, want_state_grad=ctx.has_state)
         return (*grads, ds0, None)
 
 

@@ -104,9 +104,9 @@ int check_wkv7_state(const TensorInfo &state, const TensorInfo &r) {
     return RWKV7_OK;
 }
 
-int wkv7_run(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t chunk_len,
-             rwkv7_tensor *y, rwkv7_tensor *s_out, bool want_state, void *workspace,
-             size_t workspace_bytes, rwkv7_stream stream, bool has_s0) {
+// Contract checks of a WKV7 forward call in the reference's order; fills `p` on success.
+int wkv7_validate(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t chunk_len,
+                  rwkv7_tensor *y, rwkv7_tensor *s_out, bool want_state, bool has_s0, Wkv7Args &p) {
     clear_error();
     static const char *names[6] = {"receptance", "weight_decay", "replacement_key",
                                    "value", "removal_key_normalized", "replacement"};
@@ -124,7 +124,7 @@ int wkv7_run(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t
     RWKV7_TRY(check_contiguous(out));
     if (want_state) RWKV7_TRY(check_wkv7_state(TensorInfo{"next_state", s_out}, r));
 
-    Wkv7Args p{};
+    p = Wkv7Args{};
     p.r = six_t[0]->data; p.w = six_t[1]->data; p.k = six_t[2]->data;
     p.v = six_t[3]->data; p.a = six_t[4]->data; p.b = six_t[5]->data;
     p.s0 = has_s0 ? static_cast<const float *>(s0->data) : nullptr;
@@ -133,6 +133,11 @@ int wkv7_run(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t
     p.B = r.dim(0); p.T = r.dim(1); p.H = r.dim(2); p.N = r.dim(3);
     p.bf16 = r.t->dtype == RWKV7_BF16;
     p.device = r.t->device;
+    return RWKV7_OK;
+}
+
+// Picks the kernel for validated arguments and enqueues it.
+int wkv7_dispatch(Wkv7Args &p, void *workspace, size_t workspace_bytes, rwkv7_stream stream) {
     if (p.B == 0 || p.H == 0) return RWKV7_OK;  // nothing to compute
 
     DeviceGuard guard(p.device);
@@ -163,6 +168,14 @@ int wkv7_run(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t
         return fail(RWKV7_ERR_UNSUPPORTED, "Unsupported: head size N=%lld exceeds 128", (long long)p.N);
     if (int e = launch_wkv7_sequential(p, (cudaStream_t)stream)) return cuda_fail("wkv7 sequential launch", e);
     return RWKV7_OK;
+}
+
+int wkv7_run(const rwkv7_tensor *s0, const rwkv7_tensor *const six_t[6], int64_t chunk_len,
+             rwkv7_tensor *y, rwkv7_tensor *s_out, bool want_state, void *workspace,
+             size_t workspace_bytes, rwkv7_stream stream, bool has_s0) {
+    Wkv7Args p{};
+    RWKV7_TRY(wkv7_validate(s0, six_t, chunk_len, y, s_out, want_state, has_s0, p));
+    return wkv7_dispatch(p, workspace, workspace_bytes, stream);
 }
 
 // Shared contract of the [1,1,C] scale tensors (mix6/io.rs:48-86, addcmul/io.rs:42-54).
@@ -321,23 +334,24 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *s0, const rwkv7_tenso
                                        const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
                                        const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
                                        rwkv7_tensor *next_state, rwkv7_stream stream) {
-    clear_error();
-    if (r == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: tensor descriptor receptance is null");
-    if (r->ndim == 4) {
-        const int64_t chains = r->shape[0] * r->shape[2];
-        if (chains > wkv7_static_scratch_max_chains())
-            return fail(RWKV7_ERR_UNSUPPORTED,
-                        "Unsupported: B*H = %lld chains exceed the %lld-chain capacity of the allocation-free "
-                        "entry point; use rwkv7_fused_wkv7_statepass with a workspace",
-                        (long long)chains, (long long)wkv7_static_scratch_max_chains());
-    }
-    DeviceGuard guard(r->device);
+    // The reference-ordered contract checks come first, so that a malformed call reports the same
+    // error here as through rwkv7_fused_wkv7_statepass; only then the capacity of the fixed array.
+    const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
+    Wkv7Args p{};
+    RWKV7_TRY(wkv7_validate(s0, six, chunk_len, output, next_state, true, true, p));
+    const int64_t cap = wkv7_static_scratch_max_chains();
+    if (p.B > cap || p.H > cap || p.B * p.H > cap)
+        return fail(RWKV7_ERR_UNSUPPORTED,
+                    "Unsupported: B*H = %lld chains exceed the %lld-chain capacity of the allocation-free "
+                    "entry point; use rwkv7_fused_wkv7_statepass with a workspace",
+                    (long long)(p.B * p.H), (long long)cap);
+    if (p.B == 0 || p.H == 0) return RWKV7_OK;
+    DeviceGuard guard(p.device);
     if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
-    if (int e = wkv7_static_scratch(r->device, &scratch, &scratch_bytes)) return cuda_fail("static scratch address", e);
-    const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
-    return wkv7_run(s0, six, chunk_len, output, next_state, true, scratch, scratch_bytes, stream, true);
+    if (int e = wkv7_static_scratch(p.device, &scratch, &scratch_bytes)) return cuda_fail("static scratch address", e);
+    return wkv7_dispatch(p, scratch, scratch_bytes, stream);
 }
 
 namespace {

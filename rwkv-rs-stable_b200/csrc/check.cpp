@@ -1,5 +1,7 @@
 #include "check.h"
 
+#include <cstdint>
+
 #include <cstdio>
 
 namespace rwkv7 {
@@ -140,6 +142,12 @@ int check_contiguous(const TensorInfo &x) {
             return fail(RWKV7_ERR_NOT_CONTIGUOUS, "NotContiguous: %s must be contiguous", x.name);
         expect *= x.t->shape[i];
     }
+    // Every kernel moves tensor data with 16-byte vector accesses or TMA; a view that starts at an odd
+    // element of its storage would fault on the device, so it is refused here, on the host.
+    if ((reinterpret_cast<uintptr_t>(x.t->data) & 15u) != 0)
+        return fail(RWKV7_ERR_UNSUPPORTED,
+                    "Unsupported: the data pointer of %s is not 16-byte aligned (the kernels use 16-byte "
+                    "vector accesses); pass a tensor whose storage offset is a multiple of 16 bytes", x.name);
     return RWKV7_OK;
 }
 

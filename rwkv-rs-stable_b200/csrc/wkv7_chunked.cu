@@ -894,17 +894,28 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     } else {
         if (tid == 0 && bad_decay) atomicOr(&flags[bh], 1);   // zeroed by the host before the launch
     }
-    if (!failed && s_out != nullptr && quarter < 2 && (nchunks - 1) % K == rank) {
+    auto store_state = [&]() {
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4)
             *reinterpret_cast<float4 *>(s_out + ((size_t)bh * kN + zj) * kN + cgrp * 16 + 4 * q4) =
                 make_float4(Z[4 * q4], Z[4 * q4 + 1], Z[4 * q4 + 2], Z[4 * q4 + 3]);
+    };
+    const bool owns_last = s_out != nullptr && quarter < 2 && (nchunks - 1) % K == rank;
+    if constexpr (K == 1) {
+        if (!failed && owns_last) store_state();
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, kTmemCols);
-    // No CTA of a cluster may exit while a peer can still write into its shared memory.
-    if constexpr (K > 1) cluster_sync_all();
+    if constexpr (K > 1) {
+        // No CTA of a cluster may exit while a peer can still write into its shared memory.
+        cluster_sync_all();
+        // The final state is written only if no CTA of the cluster flagged the chain: next_state may
+        // alias initial_state, and the sequential recomputation of a flagged chain starts from
+        // initial_state.  Every flag was OR-ed before the cluster barrier above (release / acquire at
+        // cluster scope), so the value read back here is final.
+        if (!failed && owns_last && atomicOr(&flags[bh], 0) == 0) store_state();
+    }
 }
 
 // ---- host side --------------------------------------------------------------------

@@ -323,10 +323,6 @@ int launch_seq(const Wkv7Args &p, cudaStream_t stream) {
         int rows = 64;
         if (chains < 2 * (int64_t)p.num_sms) rows = 32;
         if (chains * 2 < 2 * (int64_t)p.num_sms) rows = 16;
-        if (const char *env = std::getenv("RWKV7_SEQ_ROWS")) {
-            const int v = std::atoi(env);
-            if (v == 16 || v == 32 || v == 64) rows = v;
-        }
         if (rows == 64) return launch_seq64<T, 64>(p, stream);
         if (rows == 32) return launch_seq64<T, 32>(p, stream);
         return launch_seq64<T, 16>(p, stream);

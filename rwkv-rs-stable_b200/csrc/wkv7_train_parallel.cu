@@ -31,6 +31,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdint>
+
 #include "kernels.h"
 
 namespace rwkv7 {
@@ -343,7 +345,10 @@ __global__ void __launch_bounds__(kLocalThreads, 3) wkv7_bwd_local_kernel(LocalA
 }  // namespace
 
 bool wkv7_backward_parallel_supported(const Wkv7BackwardArgs &p) {
-    return p.bf16 && p.N == kN && p.chunk_len == kC && p.T >= 64 && p.T % kC == 0;
+    // The reversed run is the TMA prefill kernel (32-bit row coordinates): B*T >= 2^31 takes the
+    // token-by-token kernel.  (Pointer alignment is a host-side contract of every entry point.)
+    return p.bf16 && p.N == kN && p.chunk_len == kC && p.T >= 64 && p.T % kC == 0 &&
+           p.B * p.T < (int64_t(1) << 31);
 }
 
 // Workspace: six reversed tensors, the reversed run's two outputs (bf16 [B,T,H,64] each), its

@@ -186,3 +186,31 @@ def test_wkv7_path_switch(pkg):
     pkg.set_wkv7_path(pkg.WKV7_AUTO)
     with pytest.raises(pkg.KernelInputsError):
         pkg.set_wkv7_path(9)
+
+
+def test_unaligned_views_are_refused_on_the_host(pkg):
+    """A contiguous view that starts at an odd element of its storage is not 16-byte aligned.  Every
+    kernel (forward, both backward paths, the streaming kernels) uses 16-byte vector accesses or TMA, so
+    such a tensor is refused by the host-side contract check instead of faulting on the device."""
+    E = pkg.KernelInputsError
+    shape = (1, 64, 2, 64)
+    base = torch.zeros(1 * 64 * 2 * 64 + 1, dtype=torch.bfloat16)
+    view = base[1:].view(shape)
+    assert view.is_contiguous() and view.data_ptr() % 16 != 0
+    seq = _seq(pkg, shape, dtype=torch.bfloat16)
+    seq.receptance = view
+    with pytest.raises(E) as e:
+        pkg.wkv7_pretrain_custom(seq)
+    assert e.value.kind == "Unsupported" and "16-byte aligned" in str(e.value) and "receptance" in str(e.value)
+    # the backward entry points share the check
+    good = _seq(pkg, shape, dtype=torch.bfloat16)
+    saved = pkg.Wkv7SavedForward(output=None, next_state=None, snapshots=torch.zeros(1, 2, 4, 64, 64),
+                                 state_replacement=torch.zeros(shape, dtype=torch.bfloat16))
+    for parallel in (True, False):
+        with pytest.raises(E) as e:
+            pkg.wkv7_backward(good, saved, view, None, parallel=parallel)
+        assert e.value.kind == "Unsupported" and "16-byte aligned" in str(e.value)
+    with pytest.raises(E) as e:
+        pkg.addcmul_custom(view.view(1, 64, 128), torch.zeros(1, 64, 128, dtype=torch.bfloat16),
+                           torch.zeros(1, 1, 128, dtype=torch.bfloat16))
+    assert e.value.kind == "Unsupported" and "16-byte aligned" in str(e.value)

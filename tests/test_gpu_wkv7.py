@@ -81,16 +81,18 @@ def test_golden_fixtures(pkg, cuda, name):
     parity.assert_close_f32(s, g["s_out"], 2e-5, name)
 
 
-@pytest.mark.parametrize("rows", ["16", "32", "64"])
 @pytest.mark.parametrize("shape,dtype,state", [
     ((1, 64, 4, 64), torch.float32, None),        # benchmark configuration 0
     ((2, 37, 3, 64), torch.float32, "normal"),    # T not a multiple of 16
     ((3, 1, 5, 64), torch.float32, "normal"),     # decode step
     ((2, 200, 2, 64), torch.bfloat16, "normal"),
     ((4, 1, 8, 64), torch.bfloat16, "normal"),    # decode step, bf16 vectors
+    ((2, 21, 100, 64), torch.bfloat16, "normal"),  # 200 chains: 32 value rows per CTA on a 148-SM GPU
+    ((1, 19, 300, 64), torch.float32, "normal"),   # 300 chains: all 64 value rows in one CTA
 ])
-def test_sequential_n64(pkg, oracle, workloads, cuda, monkeypatch, rows, shape, dtype, state):
-    monkeypatch.setenv("RWKV7_SEQ_ROWS", rows)
+def test_sequential_n64(pkg, oracle, workloads, cuda, shape, dtype, state):
+    """The launcher gives a CTA 16, 32 or 64 of a chain's value rows, by the number of chains per SM;
+    the shapes cover the three cases."""
     inp = workloads.wkv7_inputs(*shape, seed=21, dtype=dtype, state=state)
     y_ref, s_ref = _oracle(oracle, inp)
     if state is None:
@@ -368,3 +370,66 @@ def test_last_wave_runs_as_clusters(pkg, oracle, workloads, cuda, T, extra):
     parity.assert_close_f32(s, s_ref, 1e-3, "state")
     assert np.array_equal(s[:, :sms], one_s[:, :sms])   # the first launch is the one-CTA kernel itself
     assert parity.headline(s[:, sms:], one_s[:, sms:]) <= 4e-4
+
+
+_LONG_CACHE = {}
+
+
+def _long_case(oracle, workloads, wmode):
+    """One chain over T = 65 536 (the context length of configuration 4) and its fp64 oracle result."""
+    if wmode not in _LONG_CACHE:
+        inp = workloads.wkv7_inputs(1, 65536, 1, 64, seed=65, dtype=torch.bfloat16)
+        if wmode == "strongest":
+            inp["w"] = torch.full_like(inp["w"], -0.5)   # the strongest decay the model's range allows
+        y_ref, s_ref = _oracle(oracle, inp)
+        inp["s0"] = torch.zeros(1, 1, 64, 64)
+        _LONG_CACHE[wmode] = (inp, y_ref, s_ref)
+    return _LONG_CACHE[wmode]
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 4])
+@pytest.mark.parametrize("wmode", ["benchmark", "strongest"])
+def test_long_context_against_oracle(pkg, oracle, workloads, cuda, wmode, cluster):
+    """Drift over 1024 chunks: one (b,h) chain of T = 65 536 tokens, bf16, zero initial state, against the
+    fp64 oracle (semantics: wkv7/mod.rs:179-242), through the one-CTA kernel and through the clusters of
+    2 and 4 CTAs that a head-sharded long-context prefill takes.  Inputs: the benchmark distribution, and
+    the same with the constant decay input w = -0.5 (per-token decay exp(-exp(-0.5)) = 0.545)."""
+    inp, y_ref, s_ref = _long_case(oracle, workloads, wmode)
+    try:
+        pkg.set_wkv7_cluster(cluster)
+        y, s = _run(pkg, cuda, inp, "statepass", pkg.WKV7_CHUNKED, reference_contract=False)
+    finally:
+        pkg.set_wkv7_cluster(0)
+    assert pkg.read_device_status(0) == 0
+    print(f"long context {wmode} cluster {cluster}: y {parity.headline(y, y_ref):.3e} "
+          f"state {parity.headline(s, s_ref):.3e}")
+    parity.assert_close_bf16_store(y, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s, s_ref, 1e-3, "state")
+
+
+@pytest.mark.parametrize("cluster", [2, 4])
+def test_cluster_keeps_an_aliased_state_for_the_fallback(pkg, oracle, workloads, cuda, cluster):
+    """next_state may be the same buffer as initial_state.  When one CTA of a cluster flags the chain for
+    the sequential recomputation (here: one 64-token chunk in the middle of the sequence has decay inputs
+    in [0.5, 1.5], the CTA that owns the last chunk sees nothing wrong), the chunked kernel must not have
+    written the final state over the initial state that the recomputation starts from."""
+    inp = workloads.wkv7_inputs(2, 768, 2, 64, seed=36, dtype=torch.bfloat16, state="normal")
+    w = inp["w"].float()
+    w[0, 5 * 64:6 * 64, 1] = torch.rand(64, 64) + 0.5   # chain (0,1), chunk 5 of 12
+    inp["w"] = w.to(torch.bfloat16)
+    y_ref, s_ref = _oracle(oracle, inp)
+    gpu = {k: v.to(cuda) for k, v in inp.items()}
+    seq = pkg.Wkv7PretrainForwardInputs(*[gpu[n] for n in "rwkvab"])
+    prev = pkg.get_wkv7_path()
+    try:
+        pkg.set_wkv7_path(pkg.WKV7_CHUNKED)
+        pkg.set_wkv7_cluster(cluster)
+        out = pkg.wkv7_statepass_custom(gpu["s0"], seq, reference_contract=False, next_state=gpu["s0"])
+        torch.cuda.synchronize()
+    finally:
+        pkg.set_wkv7_cluster(0)
+        pkg.set_wkv7_path(prev)
+    assert out.next_state.data_ptr() == gpu["s0"].data_ptr()
+    assert pkg.read_device_status(0) == 0
+    parity.assert_close_bf16_store(out.output.float().cpu().numpy(), y_ref, 1e-3, "y")
+    parity.assert_close_f32(out.next_state.cpu().numpy(), s_ref, 1e-3, "state")
