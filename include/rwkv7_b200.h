@@ -96,7 +96,8 @@ typedef struct rwkv7_tensor {
 typedef enum rwkv7_wkv7_path {
     RWKV7_WKV7_AUTO = 0,
     RWKV7_WKV7_SEQUENTIAL = 1,
-    RWKV7_WKV7_CHUNKED = 2
+    RWKV7_WKV7_CHUNKED = 2,
+    RWKV7_WKV7_SPLIT = 3
 } rwkv7_wkv7_path;
 
 int rwkv7_abi_version(void);

@@ -30,7 +30,7 @@ LIB_PATH = os.environ.get("RWKV7_B200_LIB") or os.path.join(_HERE, "librwkv7_b20
 
 MAX_DIMS = 5
 F32, BF16, F16, I32, I64, U32 = 0, 1, 2, 3, 4, 5
-WKV7_AUTO, WKV7_SEQUENTIAL, WKV7_CHUNKED = 0, 1, 2
+WKV7_AUTO, WKV7_SEQUENTIAL, WKV7_CHUNKED, WKV7_SPLIT = 0, 1, 2, 3
 
 _DTYPES = {
     torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16,

@@ -146,6 +146,21 @@ int wkv7_dispatch(Wkv7Args &p, void *workspace, size_t workspace_bytes, rwkv7_st
 
     const int path = g_wkv7_path.load();
     bool chunked = false;
+    if (path == RWKV7_WKV7_SPLIT) {
+        if (!wkv7_split_supported(p))
+            return fail(RWKV7_ERR_UNSUPPORTED,
+                        "Unsupported: the two-kernel WKV7 prefill needs N == 64 and BF16 tensors (got N=%lld)", (long long)p.N);
+        const size_t need = wkv7_split_min_workspace_bytes(p.B, p.T, p.H, p.N);
+        if (workspace == nullptr || workspace_bytes < need)
+            return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL,
+                        "WorkspaceTooSmall: wkv7 needs %zu workspace bytes, got %zu", need,
+                        workspace == nullptr ? (size_t)0 : workspace_bytes);
+        if (int e = launch_wkv7_split(p, workspace, workspace_bytes, (cudaStream_t)stream))
+            return cuda_fail("wkv7 split launch", e);
+        if (int e = launch_wkv7_sequential_flagged(p, static_cast<const int *>(workspace), (cudaStream_t)stream))
+            return cuda_fail("wkv7 flagged-chain launch", e);
+        return RWKV7_OK;
+    }
     if (path == RWKV7_WKV7_CHUNKED) {
         if (!wkv7_chunked_supported(p))
             return fail(RWKV7_ERR_UNSUPPORTED,
@@ -254,7 +269,7 @@ const char *rwkv7_status_string(int status) {
 const char *rwkv7_last_error_message(void) { return last_error(); }
 
 int rwkv7_set_wkv7_path(int path) {
-    if (path < RWKV7_WKV7_AUTO || path > RWKV7_WKV7_CHUNKED)
+    if (path < RWKV7_WKV7_AUTO || path > RWKV7_WKV7_SPLIT)
         return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: unknown wkv7 path %d", path);
     g_wkv7_path.store(path);
     return RWKV7_OK;
@@ -300,8 +315,9 @@ int rwkv7_selftest_bounded_wait(int device, int64_t max_polls, rwkv7_stream stre
 }
 
 size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype) {
-    (void)dtype;
-    if (g_wkv7_path.load() == RWKV7_WKV7_SEQUENTIAL) return 0;
+    const int path = g_wkv7_path.load();
+    if (path == RWKV7_WKV7_SEQUENTIAL) return 0;
+    if (path == RWKV7_WKV7_SPLIT && dtype == RWKV7_BF16) return wkv7_split_workspace_bytes(B, T, H, N);
     return wkv7_chunked_workspace_bytes(B, T, H, N);
 }
 

@@ -71,6 +71,19 @@ bool wkv7_chunked_supported(const Wkv7Args &p);
 int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes,
                         cudaStream_t stream);
 
+// Two-kernel tensor-core prefill (N == 64, bf16, fp16 operands): the operator of every 64-token chunk
+// is built for all chunks in parallel, then one scan per chain applies them.  The workspace holds the
+// per-chain fallback flags (first B*H ints), a carried state per chain and the operators of one
+// segment of chunks; `wkv7_split_workspace_bytes` is the size the launcher prefers (fewest segments
+// within its operator budget), `wkv7_split_min_workspace_bytes` the least it can work with.
+// Chains it cannot resolve (decay range, non-finite operators) are left flagged for the caller.
+size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+size_t wkv7_split_min_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+bool wkv7_split_supported(const Wkv7Args &p);
+int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// Sequential recomputation of the chains whose flag is set (exits at once for the others).
+int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStream_t stream);
+
 // Cluster size of the chunked kernel: 0 = by the number of chains (default), else 1, 2 or 4.
 int wkv7_cluster_override();
 void wkv7_set_cluster_override(int k);

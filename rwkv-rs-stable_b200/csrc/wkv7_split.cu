@@ -1,0 +1,890 @@
+// Two-kernel WKV7 prefill for sm_100a (N == 64, bf16 tensors, 64-token chunks, fp16 tensor-core
+// operands): everything that does not depend on the running state is computed for all chunks in
+// parallel by `wkv7_chunk_operator_kernel`, which folds a chunk into one linear operator, and
+// `wkv7_state_scan_kernel` then walks each (b,h) chain with one dependent tensor-core product per
+// chunk.
+//
+// Reference semantics: crates/rwkv-nn/src/kernels/train/time_mixer/wkv7/mod.rs:179-242 (token
+// recurrence; the reference kernel, kernel.rs:82-195, scans token by token).
+//
+// Per chain and chunk, with the in-chunk inclusive prefix c_t of the log-decay l_t = -exp(w_t),
+// c_L its value at the chunk's end and the reference point m = c_L / 2 (per channel):
+//     At = a_t e^{c_{t-1} - m}   Rt = r_t e^{c_t - m}   Bh = b_t e^{m - c_t}   Kh = k_t e^{m - c_t}
+//     G  = [At;Rt] [Bh;Kh]^T  ->  A_ab, A_ak (strictly lower), A_rb, A_rk (lower)
+//     T  = (I - A_ab)^-1                                   (fp32, CUDA cores, blocked)
+//     [A~ | A~k] = T [At e^{m} | A_ak]                     (u_t = S_{t-1} a_t = A~ S^T + A~k V)
+//     P  = A~^T Bh     Kt = Kh + A~k^T Bh     W = R + A_rb A~     Ark = A_rk + A_rb A~k
+// so that, for the state S[i][j] entering the chunk and V[s][i]:
+//     S'[i][j'] = e^{c_L} S[i][j'] + e^{c_L - m} ( sum_j S[i][j] P[j][j'] + sum_s V[s][i] Kt[s][j'] )
+//     y[t][i]   = sum_j W[t][j] S[i][j] + sum_s Ark[t][s] V[s][i].
+// The operator of a chunk is the 128 x 128 fp16 matrix O[k][n], k = (j | s), n = (j' | t):
+//     O = [[P, W^T], [Kt, Ark^T]],
+// stored in global memory exactly as its shared-memory image (two 128-row panels of 128 bytes,
+// 128-byte swizzle), together with the two fp32 vectors e^{c_L} and e^{c_L - m}.
+//
+// Every tensor-core operand is fp16 (the same 11-bit significand as tf32).  fp16 has a narrow
+// exponent range, which is why the decay factors are taken relative to the middle of the chunk;
+// a chunk whose total log-decay exceeds kMaxLogDecay in any channel, or whose operator holds a
+// non-finite value, flags its chain, and flagged chains are recomputed by the next kernel in line
+// (the launcher passes them to the tf32 chunked kernel or the sequential scan).
+//
+// Shared-memory operand tiles are [rows][64] 16-bit panels with 128-byte rows, 16-byte chunks
+// XOR-ed with (row & 7).  The same tile serves as a K-major operand (rows = M/N index) and as an
+// MN-major operand (rows = K index): no transposed copies exist anywhere.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "kernels.h"
+#include "sm100_umma.cuh"
+
+namespace rwkv7 {
+
+int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStream_t stream);
+
+namespace {
+
+using namespace sm100;
+
+constexpr int kN = 64;
+constexpr int kL = 64;
+constexpr float kMaxLogDecay = 15.f;     // |c_L| per chunk and channel that fp16 operands resolve
+constexpr float kOpScale = 8.f;          // decay-scaled operands are stored times 8: centres fp16's range
+constexpr float kInvOpScale = 1.f / kOpScale;
+constexpr uint32_t kPanel = 8192;        // one [64][64] 16-bit tile
+constexpr uint32_t kOperatorBytes = 4 * kPanel;   // O: 128 x 128 fp16
+constexpr uint32_t kVecFloats = 128;              // e^{c_L}[64], e^{c_L - m}[64]
+
+// Byte offset of element (row, col) in a [rows][64] 16-bit panel.
+__device__ __forceinline__ uint32_t off16(int row, int col) {
+    return (uint32_t)row * 128u + ((((uint32_t)col >> 3) ^ ((uint32_t)row & 7u)) << 4) + ((uint32_t)col & 7u) * 2u;
+}
+// Descriptors.  K-major: rows = M/N index, one K-step (16 elements) is 32 bytes along the row.
+// MN-major: rows = K index, one K-step is 16 rows (2048 bytes); `lbo` is the distance between
+// consecutive 64-element blocks of the M/N index.
+__device__ __forceinline__ uint64_t dK(uint32_t addr, int ks) { return make_smem_desc(addr + (uint32_t)ks * 32u, 16u, 1024u); }
+__device__ __forceinline__ uint64_t dMN(uint32_t addr, uint32_t lbo, int ks) {
+    return make_smem_desc(addr + (uint32_t)ks * 2048u, lbo, 1024u);
+}
+__host__ __device__ constexpr uint32_t idesc16(int M, int N, bool a_mn, bool b_mn) {
+    return make_idesc(kFmtF16, M, N, a_mn, b_mn);
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+__device__ __forceinline__ bool h2_nonfinite(uint32_t u) {
+    return ((u & 0x7c00u) == 0x7c00u) || ((u & 0x7c000000u) == 0x7c000000u);
+}
+__device__ __forceinline__ float2 unpack_h2(uint32_t u) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&u));
+}
+__device__ __forceinline__ float2 unpack_bf2(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+
+// ------------------------------------------------------------------------------------------
+// Kernel 1: the operator of every chunk.  One CTA of 256 threads works through chunks
+// blockIdx.x, blockIdx.x + gridDim.x, ...; two CTAs share an SM.
+// ------------------------------------------------------------------------------------------
+constexpr int kThreads1 = 256;
+// shared-memory map (bytes from a 1024-aligned base)
+constexpr uint32_t kRaw = 0;                       // five bf16 tiles r, w, k, a, b (40 KB); later scratch
+constexpr uint32_t kRawBytes = 5 * kPanel;
+constexpr int kPitchF = 68;                        // floats per row of the fp32 scratch matrices
+constexpr uint32_t kAm = kRaw;                     // fp32 A_ab [64][68]
+constexpr uint32_t kTm = kAm + 64 * kPitchF * 4;   // fp32 T    [64][68]
+constexpr uint32_t kWm = kTm + 64 * kPitchF * 4;   // fp32 join scratch [32][36]
+constexpr uint32_t kT16 = kRaw;                    // fp16 T [t][u] (over A_ab, dead by then)
+constexpr uint32_t kAf = kRaw + 18 * 1024;         // fp16 [A~ e^m | A~k]^T [c][t], 128 rows (over T fp32, dead by then)
+constexpr uint32_t kRtrue = kRaw + kRawBytes;      // fp16 r_t e^{c_t} [t][j]
+constexpr uint32_t kAR = kRtrue + kPanel;          // fp16 [At; Rt] (Rt's half later holds A_ak)
+constexpr uint32_t kArb = kAR + 2 * kPanel;        // fp16 A_rb [t][s]
+constexpr uint32_t kArk = kArb + kPanel;           // fp16 A_rk [t][s]
+constexpr uint32_t kStage = kAR;                   // the finished operator (32 KB) over AR, A_rb, A_rk
+constexpr uint32_t kBK = kArk + kPanel;            // fp16 [Bh; Kh]
+constexpr uint32_t kI64 = kBK + 2 * kPanel;        // fp16 identity [64][64]
+constexpr uint32_t kMisc1 = kI64 + kPanel;         // barriers, group sums, e^m
+constexpr uint32_t kSmem1 = kMisc1 + 3072 + 1024;  // + alignment slack
+static_assert(kWm + 32 * 36 * 4 <= kRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
+static_assert(kAf + 2 * kPanel <= kRaw + kRawBytes, "A~ tile exceeds the raw-tile region");
+static_assert(kStage + kOperatorBytes == kBK, "operator staging must cover AR, A_rb, A_rk exactly");
+static_assert(2 * (kSmem1 + 1024) <= 232448, "two CTAs per SM");
+
+struct OperatorMaps {
+    CUtensorMap m[5];   // r, w, k, a, b as [B*T, H*N] bf16, box 64 x 64, no swizzle
+};
+enum { XR = 0, XW = 1, XK = 2, XA = 3, XB = 4 };
+
+__global__ void __launch_bounds__(kThreads1, 2)
+wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned char *__restrict__ operators,
+                           float *__restrict__ vectors, int *__restrict__ flags, int Tlen, int H, int chunk0,
+                           int seg_chunks, int nchains, int *status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
+        return;
+    }
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quarter = warp & 3, hf = warp >> 2;
+    const int row = quarter * 32 + lane;          // TMEM lane of this thread
+    unsigned char *raw = smem + kRaw;
+    float *Am = reinterpret_cast<float *>(smem + kAm);
+    float *Tm = reinterpret_cast<float *>(smem + kTm);
+    float *Wm = reinterpret_cast<float *>(smem + kWm);
+    uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kMisc1);
+    uint64_t *bar_mma = bar_tma + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kMisc1 + 32);
+    int *abort_flag = reinterpret_cast<int *>(smem + kMisc1 + 48);
+    float *grp = reinterpret_cast<float *>(smem + kMisc1 + 256);     // [8][64]
+    float *emv = reinterpret_cast<float *>(smem + kMisc1 + 256 + 2048);   // e^{m_j} / kOpScale [64]
+
+    if (tid == 0) {
+        mbar_init(bar_tma, 1);
+        mbar_init(bar_mma, 1);
+        mbar_fence_init();
+        *abort_flag = 0;
+#pragma unroll
+        for (int i = 0; i < 5; ++i) tma_prefetch_desc(&maps.m[i]);
+    }
+    // identity tile (constant for the whole kernel)
+    for (int idx = tid; idx < kL * 8; idx += kThreads1) {
+        const int r = idx >> 3, ch = idx & 7;
+        uint4 z = make_uint4(0, 0, 0, 0);
+        if ((r >> 3) == ch) {
+            const uint32_t one = 0x3c00u << ((r & 1) * 16);
+            uint32_t *w = &z.x;
+            w[(r & 7) >> 1] = one;
+        }
+        *reinterpret_cast<uint4 *>(smem + kI64 + r * 128 + ((ch ^ (r & 7)) << 4)) = z;
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 128);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t sb = smem_u32(smem);
+    const long long units = (long long)nchains * seg_chunks;
+
+    auto issue_tma = [&](long long unit) {
+        const int chain = (int)(unit / seg_chunks), chunk = chunk0 + (int)(unit % seg_chunks);
+        const int bi = chain / H, h = chain % H;
+        mbar_expect_tx(bar_tma, kRawBytes);
+        const int trow = bi * Tlen + chunk * kL;
+#pragma unroll
+        for (int i = 0; i < 5; ++i) tma_load_2d(raw + i * kPanel, &maps.m[i], h * kN, trow, bar_tma);
+    };
+    long long unit = blockIdx.x;
+    if (tid == 0 && unit < units) issue_tma(unit);
+    uint32_t tma_phase = 0, mma_phase = 0;
+    bool tma_pending = unit < units;   // a tile batch is in flight (thread 0's view is what matters)
+    bool failed = false;
+
+    for (; unit < units; unit += gridDim.x) {
+        const int chain = (int)(unit / seg_chunks), chunk = chunk0 + (int)(unit % seg_chunks);
+        const int valid = min(kL, Tlen - chunk * kL);
+        if (!mbar_wait(bar_tma, tma_phase)) atomicOr(abort_flag, 1);
+        tma_phase ^= 1;
+        tma_pending = false;
+        if (valid < kL) {
+            // partial last chunk: rows past the end become no-op tokens (w = -inf: log-decay -0)
+            for (int idx = tid; idx < (kL - valid) * kN; idx += kThreads1) {
+                const int t = valid + idx / kN, jj = idx % kN;
+#pragma unroll
+                for (int x = 0; x < 5; ++x)
+                    *reinterpret_cast<unsigned short *>(raw + x * kPanel + (t * kN + jj) * 2) =
+                        (x == XW) ? (unsigned short)0xFF80 : (unsigned short)0;
+            }
+            __syncthreads();
+        }
+        // ---------------- phase A: decay prefix sums, scaled fp16 operands
+        const int j2 = lane, tg = warp;            // channel pair (2 j2, 2 j2 + 1), tokens 8 tg .. 8 tg + 7
+        const unsigned char *rp = raw + (tg * 8 * kN + 2 * j2) * 2;
+        auto ld2 = [&](int tensor, int u) {
+            return unpack_bf2(*reinterpret_cast<const uint32_t *>(rp + tensor * kPanel + u * (kN * 2)));
+        };
+        float c0[8], c1[8];
+        {
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float2 w2 = ld2(XW, u);
+                s0 -= __expf(w2.x);
+                s1 -= __expf(w2.y);
+                c0[u] = s0;
+                c1[u] = s1;
+            }
+            *reinterpret_cast<float2 *>(grp + tg * 64 + 2 * j2) = make_float2(s0, s1);
+        }
+        // the previous operator must have left its staging area before AR / A_rb / A_rk are rewritten
+        if (tid == 0) bulk_wait_group_read<0>();
+        __syncthreads();
+        if (*abort_flag) { failed = true; break; }
+        {
+            float base0 = 0.f, base1 = 0.f, tot0 = 0.f, tot1 = 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                const float2 x = *reinterpret_cast<const float2 *>(grp + g * 64 + 2 * j2);
+                tot0 += x.x;
+                tot1 += x.y;
+                if (g < tg) { base0 += x.x; base1 += x.y; }
+            }
+            const float m0 = 0.5f * tot0, m1 = 0.5f * tot1;
+            const float em0 = __expf(m0), em1 = __expf(m1);
+            if (tg == 7) {
+                if (tot0 < -kMaxLogDecay || tot1 < -kMaxLogDecay || !(tot0 <= 0.f) || !(tot1 <= 0.f))
+                    atomicOr(&flags[chain], 1);
+                float *vec = vectors + (size_t)unit * kVecFloats;
+                *reinterpret_cast<float2 *>(vec + 2 * j2) = make_float2(__expf(tot0), __expf(tot1));
+                *reinterpret_cast<float2 *>(vec + 64 + 2 * j2) = make_float2(__expf(tot0 - m0), __expf(tot1 - m1));
+                *reinterpret_cast<float2 *>(emv + 2 * j2) = make_float2(em0 * kInvOpScale, em1 * kInvOpScale);
+            }
+            float ep0 = __expf(base0 - m0) * kOpScale, ep1 = __expf(base1 - m1) * kOpScale;   // e^{c_{t-1} - m} * scale
+            const float rs0 = em0 * kInvOpScale, rs1 = em1 * kInvOpScale;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int t = tg * 8 + u;
+                const float e0 = __expf(base0 + c0[u] - m0) * kOpScale, e1 = __expf(base1 + c1[u] - m1) * kOpScale;
+                // e^{m - c_t} * scale
+                const float i0 = __fdividef(kOpScale * kOpScale, e0), i1 = __fdividef(kOpScale * kOpScale, e1);
+                const float2 a2 = ld2(XA, u), r2 = ld2(XR, u), b2 = ld2(XB, u), k2 = ld2(XK, u);
+                const uint32_t o = off16(t, 2 * j2);
+                *reinterpret_cast<uint32_t *>(smem + kAR + o) = pack_h2(a2.x * ep0, a2.y * ep1);
+                *reinterpret_cast<uint32_t *>(smem + kAR + kPanel + o) = pack_h2(r2.x * e0, r2.y * e1);
+                *reinterpret_cast<uint32_t *>(smem + kBK + o) = pack_h2(b2.x * i0, b2.y * i1);
+                *reinterpret_cast<uint32_t *>(smem + kBK + kPanel + o) = pack_h2(k2.x * i0, k2.y * i1);
+                *reinterpret_cast<uint32_t *>(smem + kRtrue + o) = pack_h2(r2.x * e0 * rs0, r2.y * e1 * rs1);
+                ep0 = e0;
+                ep1 = e1;
+            }
+        }
+        fence_proxy_async();
+        __syncthreads();
+        // ---------------- G = [At;Rt] [Bh;Kh]^T   (128 x 128, contraction over the 64 channels)
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                umma_f16(tmem, dK(sb + kAR, ks), dK(sb + kBK, ks), idesc16(128, 128, false, false), ks > 0);
+            umma_commit(bar_mma);
+        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
+        mma_phase ^= 1;
+        tc_fence_after();
+        // ---------------- G -> A_ab (fp32), A_ak, A_rb, A_rk (fp16), masked to the lower triangle
+        {
+            const bool rt_rows = quarter >= 2;        // Rt rows keep the diagonal
+            const int t = row & 63;
+            const int lim = rt_rows ? t : t - 1;      // keep s <= lim
+            constexpr float sc = kInvOpScale * kInvOpScale;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + hf * 64 + half * 32, v);
+                tmem_ld_wait();
+                if (!rt_rows && hf == 0) {
+                    float *dst = Am + t * kPitchF + half * 32;
+#pragma unroll
+                    for (int e4 = 0; e4 < 8; ++e4) {
+                        float4 o;
+                        float *of = &o.x;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int s = half * 32 + e4 * 4 + e;
+                            of[e] = (s <= lim) ? __uint_as_float(v[e4 * 4 + e]) * sc : 0.f;
+                        }
+                        *reinterpret_cast<float4 *>(dst + e4 * 4) = o;
+                    }
+                } else {
+                    const uint32_t tile = !rt_rows ? (kAR + kPanel) : (hf == 0 ? kArb : kArk);   // A_ak takes Rt's place
+#pragma unroll
+                    for (int e8 = 0; e8 < 4; ++e8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e2 = 0; e2 < 4; ++e2) {
+                            const int s = half * 32 + e8 * 8 + e2 * 2;
+                            const float x0 = (s <= lim) ? __uint_as_float(v[e8 * 8 + e2 * 2]) * sc : 0.f;
+                            const float x1 = (s + 1 <= lim) ? __uint_as_float(v[e8 * 8 + e2 * 2 + 1]) * sc : 0.f;
+                            w[e2] = pack_h2(x0, x1);
+                        }
+                        *reinterpret_cast<uint4 *>(smem + tile + off16(t, half * 32 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
+        if (*abort_flag) { failed = true; break; }
+        // ---------------- T = (I - A_ab)^-1 in fp32: 16 x 16 diagonal blocks by forward substitution,
+        // then [[T00, 0], [T11 A10 T00, T11]] for pairs of 16-blocks and once more for the two 32-blocks.
+        if (tid < 64) {
+            const int b = tid >> 4, cc = tid & 15;
+            const float *Ab = Am + (16 * b) * kPitchF + 16 * b;
+            float x[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                for (int s4 = 0; s4 < (t + 3) / 4; ++s4) {
+                    const float4 a4 = *reinterpret_cast<const float4 *>(Ab + t * kPitchF + 4 * s4);
+                    if (4 * s4 + 0 < t) acc0 = fmaf(a4.x, x[4 * s4 + 0], acc0);
+                    if (4 * s4 + 1 < t) acc1 = fmaf(a4.y, x[4 * s4 + 1], acc1);
+                    if (4 * s4 + 2 < t) acc0 = fmaf(a4.z, x[4 * s4 + 2], acc0);
+                    if (4 * s4 + 3 < t) acc1 = fmaf(a4.w, x[4 * s4 + 3], acc1);
+                }
+                x[t] = (t == cc) ? 1.f : ((t > cc) ? acc0 + acc1 : 0.f);
+                Tm[(16 * b + t) * kPitchF + 16 * b + cc] = x[t];
+            }
+        }
+        __syncthreads();
+        {   // level 1: two pairs of 16-blocks; 512 outputs per product, two per thread
+            const int pr = tid >> 7, t = (tid >> 3) & 15, cb = (tid & 7) * 2;
+            const float *arow = Am + (32 * pr + 16 + t) * kPitchF + 32 * pr;    // A10[t][.]
+            const float *tcol = Tm + (32 * pr) * kPitchF + 32 * pr + cb;        // T00[.][cb..]
+            float w0 = 0.f, w1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                const float a = arow[s];
+                const float2 tt = *reinterpret_cast<const float2 *>(tcol + s * kPitchF);
+                if (s >= cb) w0 = fmaf(a, tt.x, w0);          // T00 is lower triangular
+                if (s >= cb + 1) w1 = fmaf(a, tt.y, w1);
+            }
+            *reinterpret_cast<float2 *>(Wm + (16 * pr + t) * 36 + cb) = make_float2(w0, w1);
+            __syncthreads();
+            const float *trow = Tm + (32 * pr + 16 + t) * kPitchF + 32 * pr + 16;   // T11[t][.]
+            const float *wcol = Wm + (16 * pr) * 36 + cb;
+            float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 16; ++s) {
+                const float a = trow[s];
+                const float2 ww = *reinterpret_cast<const float2 *>(wcol + s * 36);
+                if (s <= t) { z0 = fmaf(a, ww.x, z0); z1 = fmaf(a, ww.y, z1); }
+            }
+            *reinterpret_cast<float2 *>(Tm + (32 * pr + 16 + t) * kPitchF + 32 * pr + cb) = make_float2(z0, z1);
+        }
+        __syncthreads();
+        {   // level 2: the two 32-blocks; 1024 outputs per product, four per thread
+            const int t = tid >> 3, cb = (tid & 7) * 4;
+            const float *arow = Am + (32 + t) * kPitchF;      // A10[t][.]  (columns 0..31)
+            float w[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+            for (int s = 0; s < 32; ++s) {
+                const float a = arow[s];
+                const float4 tt = *reinterpret_cast<const float4 *>(Tm + s * kPitchF + cb);
+                if (s >= cb) w[0] = fmaf(a, tt.x, w[0]);
+                if (s >= cb + 1) w[1] = fmaf(a, tt.y, w[1]);
+                if (s >= cb + 2) w[2] = fmaf(a, tt.z, w[2]);
+                if (s >= cb + 3) w[3] = fmaf(a, tt.w, w[3]);
+            }
+            *reinterpret_cast<float4 *>(Wm + t * 36 + cb) = make_float4(w[0], w[1], w[2], w[3]);
+            __syncthreads();
+            const float *trow = Tm + (32 + t) * kPitchF + 32;   // T11[t][.]
+            float z[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+            for (int s = 0; s < 32; ++s) {
+                const float a = (s <= t) ? trow[s] : 0.f;
+                const float4 ww = *reinterpret_cast<const float4 *>(Wm + s * 36 + cb);
+                z[0] = fmaf(a, ww.x, z[0]);
+                z[1] = fmaf(a, ww.y, z[1]);
+                z[2] = fmaf(a, ww.z, z[2]);
+                z[3] = fmaf(a, ww.w, z[3]);
+            }
+            *reinterpret_cast<float4 *>(Tm + (32 + t) * kPitchF + cb) = make_float4(z[0], z[1], z[2], z[3]);
+        }
+        __syncthreads();
+        {   // T -> fp16 K-major tile [t][u] (zero above the diagonal); 16 elements per thread
+            const int t = tid >> 2, u0 = (tid & 3) * 16;
+            const float *src = Tm + t * kPitchF + u0;
+            uint32_t w[8];
+#pragma unroll
+            for (int e2 = 0; e2 < 8; ++e2) {
+                const int u = u0 + 2 * e2;
+                const float2 x = *reinterpret_cast<const float2 *>(src + 2 * e2);
+                w[e2] = pack_h2(u <= t ? x.x : 0.f, u + 1 <= t ? x.y : 0.f);
+            }
+            __syncthreads();   // every read of the fp32 scratch is done: the tile goes over A_ab
+            *reinterpret_cast<uint4 *>(smem + kT16 + off16(t, u0)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(smem + kT16 + off16(t, u0 + 8)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        fence_proxy_async();
+        __syncthreads();
+        // ---------------- [A~ | A~k]^T = [At | A_ak]^T T^T   (rows c = (j | s), columns t)
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                umma_f16(tmem, dMN(sb + kAR, kPanel, ks), dK(sb + kT16, ks), idesc16(128, 64, true, false), ks > 0);
+            umma_commit(bar_mma);
+        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
+        mma_phase ^= 1;
+        tc_fence_after();
+        {
+            uint32_t v[32];
+            tmem_ld32(tmem + lane_base + hf * 32, v);
+            tmem_ld_wait();
+            const float scale = row < 64 ? emv[row] : 1.f;   // A~ rows: back to the true scale
+#pragma unroll
+            for (int e8 = 0; e8 < 4; ++e8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e2 = 0; e2 < 4; ++e2)
+                    w[e2] = pack_h2(__uint_as_float(v[e8 * 8 + 2 * e2]) * scale, __uint_as_float(v[e8 * 8 + 2 * e2 + 1]) * scale);
+                *reinterpret_cast<uint4 *>(smem + kAf + off16(row, hf * 32 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        __syncthreads();
+        if (*abort_flag) { failed = true; break; }
+        // ---------------- O = [A~|A~k]^T [Bh | A_rb^T]  +  [R|A_rk]^T [0 | I]
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)   // columns j': contraction over t with Bh[t][j'] (MN-major B)
+                umma_f16(tmem, dK(sb + kAf, ks), dMN(sb + kBK, kPanel, ks), idesc16(128, 64, false, true), ks > 0);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)   // columns t': contraction over t with A_rb[t'][t]
+                umma_f16(tmem + 64, dK(sb + kAf, ks), dK(sb + kArb, ks), idesc16(128, 64, false, false), ks > 0);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)   // + R[t'][j] and A_rk[t'][s], through the identity
+                umma_f16(tmem + 64, dMN(sb + kRtrue, kArk - kRtrue, ks), dK(sb + kI64, ks), idesc16(128, 64, true, false), true);
+            umma_commit(bar_mma);
+        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
+        mma_phase ^= 1;
+        tc_fence_after();
+        // the raw-tile region is dead from here on: request the next chunk's tiles
+        const long long next = unit + gridDim.x;
+        if (tid == 0 && next < units && !*abort_flag) issue_tma(next);
+        if (next < units) tma_pending = true;
+        {
+            bool bad = false;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + hf * 64 + half * 32, v);
+                tmem_ld_wait();
+                float add[32];
+                const bool kt_rows = hf == 0 && row >= 64;      // Kt = Kh + A~k^T Bh
+                const float sc = hf == 0 ? kInvOpScale : 1.f;   // Bh and Kh carry the operand scale
+                if (kt_rows) {
+#pragma unroll
+                    for (int e8 = 0; e8 < 4; ++e8) {
+                        const uint4 q = *reinterpret_cast<const uint4 *>(smem + kBK + kPanel + off16(row - 64, half * 32 + e8 * 8));
+                        const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int e2 = 0; e2 < 4; ++e2) {
+                            const float2 f = unpack_h2(qs[e2]);
+                            add[e8 * 8 + 2 * e2] = f.x;
+                            add[e8 * 8 + 2 * e2 + 1] = f.y;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int e8 = 0; e8 < 4; ++e8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e2 = 0; e2 < 4; ++e2) {
+                        float x0 = __uint_as_float(v[e8 * 8 + 2 * e2]), x1 = __uint_as_float(v[e8 * 8 + 2 * e2 + 1]);
+                        if (kt_rows) { x0 += add[e8 * 8 + 2 * e2]; x1 += add[e8 * 8 + 2 * e2 + 1]; }
+                        w[e2] = pack_h2(x0 * sc, x1 * sc);
+                        bad |= h2_nonfinite(w[e2]);
+                    }
+                    // panel hf, row k = this thread's lane, 16-byte chunk of columns n
+                    *reinterpret_cast<uint4 *>(smem + kStage + hf * (2 * kPanel) + off16(row, half * 32 + e8 * 8)) =
+                        make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            if (bad) atomicOr(&flags[chain], 1);
+        }
+        tc_fence_before();
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(operators + (size_t)unit * kOperatorBytes),
+                         "r"(sb + kStage), "r"(kOperatorBytes)
+                         : "memory");
+            bulk_commit_group();
+        }
+    }
+    // ---------------- epilogue
+    __syncthreads();
+    if (*abort_flag) failed = true;
+    if (tid == 0) {
+        bulk_wait_group<0>();
+        if (failed) {
+            if (tma_pending) mbar_wait(bar_tma, tma_phase);   // tiles in flight must land before the CTA leaves
+            atomicExch(status, (int)kDevTimeout);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+// ------------------------------------------------------------------------------------------
+// Kernel 2: the scan.  One CTA per chain.  Warps 0-7 own the 128 TMEM lanes twice over (two
+// column halves): lanes 0-63 are the state rows j' (fp32 state Z[j'][i] = S[i][j'] in registers),
+// lanes 64-127 the output tokens t.  Warp 8 streams operators and V tiles into a ring of stages,
+// warp 9 issues the MMAs.  Per chunk D[(j' | t)][i] = sum_k O[k][(j' | t)] [Z ; V][k][i]: the V half
+// is issued as soon as a stage has landed, only the Z half waits for the previous chunk.
+// ------------------------------------------------------------------------------------------
+constexpr int kComputeWarps = 8;
+constexpr int kThreads2 = (kComputeWarps + 2) * 32;
+constexpr uint32_t kStageBytes = kOperatorBytes + kPanel;   // operator + V tile
+
+template <int NS>
+struct ScanSmem {
+    static constexpr uint32_t kStages = 0;
+    static constexpr uint32_t kZ = NS * kStageBytes;       // fp16 state tile Z[j][i]
+    static constexpr uint32_t kBars = kZ + kPanel;
+    static constexpr uint32_t kBytes = kBars + 512 + 1024;   // + alignment slack
+};
+
+struct ScanMaps {
+    CUtensorMap v;   // [B*T, H*N] bf16, box 64 x 64, 128-byte swizzle
+};
+
+template <int NS>
+__global__ void __launch_bounds__(kThreads2, NS <= 2 ? 2 : 1)
+wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned char *__restrict__ operators,
+                       const float *__restrict__ vectors, const float *state_in, float *state_out,
+                       __nv_bfloat16 *__restrict__ y, const int *__restrict__ flags, int Tlen, int H, int chunk0,
+                       int seg_chunks, int nseg, int check_flags, int *status) {
+    using SM = ScanSmem<NS>;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
+        return;
+    }
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + SM::kBars);   // [NS] stage landed (bytes)
+    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (128 arrivals)
+    uint64_t *bar_empty = bar_vready + NS;     // [NS] the stage's MMAs are done
+    uint64_t *bar_accfull = bar_empty + NS;    // [2] accumulator complete
+    uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (256 arrivals)
+    uint64_t *bar_zready = bar_accfree + 2;    // state tile written (128 arrivals)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_zready + 1);
+    int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
+
+    const int chain = blockIdx.x;
+    const int bi = chain / H, h = chain % H;
+    const int n = nseg;   // chunks this launch covers: chunk0 .. chunk0 + n - 1
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(bar_full + s, 1);
+            mbar_init(bar_vready + s, 128);
+            mbar_init(bar_empty + s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_accfull + a, 1);
+            mbar_init(bar_accfree + a, 256);
+        }
+        mbar_init(bar_zready, 128);
+        mbar_fence_init();
+        *abort_flag = 0;
+        tma_prefetch_desc(&maps.v);
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 128);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t sb = smem_u32(smem);
+    const unsigned char *ops = operators + ((size_t)chain * seg_chunks) * kOperatorBytes;
+    const float *vecs = vectors + ((size_t)chain * seg_chunks) * kVecFloats;
+
+    if (warp == kComputeWarps) {
+        // ---------------- loader: operator (bulk copy) + V tile (TMA) per stage
+        if (lane == 0) {
+            int issued = 0, landed_needed = 0;
+            for (int c = 0; c < n; ++c) {
+                const int s = c % NS;
+                if (c >= NS && !mbar_wait(bar_empty + s, (uint32_t)((c / NS - 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                if (*reinterpret_cast<volatile int *>(abort_flag)) break;
+                mbar_expect_tx(bar_full + s, kStageBytes);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(sb + SM::kStages + s * kStageBytes), "l"(ops + (size_t)c * kOperatorBytes),
+                               "r"(kOperatorBytes), "r"(smem_u32(bar_full + s))
+                             : "memory");
+                tma_load_2d(smem + SM::kStages + s * kStageBytes + kOperatorBytes, &maps.v, h * kN,
+                            bi * Tlen + (chunk0 + c) * kL, bar_full + s);
+                ++issued;
+            }
+            // On an abort the copies already requested must land before the CTA gives up its shared memory.
+            if (*reinterpret_cast<volatile int *>(abort_flag)) {
+                (void)landed_needed;
+                for (int c = max(0, issued - NS); c < issued; ++c) mbar_wait(bar_full + c % NS, (uint32_t)((c / NS) & 1));
+            }
+        }
+    } else if (warp == kComputeWarps + 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t id = idesc16(128, 64, true, true);
+            for (int c = 0; c < n; ++c) {
+                const int s = c % NS, a = c & 1;
+                const uint32_t op = sb + SM::kStages + s * kStageBytes, vt = op + kOperatorBytes;
+                if (!mbar_wait(bar_vready + s, (uint32_t)((c / NS) & 1))) { atomicOr(abort_flag, 1); break; }
+                if (!mbar_wait(bar_accfree + a, (uint32_t)(((c >> 1) & 1) ^ 1))) { atomicOr(abort_flag, 1); break; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // k = 64 + s: rows 64.. of both operator panels against V[s][i]
+                    umma_f16(tmem + a * 64, dMN(op, 2 * kPanel, 4 + ks), dMN(vt, kPanel, ks), id, ks > 0);
+                if (!mbar_wait_spin(bar_zready, (uint32_t)(c & 1))) { atomicOr(abort_flag, 1); break; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // k = j: rows 0..63 against Z[j][i]
+                    umma_f16(tmem + a * 64, dMN(op, 2 * kPanel, ks), dMN(sb + SM::kZ, kPanel, ks), id, true);
+                umma_commit(bar_accfull + a);
+                umma_commit(bar_empty + s);
+            }
+        }
+    } else {
+        const int quarter = warp & 3, hf = warp >> 2;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int i0 = hf * 32;                       // this thread's 32 value channels
+        if (quarter < 2) {
+            // ---------------- state rows j'
+            const int jp = quarter * 32 + lane;
+            float Z[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+                Z[e] = state_in ? state_in[((size_t)chain * kN + i0 + e) * kN + jp] : 0.f;
+            auto put_tile = [&]() {
+#pragma unroll
+                for (int e8 = 0; e8 < 4; ++e8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e2 = 0; e2 < 4; ++e2) w[e2] = pack_h2(Z[e8 * 8 + 2 * e2], Z[e8 * 8 + 2 * e2 + 1]);
+                    *reinterpret_cast<uint4 *>(smem + SM::kZ + off16(jp, i0 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                fence_proxy_async();
+                mbar_arrive(bar_zready);
+            };
+            put_tile();
+            float2 gg = n > 0 ? make_float2(vecs[jp], vecs[64 + jp]) : make_float2(1.f, 0.f);
+            for (int c = 0; c < n; ++c) {
+                const int a = c & 1;
+                float2 gg_next = gg;
+                if (c + 1 < n) gg_next = make_float2(vecs[(size_t)(c + 1) * kVecFloats + jp], vecs[(size_t)(c + 1) * kVecFloats + 64 + jp]);
+                if (!mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                tc_fence_after();
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + a * 64 + i0, v);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(bar_accfree + a);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) Z[e] = fmaf(gg.y, __uint_as_float(v[e]), gg.x * Z[e]);
+                if (c + 1 < n) put_tile();
+                gg = gg_next;
+            }
+            const bool skip = check_flags && flags[chain] != 0;   // a flagged chain is recomputed from state_in
+            if (state_out != nullptr && !skip && !*reinterpret_cast<volatile int *>(abort_flag)) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) state_out[((size_t)chain * kN + i0 + e) * kN + jp] = Z[e];
+            }
+        } else {
+            // ---------------- output tokens t, and the fp16 copy of each V tile
+            const int tq = (quarter - 2) * 32 + lane;     // token within the chunk
+            const int yt = (quarter - 2) * 2 + hf;        // 0..3: which of the four y warps
+            auto convert_v = [&](int c) -> bool {
+                const int s = c % NS;
+                if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+                unsigned char *vt = smem + SM::kStages + s * kStageBytes + kOperatorBytes;
+                // element-wise bf16 -> fp16 in place (the layout does not matter): 64 bytes per thread
+                uint4 *p = reinterpret_cast<uint4 *>(vt + (yt * 32 + lane) * 64);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 x = p[q];
+                    uint32_t *xs = &x.x;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = unpack_bf2(xs[e]);
+                        xs[e] = pack_h2(f.x, f.y);
+                    }
+                    p[q] = x;
+                }
+                fence_proxy_async();
+                mbar_arrive(bar_vready + s);
+                return true;
+            };
+            bool ok = n > 0 ? convert_v(0) : true;
+            if (!ok) atomicOr(abort_flag, 1);
+            for (int c = 0; ok && c < n; ++c) {
+                const int a = c & 1;
+                if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
+                if (!mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                tc_fence_after();
+                uint32_t v[32];
+                tmem_ld32(tmem + lane_base + a * 64 + i0, v);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(bar_accfree + a);
+                const int t = (chunk0 + c) * kL + tq;
+                if (t < Tlen) {
+                    __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + t) * H + h) * kN + i0;
+#pragma unroll
+                    for (int e8 = 0; e8 < 4; ++e8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e2 = 0; e2 < 4; ++e2) {
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[e8 * 8 + 2 * e2]),
+                                                                             __uint_as_float(v[e8 * 8 + 2 * e2 + 1]));
+                            w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + e8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (*abort_flag && tid == 0) atomicExch(status, (int)kDevTimeout);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+constexpr size_t kAlign = 256;
+size_t align_up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+// Operator storage the launcher aims for: beyond this a call is cut into segments of chunks.
+constexpr size_t kOperatorBudget = (size_t)768 << 20;
+
+}  // namespace
+
+// Workspace: one fallback flag per chain, a carried fp32 state per chain (used only when a call is
+// cut into segments), then per (chain, chunk of a segment) the two fp32 vectors and the operator.
+size_t wkv7_split_min_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
+    (void)T;
+    if (N != kN) return 0;
+    const size_t chains = (size_t)(B * H);
+    return align_up(chains * sizeof(int)) + align_up(chains * kN * kN * sizeof(float)) +
+           align_up(chains * kVecFloats * sizeof(float)) + chains * kOperatorBytes;
+}
+
+size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
+    if (N != kN) return 0;
+    const size_t chains = (size_t)(B * H);
+    const size_t nchunks = (size_t)((T + kL - 1) / kL);
+    size_t seg = nchunks;
+    if (chains * seg * kOperatorBytes > kOperatorBudget) seg = kOperatorBudget / (chains * kOperatorBytes);
+    if (seg < 1) seg = 1;
+    return align_up(chains * sizeof(int)) + align_up(chains * kN * kN * sizeof(float)) +
+           align_up(chains * seg * kVecFloats * sizeof(float)) + chains * seg * kOperatorBytes;
+}
+
+bool wkv7_split_supported(const Wkv7Args &p) {
+    auto aligned = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    return p.N == kN && p.bf16 && aligned(p.r) && aligned(p.w) && aligned(p.k) && aligned(p.v) && aligned(p.a) &&
+           aligned(p.b) && aligned(p.y) && p.B * p.T < (int64_t(1) << 31) && p.B * p.H < (int64_t(1) << 30);
+}
+
+// Enqueues the two kernels (once per segment of chunks) and leaves one flag per chain in the first
+// B*H ints of the workspace: 1 for chains that must be recomputed by the caller's next kernel.
+// `check_flags_for_state`: the final state of a flagged chain is not written (it may alias the initial state).
+int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    EncodeTiledFn encode = encode_fn();
+    if (encode == nullptr) return (int)cudaErrorNotSupported;
+    const size_t chains = (size_t)(p.B * p.H);
+    const int nchunks = (int)((p.T + kL - 1) / kL);
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    int *flags = reinterpret_cast<int *>(ws);
+    size_t off = align_up(chains * sizeof(int));
+    float *carry = reinterpret_cast<float *>(ws + off);
+    off += align_up(chains * kN * kN * sizeof(float));
+    if (workspace_bytes < off) return (int)cudaErrorInvalidValue;
+    // segment length from the space that is left
+    const size_t per_chunk = chains * ((size_t)kVecFloats * sizeof(float) + kOperatorBytes);
+    size_t seg = (workspace_bytes - off) / per_chunk;   // (a chunk's vectors are 512 bytes: no padding between them)
+    if (seg < 1) return (int)cudaErrorInvalidValue;
+    if (seg > (size_t)nchunks) seg = (size_t)nchunks;
+    float *vectors = reinterpret_cast<float *>(ws + off);
+    off += align_up(chains * seg * kVecFloats * sizeof(float));
+    unsigned char *operators = ws + off;
+
+    OperatorMaps omaps;
+    ScanMaps smaps;
+    const void *ptrs[5] = {p.r, p.w, p.k, p.a, p.b};
+    const cuuint64_t dims[2] = {(cuuint64_t)(p.H * p.N), (cuuint64_t)(p.B * p.T)};
+    const cuuint64_t strides[1] = {(cuuint64_t)(p.H * p.N * 2)};
+    const cuuint32_t box[2] = {(cuuint32_t)kN, (cuuint32_t)kL};
+    const cuuint32_t estr[2] = {1, 1};
+    for (int i = 0; i < 5; ++i) {
+        CUresult r = encode(&omaps.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptrs[i]), dims, strides,
+                            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    }
+    {
+        CUresult r = encode(&smaps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(p.v), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    }
+    int *status = nullptr;
+    if (int e = device_status_ptr(p.device, &status)) return e;
+    cudaError_t e = cudaMemsetAsync(flags, 0, chains * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+
+    auto k1 = wkv7_chunk_operator_kernel;
+    e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem1);
+    if (e != cudaSuccess) return (int)e;
+    const bool many = (int64_t)chains > (int64_t)p.num_sms;   // more chains than SMs: two scan CTAs per SM
+    auto launch_scan = [&](auto kern, size_t smem_bytes, const float *s_in, float *s_out, int c0, int n,
+                           int check) -> cudaError_t {
+        cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (err != cudaSuccess) return err;
+        kern<<<(unsigned)chains, kThreads2, smem_bytes, stream>>>(
+            smaps, operators, vectors, s_in, s_out, reinterpret_cast<__nv_bfloat16 *>(p.y), flags, (int)p.T, (int)p.H,
+            c0, n, n, check, status);
+        count_launch();
+        return cudaGetLastError();
+    };
+    for (int c0 = 0; c0 < nchunks; c0 += (int)seg) {
+        const int n = (int)((size_t)(nchunks - c0) < seg ? (size_t)(nchunks - c0) : seg);
+        const long long units = (long long)chains * n;
+        const unsigned grid = (unsigned)(units < 2LL * p.num_sms ? units : 2LL * p.num_sms);
+        k1<<<grid, kThreads1, kSmem1, stream>>>(omaps, operators, vectors, flags, (int)p.T, (int)p.H, c0, n, (int)chains,
+                                                status);
+        count_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+        const bool first = c0 == 0, last = c0 + n >= nchunks;
+        const float *s_in = first ? p.s0 : carry;
+        float *s_out = last ? p.s_out : carry;
+        // (the operator of (chain, chunk) sits at index chain * n + chunk - c0 in both kernels)
+        if (many) e = launch_scan(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes, s_in, s_out, c0, n, last ? 1 : 0);
+        else e = launch_scan(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes, s_in, s_out, c0, n, last ? 1 : 0);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+
+}  // namespace rwkv7
