@@ -78,9 +78,6 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t *>(&h);
 }
-__device__ __forceinline__ bool h2_nonfinite(uint32_t u) {
-    return ((u & 0x7c00u) == 0x7c00u) || ((u & 0x7c000000u) == 0x7c000000u);
-}
 __device__ __forceinline__ float2 unpack_h2(uint32_t u) {
     return __half22float2(*reinterpret_cast<const __half2 *>(&u));
 }
@@ -96,12 +93,13 @@ constexpr int kThreads1 = 256;
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kRaw = 0;                       // five bf16 tiles r, w, k, a, b (40 KB); later scratch
 constexpr uint32_t kRawBytes = 5 * kPanel;
-constexpr int kPitchF = 68;                        // floats per row of the fp32 scratch matrices
-constexpr uint32_t kAm = kRaw;                     // fp32 A_ab [64][68]
-constexpr uint32_t kTm = kAm + 64 * kPitchF * 4;   // fp32 T    [64][68]
-constexpr uint32_t kWm = kTm + 64 * kPitchF * 4;   // fp32 join scratch [32][36]
-constexpr uint32_t kT16 = kRaw;                    // fp16 T [t][u] (over A_ab, dead by then)
-constexpr uint32_t kAf = kRaw + 18 * 1024;         // fp16 [A~ e^m | A~k]^T [c][t], 128 rows (over T fp32, dead by then)
+constexpr int kPitchF = 36;                        // floats per row of the fp32 scratch matrices (a row's own 32-block)
+constexpr uint32_t kAm = kRaw;                     // fp32 diagonal 32 x 32 blocks of A_ab [64][36]
+constexpr uint32_t kTm = kAm + 64 * kPitchF * 4;   // fp32 their inverses           [64][36]
+constexpr uint32_t kWm = kTm + 64 * kPitchF * 4;   // fp32 join scratch [32][20]
+constexpr uint32_t kT16 = kRaw + 24 * 1024;        // fp16 T [t][u]
+constexpr uint32_t kW2 = kT16 + kPanel;            // fp16 A10 T00 [s][c], 32 rows
+constexpr uint32_t kAf = kRaw;                     // fp16 [A~ e^m | A~k]^T [c][t], 128 rows (over the fp32 scratch, dead by then)
 constexpr uint32_t kRtrue = kRaw + kRawBytes;      // fp16 r_t e^{c_t} [t][j]
 constexpr uint32_t kAR = kRtrue + kPanel;          // fp16 [At; Rt] (Rt's half later holds A_ak)
 constexpr uint32_t kArb = kAR + 2 * kPanel;        // fp16 A_rb [t][s]
@@ -111,8 +109,8 @@ constexpr uint32_t kBK = kArk + kPanel;            // fp16 [Bh; Kh]
 constexpr uint32_t kI64 = kBK + 2 * kPanel;        // fp16 identity [64][64]
 constexpr uint32_t kMisc1 = kI64 + kPanel;         // barriers, group sums, e^m
 constexpr uint32_t kSmem1 = kMisc1 + 3072 + 1024;  // + alignment slack
-static_assert(kWm + 32 * 36 * 4 <= kRaw + kRawBytes, "inverse scratch exceeds the raw-tile region");
-static_assert(kAf + 2 * kPanel <= kRaw + kRawBytes, "A~ tile exceeds the raw-tile region");
+static_assert(kWm + 32 * 20 * 4 <= kT16, "inverse scratch runs into the fp16 tile of T");
+static_assert(kW2 + kPanel / 2 <= kRaw + kRawBytes && kAf + 2 * kPanel <= kT16, "scratch exceeds the raw-tile region");
 static_assert(kStage + kOperatorBytes == kBK, "operator staging must cover AR, A_rb, A_rk exactly");
 static_assert(2 * (kSmem1 + 1024) <= 232448, "two CTAs per SM");
 
@@ -277,41 +275,62 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
         mma_phase ^= 1;
         tc_fence_after();
-        // ---------------- G -> A_ab (fp32), A_ak, A_rb, A_rk (fp16), masked to the lower triangle
+        // ---------------- G -> A_ab, A_ak, A_rb, A_rk, masked to the lower triangle.  A_ab's two diagonal
+        // 32 x 32 blocks go to the fp32 scratch of the inverse, its lower-left block straight into the
+        // fp16 tile of T (where the second level of the inverse replaces it); the others are fp16 tiles.
         {
             const bool rt_rows = quarter >= 2;        // Rt rows keep the diagonal
             const int t = row & 63;
+            const bool low_rows = t < 32;             // (warp-uniform: one quarter is 32 consecutive rows)
             const int lim = rt_rows ? t : t - 1;      // keep s <= lim
             constexpr float sc = kInvOpScale * kInvOpScale;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + hf * 64 + half * 32, v);
-                tmem_ld_wait();
+                const bool zero_half = low_rows && half == 1;   // columns 32..63 of rows 0..31: above the diagonal
                 if (!rt_rows && hf == 0) {
-                    float *dst = Am + t * kPitchF + half * 32;
+                    if (zero_half) continue;
+                    uint32_t v[32];
+                    tmem_ld32(tmem + lane_base + half * 32, v);
+                    tmem_ld_wait();
+                    if (low_rows == (half == 0)) {   // diagonal block of this row: fp32, strictly lower
+                        float *dst = Am + t * kPitchF;
 #pragma unroll
-                    for (int e4 = 0; e4 < 8; ++e4) {
-                        float4 o;
-                        float *of = &o.x;
+                        for (int e4 = 0; e4 < 8; ++e4) {
+                            float4 o;
+                            float *of = &o.x;
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int s = half * 32 + e4 * 4 + e;
-                            of[e] = (s <= lim) ? __uint_as_float(v[e4 * 4 + e]) * sc : 0.f;
+                            for (int e = 0; e < 4; ++e)
+                                of[e] = (half * 32 + e4 * 4 + e <= lim) ? __uint_as_float(v[e4 * 4 + e]) * sc : 0.f;
+                            *reinterpret_cast<float4 *>(dst + e4 * 4) = o;
                         }
-                        *reinterpret_cast<float4 *>(dst + e4 * 4) = o;
+                    } else {                          // rows 32..63, columns 0..31: A_10 of the second level
+#pragma unroll
+                        for (int e8 = 0; e8 < 4; ++e8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e2 = 0; e2 < 4; ++e2)
+                                w[e2] = pack_h2(__uint_as_float(v[e8 * 8 + e2 * 2]) * sc, __uint_as_float(v[e8 * 8 + e2 * 2 + 1]) * sc);
+                            *reinterpret_cast<uint4 *>(smem + kT16 + off16(t, e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                     }
                 } else {
                     const uint32_t tile = !rt_rows ? (kAR + kPanel) : (hf == 0 ? kArb : kArk);   // A_ak takes Rt's place
+                    uint32_t v[32];
+                    if (!zero_half) {
+                        tmem_ld32(tmem + lane_base + hf * 64 + half * 32, v);
+                        tmem_ld_wait();
+                    }
 #pragma unroll
                     for (int e8 = 0; e8 < 4; ++e8) {
-                        uint32_t w[4];
+                        uint32_t w[4] = {0u, 0u, 0u, 0u};
+                        if (!zero_half) {
 #pragma unroll
-                        for (int e2 = 0; e2 < 4; ++e2) {
-                            const int s = half * 32 + e8 * 8 + e2 * 2;
-                            const float x0 = (s <= lim) ? __uint_as_float(v[e8 * 8 + e2 * 2]) * sc : 0.f;
-                            const float x1 = (s + 1 <= lim) ? __uint_as_float(v[e8 * 8 + e2 * 2 + 1]) * sc : 0.f;
-                            w[e2] = pack_h2(x0, x1);
+                            for (int e2 = 0; e2 < 4; ++e2) {
+                                const int sidx = half * 32 + e8 * 8 + e2 * 2;
+                                const float x0 = (sidx <= lim) ? __uint_as_float(v[e8 * 8 + e2 * 2]) * sc : 0.f;
+                                const float x1 = (sidx + 1 <= lim) ? __uint_as_float(v[e8 * 8 + e2 * 2 + 1]) * sc : 0.f;
+                                w[e2] = pack_h2(x0, x1);
+                            }
                         }
                         *reinterpret_cast<uint4 *>(smem + tile + off16(t, half * 32 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
@@ -319,13 +338,13 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             }
         }
         tc_fence_before();
-        __syncthreads();
-        if (*abort_flag) { failed = true; break; }
-        // ---------------- T = (I - A_ab)^-1 in fp32: 16 x 16 diagonal blocks by forward substitution,
-        // then [[T00, 0], [T11 A10 T00, T11]] for pairs of 16-blocks and once more for the two 32-blocks.
+        // ---------------- T = (I - A_ab)^-1.  The two 32 x 32 diagonal blocks in fp32 on the CUDA cores:
+        // 16 x 16 blocks by forward substitution (the 64 threads that wrote the scratch go on as soon as they
+        // are done, the others are still writing their tiles), then [[T00, 0], [T11 A10 T00, T11]].
         if (tid < 64) {
+            asm volatile("bar.sync 1, 64;" ::: "memory");
             const int b = tid >> 4, cc = tid & 15;
-            const float *Ab = Am + (16 * b) * kPitchF + 16 * b;
+            const float *Ab = Am + (16 * b) * kPitchF + 16 * (b & 1);
             float x[16];
 #pragma unroll
             for (int t = 0; t < 16; ++t) {
@@ -339,79 +358,100 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                     if (4 * s4 + 3 < t) acc1 = fmaf(a4.w, x[4 * s4 + 3], acc1);
                 }
                 x[t] = (t == cc) ? 1.f : ((t > cc) ? acc0 + acc1 : 0.f);
-                Tm[(16 * b + t) * kPitchF + 16 * b + cc] = x[t];
+                Tm[(16 * b + t) * kPitchF + 16 * (b & 1) + cc] = x[t];
             }
         }
         __syncthreads();
-        {   // level 1: two pairs of 16-blocks; 512 outputs per product, two per thread
+        if (*abort_flag) { failed = true; break; }
+        {   // the two pairs of 16-blocks; 512 outputs per product, two per thread
             const int pr = tid >> 7, t = (tid >> 3) & 15, cb = (tid & 7) * 2;
-            const float *arow = Am + (32 * pr + 16 + t) * kPitchF + 32 * pr;    // A10[t][.]
-            const float *tcol = Tm + (32 * pr) * kPitchF + 32 * pr + cb;        // T00[.][cb..]
+            const float *arow = Am + (32 * pr + 16 + t) * kPitchF;       // A10[t][.]  (row-local columns 0..15)
+            const float *tcol = Tm + (32 * pr) * kPitchF + cb;           // T00[.][cb..]
             float w0 = 0.f, w1 = 0.f;
 #pragma unroll
             for (int s = 0; s < 16; ++s) {
                 const float a = arow[s];
                 const float2 tt = *reinterpret_cast<const float2 *>(tcol + s * kPitchF);
-                if (s >= cb) w0 = fmaf(a, tt.x, w0);          // T00 is lower triangular
-                if (s >= cb + 1) w1 = fmaf(a, tt.y, w1);
+                w0 = fmaf(a, tt.x, w0);   // (T00 is complete: zeros above its diagonal were written)
+                w1 = fmaf(a, tt.y, w1);
             }
-            *reinterpret_cast<float2 *>(Wm + (16 * pr + t) * 36 + cb) = make_float2(w0, w1);
+            *reinterpret_cast<float2 *>(Wm + (16 * pr + t) * 20 + cb) = make_float2(w0, w1);
             __syncthreads();
-            const float *trow = Tm + (32 * pr + 16 + t) * kPitchF + 32 * pr + 16;   // T11[t][.]
-            const float *wcol = Wm + (16 * pr) * 36 + cb;
+            const float *trow = Tm + (32 * pr + 16 + t) * kPitchF + 16;   // T11[t][.]
+            const float *wcol = Wm + (16 * pr) * 20 + cb;
             float z0 = 0.f, z1 = 0.f;
 #pragma unroll
             for (int s = 0; s < 16; ++s) {
                 const float a = trow[s];
-                const float2 ww = *reinterpret_cast<const float2 *>(wcol + s * 36);
-                if (s <= t) { z0 = fmaf(a, ww.x, z0); z1 = fmaf(a, ww.y, z1); }
+                const float2 ww = *reinterpret_cast<const float2 *>(wcol + s * 20);
+                z0 = fmaf(a, ww.x, z0);
+                z1 = fmaf(a, ww.y, z1);
             }
-            *reinterpret_cast<float2 *>(Tm + (32 * pr + 16 + t) * kPitchF + 32 * pr + cb) = make_float2(z0, z1);
+            *reinterpret_cast<float2 *>(Tm + (32 * pr + 16 + t) * kPitchF + cb) = make_float2(z0, z1);
         }
         __syncthreads();
-        {   // level 2: the two 32-blocks; 1024 outputs per product, four per thread
-            const int t = tid >> 3, cb = (tid & 7) * 4;
-            const float *arow = Am + (32 + t) * kPitchF;      // A10[t][.]  (columns 0..31)
-            float w[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-            for (int s = 0; s < 32; ++s) {
-                const float a = arow[s];
-                const float4 tt = *reinterpret_cast<const float4 *>(Tm + s * kPitchF + cb);
-                if (s >= cb) w[0] = fmaf(a, tt.x, w[0]);
-                if (s >= cb + 1) w[1] = fmaf(a, tt.y, w[1]);
-                if (s >= cb + 2) w[2] = fmaf(a, tt.z, w[2]);
-                if (s >= cb + 3) w[3] = fmaf(a, tt.w, w[3]);
-            }
-            *reinterpret_cast<float4 *>(Wm + t * 36 + cb) = make_float4(w[0], w[1], w[2], w[3]);
-            __syncthreads();
-            const float *trow = Tm + (32 + t) * kPitchF + 32;   // T11[t][.]
-            float z[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 8
-            for (int s = 0; s < 32; ++s) {
-                const float a = (s <= t) ? trow[s] : 0.f;
-                const float4 ww = *reinterpret_cast<const float4 *>(Wm + s * 36 + cb);
-                z[0] = fmaf(a, ww.x, z[0]);
-                z[1] = fmaf(a, ww.y, z[1]);
-                z[2] = fmaf(a, ww.z, z[2]);
-                z[3] = fmaf(a, ww.w, z[3]);
-            }
-            *reinterpret_cast<float4 *>(Tm + (32 + t) * kPitchF + cb) = make_float4(z[0], z[1], z[2], z[3]);
+        {   // diagonal 32-blocks -> fp16 tile T[t][u] (zero above the diagonal), and zeros in the block above them
+            const int t = tid >> 2, c0 = (tid & 3) * 8, tl = t & 31;
+            const float *src = Tm + t * kPitchF + c0;
+            const float4 x0 = *reinterpret_cast<const float4 *>(src), x1 = *reinterpret_cast<const float4 *>(src + 4);
+            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            uint32_t w[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2)
+                w[e2] = pack_h2(c0 + 2 * e2 <= tl ? xs[2 * e2] : 0.f, c0 + 2 * e2 + 1 <= tl ? xs[2 * e2 + 1] : 0.f);
+            *reinterpret_cast<uint4 *>(smem + kT16 + off16(t, 32 * (t >> 5) + c0)) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (tid < 128)   // rows 0..31, columns 32..63
+                *reinterpret_cast<uint4 *>(smem + kT16 + off16(tid >> 2, 32 + (tid & 3) * 8)) = make_uint4(0, 0, 0, 0);
         }
+        fence_proxy_async();
         __syncthreads();
-        {   // T -> fp16 K-major tile [t][u] (zero above the diagonal); 16 elements per thread
-            const int t = tid >> 2, u0 = (tid & 3) * 16;
-            const float *src = Tm + t * kPitchF + u0;
+        // second level on the tensor core: T10 = T11 (A10 T00), fp16 operands, two dependent products
+        // (N = 64: the upper 32 columns of both results are never read)
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)   // rows 32.. of the tile (A10) against T00[u][c] (rows u of the same tile, MN-major)
+                umma_f16(tmem, dK(sb + kT16 + 32 * 128, ks), dMN(sb + kT16, kPanel, ks), idesc16(128, 64, false, true), ks > 0);
+            umma_commit(bar_mma);
+        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
+        mma_phase ^= 1;
+        tc_fence_after();
+        if (quarter == 0) {   // lanes 0..31 hold the 32 rows; 16 columns per warp
+            uint32_t v[16];
+            tmem_ld16(tmem + hf * 16, v);
+            tmem_ld_wait();
             uint32_t w[8];
 #pragma unroll
-            for (int e2 = 0; e2 < 8; ++e2) {
-                const int u = u0 + 2 * e2;
-                const float2 x = *reinterpret_cast<const float2 *>(src + 2 * e2);
-                w[e2] = pack_h2(u <= t ? x.x : 0.f, u + 1 <= t ? x.y : 0.f);
-            }
-            __syncthreads();   // every read of the fp32 scratch is done: the tile goes over A_ab
-            *reinterpret_cast<uint4 *>(smem + kT16 + off16(t, u0)) = make_uint4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<uint4 *>(smem + kT16 + off16(t, u0 + 8)) = make_uint4(w[4], w[5], w[6], w[7]);
+            for (int e2 = 0; e2 < 8; ++e2) w[e2] = pack_h2(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1]));
+            *reinterpret_cast<uint4 *>(smem + kW2 + off16(lane, hf * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(smem + kW2 + off16(lane, hf * 16 + 8)) = make_uint4(w[4], w[5], w[6], w[7]);
         }
+        tc_fence_before();
+        fence_proxy_async();
+        __syncthreads();
+        if (*abort_flag) { failed = true; break; }
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)   // T11 (rows 32.., columns 32..63) against W[s][c] (MN-major)
+                umma_f16(tmem, dK(sb + kT16 + 32 * 128, 2 + ks), dMN(sb + kW2, kPanel, ks), idesc16(128, 64, false, true), ks > 0);
+            umma_commit(bar_mma);
+        }
+        if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
+        mma_phase ^= 1;
+        tc_fence_after();
+        if (quarter == 0) {
+            uint32_t v[16];
+            tmem_ld16(tmem + hf * 16, v);
+            tmem_ld_wait();
+            uint32_t w[8];
+#pragma unroll
+            for (int e2 = 0; e2 < 8; ++e2) w[e2] = pack_h2(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1]));
+            *reinterpret_cast<uint4 *>(smem + kT16 + off16(32 + lane, hf * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(smem + kT16 + off16(32 + lane, hf * 16 + 8)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        tc_fence_before();
         fence_proxy_async();
         __syncthreads();
         // ---------------- [A~ | A~k]^T = [At | A_ak]^T T^T   (rows c = (j | s), columns t)
@@ -465,7 +505,6 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         if (tid == 0 && next < units && !*abort_flag) issue_tma(next);
         if (next < units) tma_pending = true;
         {
-            bool bad = false;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t v[32];
@@ -495,14 +534,12 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                         float x0 = __uint_as_float(v[e8 * 8 + 2 * e2]), x1 = __uint_as_float(v[e8 * 8 + 2 * e2 + 1]);
                         if (kt_rows) { x0 += add[e8 * 8 + 2 * e2]; x1 += add[e8 * 8 + 2 * e2 + 1]; }
                         w[e2] = pack_h2(x0 * sc, x1 * sc);
-                        bad |= h2_nonfinite(w[e2]);
                     }
                     // panel hf, row k = this thread's lane, 16-byte chunk of columns n
                     *reinterpret_cast<uint4 *>(smem + kStage + hf * (2 * kPanel) + off16(row, half * 32 + e8 * 8)) =
                         make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
-            if (bad) atomicOr(&flags[chain], 1);
         }
         tc_fence_before();
         fence_proxy_async();
@@ -556,7 +593,7 @@ template <int NS>
 __global__ void __launch_bounds__(kThreads2, NS <= 2 ? 2 : 1)
 wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned char *__restrict__ operators,
                        const float *__restrict__ vectors, const float *state_in, float *state_out,
-                       __nv_bfloat16 *__restrict__ y, const int *__restrict__ flags, int Tlen, int H, int chunk0,
+                       __nv_bfloat16 *__restrict__ y, int *flags, int Tlen, int H, int chunk0,
                        int seg_chunks, int nseg, int check_flags, int *status) {
     using SM = ScanSmem<NS>;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -573,6 +610,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     uint64_t *bar_zready = bar_accfree + 2;    // state tile written (128 arrivals)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_zready + 1);
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
+    int *chain_bad = abort_flag + 1;
 
     const int chain = blockIdx.x;
     const int bi = chain / H, h = chain % H;
@@ -591,6 +629,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         mbar_init(bar_zready, 128);
         mbar_fence_init();
         *abort_flag = 0;
+        *chain_bad = 0;
         tma_prefetch_desc(&maps.v);
     }
     if (warp == 0) tmem_alloc(tmem_slot, 128);
@@ -687,7 +726,13 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (c + 1 < n) put_tile();
                 gg = gg_next;
             }
-            const bool skip = check_flags && flags[chain] != 0;   // a flagged chain is recomputed from state_in
+            // A non-finite operator (fp16 overflow upstream) shows in the state for good: flag the chain.
+            bool bad = false;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) bad |= !(fabsf(Z[e]) <= 3.0e38f);
+            if (bad) atomicOr(chain_bad, 1);
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight compute warps: every flag of this chain is in
+            const bool skip = *chain_bad != 0 || (check_flags && flags[chain] != 0);   // flagged chains are recomputed from state_in
             if (state_out != nullptr && !skip && !*reinterpret_cast<volatile int *>(abort_flag)) {
 #pragma unroll
                 for (int e = 0; e < 32; ++e) state_out[((size_t)chain * kN + i0 + e) * kN + jp] = Z[e];
@@ -717,6 +762,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 mbar_arrive(bar_vready + s);
                 return true;
             };
+            bool ybad = false;   // a non-finite output: the chain is flagged for recomputation
             bool ok = n > 0 ? convert_v(0) : true;
             if (!ok) atomicOr(abort_flag, 1);
             for (int c = 0; ok && c < n; ++c) {
@@ -740,15 +786,21 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                             const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[e8 * 8 + 2 * e2]),
                                                                              __uint_as_float(v[e8 * 8 + 2 * e2 + 1]));
                             w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
+                            ybad |= ((w[e2] & 0x7f80u) == 0x7f80u) || ((w[e2] & 0x7f800000u) == 0x7f800000u);
                         }
                         *reinterpret_cast<uint4 *>(dst + e8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
+            if (ybad) atomicOr(chain_bad, 1);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
         }
     }
     __syncthreads();
-    if (*abort_flag && tid == 0) atomicExch(status, (int)kDevTimeout);
+    if (tid == 0) {
+        if (*abort_flag) atomicExch(status, (int)kDevTimeout);
+        if (*chain_bad) atomicOr(&flags[chain], 1);
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 128);
