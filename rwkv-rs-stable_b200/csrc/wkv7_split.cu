@@ -99,9 +99,9 @@ constexpr uint32_t kTm = kAm + 64 * kPitchF * 4;   // fp32 their inverses       
 constexpr uint32_t kWm = kTm + 64 * kPitchF * 4;   // fp32 join scratch [32][20]
 constexpr uint32_t kT16 = kRaw + 24 * 1024;        // fp16 T [t][u]
 constexpr uint32_t kW2 = kT16 + kPanel;            // fp16 A10 T00 [s][c], 32 rows
-constexpr uint32_t kAf = kRaw;                     // fp16 [A~ e^m | A~k]^T [c][t], 128 rows (over the fp32 scratch, dead by then)
 constexpr uint32_t kRtrue = kRaw + kRawBytes;      // fp16 r_t e^{c_t} [t][j]
 constexpr uint32_t kAR = kRtrue + kPanel;          // fp16 [At; Rt] (Rt's half later holds A_ak)
+constexpr uint32_t kAf = kAR;                      // fp16 [A~ e^m | A~k]^T [c][t], 128 rows: replaces [At | A_ak] once it has been read
 constexpr uint32_t kArb = kAR + 2 * kPanel;        // fp16 A_rb [t][s]
 constexpr uint32_t kArk = kArb + kPanel;           // fp16 A_rk [t][s]
 constexpr uint32_t kStage = kAR;                   // the finished operator (32 KB) over AR, A_rb, A_rk
@@ -110,7 +110,7 @@ constexpr uint32_t kI64 = kBK + 2 * kPanel;        // fp16 identity [64][64]
 constexpr uint32_t kMisc1 = kI64 + kPanel;         // barriers, group sums, e^m
 constexpr uint32_t kSmem1 = kMisc1 + 3072 + 1024;  // + alignment slack
 static_assert(kWm + 32 * 20 * 4 <= kT16, "inverse scratch runs into the fp16 tile of T");
-static_assert(kW2 + kPanel / 2 <= kRaw + kRawBytes && kAf + 2 * kPanel <= kT16, "scratch exceeds the raw-tile region");
+static_assert(kW2 + kPanel / 2 <= kRaw + kRawBytes, "scratch exceeds the raw-tile region");
 static_assert(kStage + kOperatorBytes == kBK, "operator staging must cover AR, A_rb, A_rk exactly");
 static_assert(2 * (kSmem1 + 1024) <= 232448, "two CTAs per SM");
 
@@ -465,6 +465,10 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
         mma_phase ^= 1;
         tc_fence_after();
+        // T has been read: the raw-tile region (scratch of the inverse, T, W) is dead, request the next chunk's tiles
+        const long long next = unit + gridDim.x;
+        if (tid == 0 && next < units && !*abort_flag) issue_tma(next);
+        if (next < units) tma_pending = true;
         {
             uint32_t v[32];
             tmem_ld32(tmem + lane_base + hf * 32, v);
@@ -500,10 +504,6 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
         mma_phase ^= 1;
         tc_fence_after();
-        // the raw-tile region is dead from here on: request the next chunk's tiles
-        const long long next = unit + gridDim.x;
-        if (tid == 0 && next < units && !*abort_flag) issue_tma(next);
-        if (next < units) tma_pending = true;
         {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
@@ -581,12 +581,14 @@ template <int NS>
 struct ScanSmem {
     static constexpr uint32_t kStages = 0;
     static constexpr uint32_t kZ = NS * kStageBytes;       // fp16 state tile Z[j][i]
-    static constexpr uint32_t kBars = kZ + kPanel;
+    static constexpr uint32_t kY = kZ + kPanel;            // two bf16 output tiles [t][i] (128-byte swizzle) on their way out
+    static constexpr uint32_t kBars = kY + 2 * kPanel;
     static constexpr uint32_t kBytes = kBars + 512 + 1024;   // + alignment slack
 };
 
 struct ScanMaps {
     CUtensorMap v;   // [B*T, H*N] bf16, box 64 x 64, 128-byte swizzle
+    CUtensorMap y;   // the output, same view and box
 };
 
 template <int NS>
@@ -603,7 +605,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + SM::kBars);   // [NS] stage landed (bytes)
-    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (128 arrivals)
+    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (256 arrivals)
     uint64_t *bar_empty = bar_vready + NS;     // [NS] the stage's MMAs are done
     uint64_t *bar_accfull = bar_empty + NS;    // [2] accumulator complete
     uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (256 arrivals)
@@ -619,7 +621,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(bar_full + s, 1);
-            mbar_init(bar_vready + s, 128);
+            mbar_init(bar_vready + s, 256);
             mbar_init(bar_empty + s, 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -631,6 +633,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         *abort_flag = 0;
         *chain_bad = 0;
         tma_prefetch_desc(&maps.v);
+        tma_prefetch_desc(&maps.y);
     }
     if (warp == 0) tmem_alloc(tmem_slot, 128);
     tc_fence_before();
@@ -690,6 +693,28 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         const int quarter = warp & 3, hf = warp >> 2;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int i0 = hf * 32;                       // this thread's 32 value channels
+        // The V tile arrives as bf16 and the tensor core wants both operands of a product in one format:
+        // the 256 compute threads turn it into fp16 in place (element by element, the layout is untouched),
+        // 32 bytes each, one chunk ahead of the product that reads it.
+        auto convert_v = [&](int c) -> bool {
+            const int s = c % NS;
+            if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+            uint4 *p = reinterpret_cast<uint4 *>(smem + SM::kStages + s * kStageBytes + kOperatorBytes + tid * 32);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint4 x = p[q];
+                uint32_t *xs = &x.x;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf2(xs[e]);
+                    xs[e] = pack_h2(f.x, f.y);
+                }
+                p[q] = x;
+            }
+            fence_proxy_async();
+            mbar_arrive(bar_vready + s);
+            return true;
+        };
         if (quarter < 2) {
             // ---------------- state rows j'
             const int jp = quarter * 32 + lane;
@@ -710,8 +735,11 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             };
             put_tile();
             float2 gg = n > 0 ? make_float2(vecs[jp], vecs[64 + jp]) : make_float2(1.f, 0.f);
+            if (n > 0 && !convert_v(0)) atomicOr(abort_flag, 1);
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
+                // (the tensor core is busy with this chunk's state product: time for the next V tile)
+                if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
                 float2 gg_next = gg;
                 if (c + 1 < n) gg_next = make_float2(vecs[(size_t)(c + 1) * kVecFloats + jp], vecs[(size_t)(c + 1) * kVecFloats + 64 + jp]);
                 if (!mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
@@ -738,60 +766,56 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 for (int e = 0; e < 32; ++e) state_out[((size_t)chain * kN + i0 + e) * kN + jp] = Z[e];
             }
         } else {
-            // ---------------- output tokens t, and the fp16 copy of each V tile
+            // ---------------- output tokens t.  A chunk's y tile is staged in shared memory (one of two
+            // buffers, 128-byte swizzle) and leaves by one bulk tensor store; a partial last chunk is stored
+            // by the threads themselves.
             const int tq = (quarter - 2) * 32 + lane;     // token within the chunk
-            const int yt = (quarter - 2) * 2 + hf;        // 0..3: which of the four y warps
-            auto convert_v = [&](int c) -> bool {
-                const int s = c % NS;
-                if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
-                unsigned char *vt = smem + SM::kStages + s * kStageBytes + kOperatorBytes;
-                // element-wise bf16 -> fp16 in place (the layout does not matter): 64 bytes per thread
-                uint4 *p = reinterpret_cast<uint4 *>(vt + (yt * 32 + lane) * 64);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    uint4 x = p[q];
-                    uint32_t *xs = &x.x;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 f = unpack_bf2(xs[e]);
-                        xs[e] = pack_h2(f.x, f.y);
-                    }
-                    p[q] = x;
-                }
-                fence_proxy_async();
-                mbar_arrive(bar_vready + s);
-                return true;
-            };
+            const bool elected = warp == 2 && lane == 0;
             bool ybad = false;   // a non-finite output: the chain is flagged for recomputation
-            bool ok = n > 0 ? convert_v(0) : true;
-            if (!ok) atomicOr(abort_flag, 1);
-            for (int c = 0; ok && c < n; ++c) {
+            // After an expired wait this thread stops waiting but still walks the loop, so that the four
+            // warps keep meeting at the named barrier below (the call then reports a time-out).
+            bool dead = n > 0 && !convert_v(0);
+            for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
-                if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
-                if (!mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                if (!dead && c + 1 < n && !convert_v(c + 1)) dead = true;
+                if (!dead && !mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) dead = true;
                 tc_fence_after();
                 uint32_t v[32];
                 tmem_ld32(tmem + lane_base + a * 64 + i0, v);
                 tmem_ld_wait();
                 tc_fence_before();
                 mbar_arrive(bar_accfree + a);
-                const int t = (chunk0 + c) * kL + tq;
-                if (t < Tlen) {
-                    __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + t) * H + h) * kN + i0;
+                uint32_t w[16];
 #pragma unroll
-                    for (int e8 = 0; e8 < 4; ++e8) {
-                        uint32_t w[4];
+                for (int e2 = 0; e2 < 16; ++e2) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1]));
+                    w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
+                    ybad |= ((w[e2] & 0x7f80u) == 0x7f80u) || ((w[e2] & 0x7f800000u) == 0x7f800000u);
+                }
+                const int t0 = (chunk0 + c) * kL;
+                if (t0 + kL <= Tlen) {
+                    unsigned char *stage = smem + SM::kY + a * kPanel;
+                    // the store that last read this buffer (two chunks ago) must be done with it
+                    if (elected) bulk_wait_group_read<1>();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll
-                        for (int e2 = 0; e2 < 4; ++e2) {
-                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[e8 * 8 + 2 * e2]),
-                                                                             __uint_as_float(v[e8 * 8 + 2 * e2 + 1]));
-                            w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
-                            ybad |= ((w[e2] & 0x7f80u) == 0x7f80u) || ((w[e2] & 0x7f800000u) == 0x7f800000u);
-                        }
-                        *reinterpret_cast<uint4 *>(dst + e8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int e8 = 0; e8 < 4; ++e8)
+                        *reinterpret_cast<uint4 *>(stage + off16(tq, i0 + e8 * 8)) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
+                    fence_proxy_async();
+                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                    if (elected) {
+                        tma_store_2d(&maps.y, h * kN, bi * Tlen + t0, stage);
+                        bulk_commit_group();
                     }
+                } else if (t0 + tq < Tlen) {
+                    __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + t0 + tq) * H + h) * kN + i0;
+#pragma unroll
+                    for (int e8 = 0; e8 < 4; ++e8)
+                        *reinterpret_cast<uint4 *>(dst + e8 * 8) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
                 }
             }
+            if (elected) bulk_wait_group<0>();   // the stores read this CTA's shared memory
+            if (dead) atomicOr(abort_flag, 1);
             if (ybad) atomicOr(chain_bad, 1);
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
@@ -896,6 +920,12 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     }
     {
         CUresult r = encode(&smaps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(p.v), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    }
+    {
+        CUresult r = encode(&smaps.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.y, dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
