@@ -62,6 +62,9 @@ int num_sms(int device, int *out) {
 
 bool float_dtype_supported(int32_t dt) { return dt == RWKV7_F32 || dt == RWKV7_BF16; }
 
+// Shortest sequence the automatic choice gives to the two-kernel prefill.
+constexpr int64_t kSplitMinTokens = 512;
+
 #define RWKV7_TRY(expr)                 \
     do {                                \
         if (int st_ = (expr)) return st_; \
@@ -146,18 +149,22 @@ int wkv7_dispatch(Wkv7Args &p, void *workspace, size_t workspace_bytes, rwkv7_st
 
     const int path = g_wkv7_path.load();
     bool chunked = false;
-    if (path == RWKV7_WKV7_SPLIT) {
+    // The two-kernel prefill first, where it applies and the workspace holds at least one segment of
+    // operators; chains it leaves flagged (decay beyond what fp16 operands resolve, non-finite values)
+    // go to the tf32 chunked kernel, and from there to the sequential scan.
+    const bool split_fits = wkv7_split_supported(p) && workspace != nullptr &&
+                            workspace_bytes >= wkv7_split_min_workspace_bytes(p.B, p.T, p.H, p.N);
+    if (path == RWKV7_WKV7_SPLIT && !split_fits) {
         if (!wkv7_split_supported(p))
             return fail(RWKV7_ERR_UNSUPPORTED,
                         "Unsupported: the two-kernel WKV7 prefill needs N == 64 and BF16 tensors (got N=%lld)", (long long)p.N);
-        const size_t need = wkv7_split_min_workspace_bytes(p.B, p.T, p.H, p.N);
-        if (workspace == nullptr || workspace_bytes < need)
-            return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL,
-                        "WorkspaceTooSmall: wkv7 needs %zu workspace bytes, got %zu", need,
-                        workspace == nullptr ? (size_t)0 : workspace_bytes);
+        return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: wkv7 needs %zu workspace bytes, got %zu",
+                    wkv7_split_min_workspace_bytes(p.B, p.T, p.H, p.N), workspace == nullptr ? (size_t)0 : workspace_bytes);
+    }
+    if (path == RWKV7_WKV7_SPLIT || (path == RWKV7_WKV7_AUTO && split_fits && p.T >= kSplitMinTokens)) {
         if (int e = launch_wkv7_split(p, workspace, workspace_bytes, (cudaStream_t)stream))
             return cuda_fail("wkv7 split launch", e);
-        if (int e = launch_wkv7_sequential_flagged(p, static_cast<const int *>(workspace), (cudaStream_t)stream))
+        if (int e = launch_wkv7_chunked_flagged(p, workspace, (cudaStream_t)stream))
             return cuda_fail("wkv7 flagged-chain launch", e);
         return RWKV7_OK;
     }
@@ -317,7 +324,8 @@ int rwkv7_selftest_bounded_wait(int device, int64_t max_polls, rwkv7_stream stre
 size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype) {
     const int path = g_wkv7_path.load();
     if (path == RWKV7_WKV7_SEQUENTIAL) return 0;
-    if (path == RWKV7_WKV7_SPLIT && dtype == RWKV7_BF16) return wkv7_split_workspace_bytes(B, T, H, N);
+    if ((path == RWKV7_WKV7_SPLIT || (path == RWKV7_WKV7_AUTO && T >= kSplitMinTokens)) && dtype == RWKV7_BF16 && N == 64)
+        return wkv7_split_workspace_bytes(B, T, H, N);
     return wkv7_chunked_workspace_bytes(B, T, H, N);
 }
 

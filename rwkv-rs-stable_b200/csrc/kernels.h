@@ -81,6 +81,9 @@ size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 size_t wkv7_split_min_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 bool wkv7_split_supported(const Wkv7Args &p);
 int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// The flagged chains only, by the tf32 chunked kernel (one CTA per chain), then by the sequential scan
+// for those that are still flagged afterwards.
+int launch_wkv7_chunked_flagged(const Wkv7Args &p, void *workspace, cudaStream_t stream);
 // Sequential recomputation of the chains whose flag is set (exits at once for the others).
 int launch_wkv7_sequential_flagged(const Wkv7Args &p, const int *flags, cudaStream_t stream);
 

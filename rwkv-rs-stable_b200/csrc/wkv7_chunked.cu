@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                     __nv_bfloat16 *__restrict__ y, float *s_out, int *__restrict__ flags,
                     int Tlen, int H, int *status, float *__restrict__ snapshots,
-                    __nv_bfloat16 *__restrict__ state_repl, int chain0) {
+                    __nv_bfloat16 *__restrict__ state_repl, int chain0, int only_flagged) {
     // Every pointer is derived from the array itself so that the accesses stay in
     // the shared address space; the 1024-byte alignment the swizzled tiles need is
     // what the runtime provides and is verified before anything else happens.
@@ -223,6 +223,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     if (smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
         return;
+    }
+    if constexpr (K == 1 && !SAVE) {
+        // Second in line after the two-kernel prefill: only the chains that one left flagged are computed.
+        if (only_flagged && flags[chain0 + blockIdx.x] == 0) return;
     }
     unsigned char *raw = smem + kOffRaw, *tAR = smem + kOffAR, *tBK = smem + kOffBK, *tZT = smem + kOffZT,
                   *tS = smem + kOffS, *tVT = smem + kOffVT, *tAKRK = smem + kOffAKRK, *tXU = smem + kOffXU;
@@ -1053,7 +1057,7 @@ int launch_wkv7_sequential_flagged_saved(const Wkv7Args &p, const int *flags, fl
                                          void *state_replacement, int chunk_len, cudaStream_t stream);
 
 static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapshots, void *state_replacement,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, bool only_flagged = false) {
     EncodeTiledFn encode = encode_fn();
     if (encode == nullptr) return (int)cudaErrorNotSupported;
     TmaMaps maps;
@@ -1107,7 +1111,7 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
     // of the SMs idle, its chains form a second launch with a cluster per chain, which ends sooner.
     int cluster = 1;
     int64_t head = 0;
-    if (!save) {
+    if (!save && !only_flagged) {
         const int forced = wkv7_cluster_override();
         if (forced > 0) cluster = forced;
         else {
@@ -1140,7 +1144,8 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
         cfg.numAttrs = k > 1 ? 1 : 0;
         err = cudaLaunchKernelEx(&cfg, kern, maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags,
                                  (int)p.T, (int)p.H, status, snapshots,
-                                 reinterpret_cast<__nv_bfloat16 *>(state_replacement), (int)first);
+                                 reinterpret_cast<__nv_bfloat16 *>(state_replacement), (int)first,
+                                 only_flagged ? 1 : 0);
         if (err == cudaSuccess) count_launch();
         return err;
     };
@@ -1168,6 +1173,12 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
 int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
     (void)workspace_bytes;
     return launch_chunked_impl(p, workspace, nullptr, nullptr, stream);
+}
+
+// The chains whose flag (first B*H ints of the workspace) is set, by the one-CTA kernel; chains it cannot
+// resolve either stay flagged and go through the sequential scan.
+int launch_wkv7_chunked_flagged(const Wkv7Args &p, void *workspace, cudaStream_t stream) {
+    return launch_chunked_impl(p, workspace, nullptr, nullptr, stream, true);
 }
 
 // Training forward on the tensor cores: chunk_len 16, T a multiple of 16.
