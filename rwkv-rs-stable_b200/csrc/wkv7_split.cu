@@ -52,8 +52,13 @@ using namespace sm100;
 
 constexpr int kN = 64;
 constexpr int kL = 64;
-constexpr float kMaxLogDecay = 15.f;     // |c_L| per chunk and channel that fp16 operands resolve
-constexpr float kOpScale = 8.f;          // decay-scaled operands are stored times 8: centres fp16's range
+// |c_L| per chunk and channel up to which fp16 operands keep their precision (the small factor
+// e^{-|c_L|/2} times a typical vector entry stays a normal fp16 number).  Whether the large factor
+// e^{+|c_L|/2} overflows depends on the data (keys and receptances of magnitude 5 overflow from about
+// |c_L| = 17); overflow is not predicted but detected: it turns the chunk's operator non-finite, the
+// scan sees that in its outputs and flags the chain.
+constexpr float kMaxLogDecay = 18.f;
+constexpr float kOpScale = 4.f;          // decay-scaled operands are stored times 4: centres fp16's range
 constexpr float kInvOpScale = 1.f / kOpScale;
 constexpr uint32_t kPanel = 8192;        // one [64][64] 16-bit tile
 constexpr uint32_t kOperatorBytes = 4 * kPanel;   // O: 128 x 128 fp16
