@@ -218,6 +218,48 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *initial_state,
                                        rwkv7_tensor *output, rwkv7_tensor *next_state,
                                        rwkv7_stream stream);
 
+/* ---------------------------------------------- wkv7 from host buffers -- */
+/*
+ * Statepass for callers whose six sequence tensors, y and the states live in
+ * PINNED HOST memory (an inference server that receives activations from another
+ * process; the end-to-end leg of the benchmark).  No counterpart in the reference,
+ * whose tensors are device-resident; the arithmetic is rwkv7_fused_wkv7_statepass.
+ *
+ * The batch is cut into `slices` equal parts.  Slice i uses streams[i % n_streams]
+ * for its host-to-device copies (one cudaMemcpyAsync per tensor), its kernels and its
+ * device-to-host copies, so the copies of one slice overlap the kernels and the
+ * copy-back of the slices before it.  (b,h) chains are independent, so slicing the
+ * batch changes no arithmetic.
+ *
+ * Host tensors are described like device tensors, with `device` = RWKV7_HOST and a
+ * pointer that the CUDA device can copy from asynchronously (page-locked memory).
+ * host_initial_state may be NULL (zero state).  `device_staging` is caller-allocated
+ * device memory of rwkv7_wkv7_host_staging_bytes(...) bytes, 256-byte aligned,
+ * borrowed until the enqueued work has run; it holds n_streams sets of slice
+ * tensors and the kernels' workspace.  The library creates and destroys a few CUDA
+ * events per call and allocates nothing else.
+ *
+ * Ordering: the work is ordered after everything enqueued on `caller_stream` so far.
+ * Without RWKV7_HOST_NO_JOIN, `caller_stream` is made to wait for all of it, so a
+ * synchronisation on `caller_stream` marks completion.  With the flag the caller
+ * issues several passes back to back (each pass still starts after the previous
+ * one's work on the same stream set, so host buffers are written in order) and calls
+ * rwkv7_wkv7_host_join once at the end.
+ */
+#define RWKV7_HOST (-1)
+#define RWKV7_HOST_NO_JOIN 1
+size_t rwkv7_wkv7_host_staging_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype,
+                                     int32_t slices, int32_t n_streams);
+int rwkv7_wkv7_statepass_host(const rwkv7_tensor *host_initial_state,
+                              const rwkv7_tensor *const host_six[6], int64_t chunk_len,
+                              rwkv7_tensor *host_output, rwkv7_tensor *host_next_state,
+                              int32_t device, int32_t slices, void *device_staging,
+                              size_t staging_bytes, const rwkv7_stream *streams, int32_t n_streams,
+                              rwkv7_stream caller_stream, int32_t flags);
+/* Makes `caller_stream` wait for everything enqueued so far on the given streams. */
+int rwkv7_wkv7_host_join(int32_t device, const rwkv7_stream *streams, int32_t n_streams,
+                         rwkv7_stream caller_stream);
+
 /* ------------------------------------------------------- wkv7 training -- */
 /*
  * The forward pass as the reference runs it under autodiff: the recurrence of

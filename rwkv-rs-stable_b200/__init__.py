@@ -394,22 +394,19 @@ def wkv7_statepass_autograd(initial_state: Optional[torch.Tensor], sequence: Wkv
 
 
 class Wkv7HostStatepass:
-    """Statepass for callers whose six sequence tensors, y and S_T live in pinned
-    host memory (an inference server that receives activations from another
-    process, a benchmark that counts the copies).  The batch is cut into equal
-    slices; slice ``i`` uses stream ``i % n_streams`` for its host-to-device copies,
-    its kernel and its device-to-host copies, so the copy of one slice overlaps
-    the kernel and the copy-back of the slices before it.  (b,h) chains are
-    independent, so slicing the batch changes no arithmetic: results are bitwise
-    those of one call on the whole batch whenever both run the same variant of the
-    kernel (a slice with at most half as many chains as the GPU has SMs takes the
-    cluster variant, whose state hand-off differs in the last bits).
+    """``rwkv7_wkv7_statepass_host``: statepass for callers whose six sequence tensors, y and
+    S_T live in pinned host memory (an inference server that receives activations from
+    another process, a benchmark that counts the copies).  The library cuts the batch into
+    equal slices; slice ``i`` uses stream ``i % n_streams`` for its host-to-device copies,
+    its kernels and its device-to-host copies, so the copy of one slice overlaps the kernels
+    and the copy-back of the slices before it.  (b,h) chains are independent, so slicing the
+    batch changes no arithmetic: results are bitwise those of one call on the whole batch
+    whenever both run the same variant of the kernel.
 
-    ``host_state_in`` may be None (S0 = 0).  Device staging buffers for
-    ``n_streams`` slices are allocated once, here; ``__call__`` allocates nothing.
-    The call is asynchronous: work is ordered after the caller's current stream, and
-    the current stream waits for it, so ``torch.cuda.current_stream().synchronize()``
-    (or an event recorded after the call) marks completion."""
+    ``host_state_in`` may be None (S0 = 0).  The device staging buffer and the worker streams
+    are created once, here; ``__call__`` allocates nothing.  The call is asynchronous: work is
+    ordered after the caller's current stream, and (unless ``join=False``) the current stream
+    waits for it, so ``torch.cuda.current_stream().synchronize()`` marks completion."""
 
     def __init__(self, host_six: Sequence[torch.Tensor], host_state_in: Optional[torch.Tensor],
                  host_output: torch.Tensor, host_state_out: torch.Tensor, *, device,
@@ -426,20 +423,22 @@ class Wkv7HostStatepass:
         if slices < 1 or B % slices:
             raise KernelInputsError(2, f"ShapeMismatch: {slices} slices do not divide B={B}")
         self._device = torch.device(device)
-        self._rows = B // slices
+        self._index = self._device.index if self._device.index is not None else torch.cuda.current_device()
         self._slices = slices
         n_streams = max(1, min(n_streams, slices))
         self._streams = [torch.cuda.Stream(self._device) for _ in range(n_streams)]
+        self._stream_array = (ctypes.c_void_p * n_streams)(*[st.cuda_stream for st in self._streams])
         self._host = (list(host_six), host_state_in, host_output, host_state_out)
-        self._sets = []
-        for _ in range(n_streams):
-            six = [torch.empty((self._rows, T, H, N), dtype=r.dtype, device=self._device) for _ in range(6)]
-            s_in = torch.zeros((self._rows, H, N, N), dtype=torch.float32, device=self._device)
-            y = torch.empty_like(six[0])
-            s_out = torch.empty_like(s_in)
-            ws, _ = _wkv7_workspace(six[0])
-            seq = Wkv7PretrainForwardInputs(*six, chunk_len=chunk_len)
-            self._sets.append((six, s_in, y, s_out, Wkv7StatepassCall(s_in, seq, y, s_out, ws)))
+        L = lib()
+        L.rwkv7_wkv7_host_staging_bytes.restype = ctypes.c_size_t
+        L.rwkv7_wkv7_host_staging_bytes.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_int32] * 3
+        nbytes = int(L.rwkv7_wkv7_host_staging_bytes(B, T, H, N, _DTYPES.get(r.dtype, 0), slices, n_streams))
+        self._staging = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self._device)
+        self._desc = [describe(t, device=-1) for t in host_six]
+        self._six = (ctypes.POINTER(Tensor) * 6)(*[ctypes.pointer(d) for d in self._desc])
+        self._s_in = describe(host_state_in, device=-1)
+        self._y, self._s_out = describe(host_output, device=-1), describe(host_state_out, device=-1)
+        self._chunk_len = chunk_len
 
     def __call__(self, join: bool = True) -> None:
         """Enqueues one pass.  With ``join=False`` the caller's stream is not made to wait for the
@@ -447,31 +446,18 @@ class Wkv7HostStatepass:
         copy-in of the next pass overlap the tail of this one, and calls :meth:`join` (or a last
         pass with ``join=True``) before it reads the host outputs.  Passes always execute in
         issue order slice by slice, so the host buffers are never written out of order."""
-        host_six, host_s_in, host_y, host_s_out = self._host
         cur = torch.cuda.current_stream(self._device)
-        start = cur.record_event()
-        for st in self._streams:
-            st.wait_event(start)
-        n = len(self._streams)
-        for i in range(self._slices):
-            b0, b1 = i * self._rows, (i + 1) * self._rows
-            six, s_in, y, s_out, call = self._sets[i % n]
-            with torch.cuda.stream(self._streams[i % n]):
-                for d, h in zip(six, host_six):
-                    d.copy_(h[b0:b1], non_blocking=True)
-                if host_s_in is not None:
-                    s_in.copy_(host_s_in[b0:b1], non_blocking=True)
-                call()
-                host_y[b0:b1].copy_(y, non_blocking=True)
-                host_s_out[b0:b1].copy_(s_out, non_blocking=True)
-        if join:
-            self.join()
+        _check(lib().rwkv7_wkv7_statepass_host(
+            _ref(self._s_in), self._six, ctypes.c_int64(self._chunk_len), _ref(self._y), _ref(self._s_out),
+            ctypes.c_int32(self._index), ctypes.c_int32(self._slices), ctypes.c_void_p(self._staging.data_ptr()),
+            ctypes.c_size_t(self._staging.numel()), self._stream_array, ctypes.c_int32(len(self._streams)),
+            ctypes.c_void_p(cur.cuda_stream), ctypes.c_int32(0 if join else 1)))
 
     def join(self) -> None:
         """Makes the caller's current stream wait for every pass issued so far."""
         cur = torch.cuda.current_stream(self._device)
-        for st in self._streams:
-            cur.wait_event(st.record_event())
+        _check(lib().rwkv7_wkv7_host_join(ctypes.c_int32(self._index), self._stream_array,
+                                          ctypes.c_int32(len(self._streams)), ctypes.c_void_p(cur.cuda_stream)))
 
     def bytes_per_call(self) -> tuple[int, int]:
         """(host-to-device, device-to-host) bytes one call moves."""

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdint>
 #include <mutex>
 #include <vector>
 
@@ -376,6 +377,133 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *s0, const rwkv7_tenso
     size_t scratch_bytes = 0;
     if (int e = wkv7_static_scratch(p.device, &scratch, &scratch_bytes)) return cuda_fail("static scratch address", e);
     return wkv7_dispatch(p, scratch, scratch_bytes, stream);
+}
+
+// ---- wkv7 from pinned host buffers ---------------------------------------------------------
+
+namespace {
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+// Device memory of one slice set: six sequence tensors, y, state in, state out, workspace.
+struct HostSliceLayout {
+    size_t seq, state, ws, total;
+};
+
+HostSliceLayout host_slice_layout(int64_t rows, int64_t T, int64_t H, int64_t N, int32_t dtype) {
+    HostSliceLayout l{};
+    l.seq = align256((size_t)(rows * T * H * N) * dtype_size(dtype));
+    l.state = align256((size_t)(rows * H * N * N) * sizeof(float));
+    l.ws = align256(rwkv7_wkv7_workspace_bytes(rows, T, H, N, dtype));
+    l.total = 7 * l.seq + 2 * l.state + l.ws;
+    return l;
+}
+
+}  // namespace
+
+size_t rwkv7_wkv7_host_staging_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype, int32_t slices,
+                                     int32_t n_streams) {
+    if (slices < 1 || n_streams < 1 || B < 0 || T < 0 || H < 0 || N < 0 || B % slices != 0 || dtype_size(dtype) == 0)
+        return 0;
+    const int32_t sets = n_streams < slices ? n_streams : slices;
+    return (size_t)sets * host_slice_layout(B / slices, T, H, N, dtype).total;
+}
+
+int rwkv7_wkv7_host_join(int32_t device, const rwkv7_stream *streams, int32_t n_streams, rwkv7_stream caller_stream) {
+    clear_error();
+    if (streams == nullptr || n_streams < 1)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: at least one worker stream is required");
+    DeviceGuard guard(device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+    for (int32_t i = 0; i < n_streams; ++i) {
+        cudaEvent_t ev;
+        cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventRecord(ev, (cudaStream_t)streams[i]);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent((cudaStream_t)caller_stream, ev, 0);
+        cudaEventDestroy(ev);   // (released once the recorded work has completed)
+        if (e != cudaSuccess) return cuda_fail("joining the worker streams", (int)e);
+    }
+    return RWKV7_OK;
+}
+
+int rwkv7_wkv7_statepass_host(const rwkv7_tensor *host_s0, const rwkv7_tensor *const host_six[6], int64_t chunk_len,
+                              rwkv7_tensor *host_y, rwkv7_tensor *host_s_out, int32_t device, int32_t slices,
+                              void *device_staging, size_t staging_bytes, const rwkv7_stream *streams,
+                              int32_t n_streams, rwkv7_stream caller_stream, int32_t flags) {
+    clear_error();
+    if (host_six == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: the array of sequence tensors is null");
+    if (streams == nullptr || n_streams < 1)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: at least one worker stream is required");
+    // The contract of the device-resident statepass, applied to the host descriptors.
+    Wkv7Args whole{};
+    RWKV7_TRY(wkv7_validate(host_s0, host_six, chunk_len, host_y, host_s_out, true, host_s0 != nullptr, whole));
+    if (host_six[0]->device != RWKV7_HOST)
+        return fail(RWKV7_ERR_DEVICE_MISMATCH, "DeviceMismatch: host tensors must carry device = RWKV7_HOST (-1), got %d",
+                    host_six[0]->device);
+    const int64_t B = whole.B, T = whole.T, H = whole.H, N = whole.N;
+    if (slices < 1 || B % slices != 0)
+        return fail(RWKV7_ERR_SHAPE_MISMATCH, "ShapeMismatch: %d slices do not divide B=%lld", slices, (long long)B);
+    if (B == 0 || H == 0) return RWKV7_OK;
+    const int32_t dtype = host_six[0]->dtype;
+    const int64_t rows = B / slices;
+    const int32_t sets = n_streams < slices ? n_streams : slices;
+    const HostSliceLayout lay = host_slice_layout(rows, T, H, N, dtype);
+    if (device_staging == nullptr || staging_bytes < (size_t)sets * lay.total)
+        return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: the host statepass needs %zu bytes of device staging, got %zu",
+                    (size_t)sets * lay.total, device_staging == nullptr ? (size_t)0 : staging_bytes);
+    if ((reinterpret_cast<uintptr_t>(device_staging) & 255u) != 0)
+        return fail(RWKV7_ERR_BAD_ARGUMENT, "BadArgument: device staging must be 256-byte aligned");
+    DeviceGuard guard(device);
+    if (guard.error() != cudaSuccess) return cuda_fail("cudaSetDevice", (int)guard.error());
+
+    // fork: every worker stream starts after what the caller has enqueued so far
+    {
+        cudaEvent_t ev;
+        cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventRecord(ev, (cudaStream_t)caller_stream);
+        for (int32_t i = 0; e == cudaSuccess && i < sets; ++i) e = cudaStreamWaitEvent((cudaStream_t)streams[i], ev, 0);
+        cudaEventDestroy(ev);
+        if (e != cudaSuccess) return cuda_fail("ordering the worker streams after the caller's stream", (int)e);
+    }
+    const size_t seq_bytes = (size_t)(rows * T * H * N) * dtype_size(dtype);
+    const size_t state_bytes = (size_t)(rows * H * N * N) * sizeof(float);
+    for (int32_t i = 0; i < slices; ++i) {
+        const int32_t set = i % sets;
+        cudaStream_t st = (cudaStream_t)streams[set];
+        unsigned char *base = static_cast<unsigned char *>(device_staging) + (size_t)set * lay.total;
+        unsigned char *dev_six[6];
+        for (int k = 0; k < 6; ++k) dev_six[k] = base + (size_t)k * lay.seq;
+        unsigned char *dev_y = base + 6 * lay.seq;
+        unsigned char *dev_s_in = base + 7 * lay.seq, *dev_s_out = dev_s_in + lay.state, *dev_ws = dev_s_out + lay.state;
+        cudaError_t e = cudaSuccess;
+        for (int k = 0; e == cudaSuccess && k < 6; ++k)
+            e = cudaMemcpyAsync(dev_six[k], static_cast<const unsigned char *>(host_six[k]->data) + (size_t)i * seq_bytes,
+                                seq_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess) {
+            if (host_s0 != nullptr)
+                e = cudaMemcpyAsync(dev_s_in, static_cast<const unsigned char *>(host_s0->data) + (size_t)i * state_bytes,
+                                    state_bytes, cudaMemcpyHostToDevice, st);
+            else
+                e = cudaMemsetAsync(dev_s_in, 0, state_bytes, st);
+        }
+        if (e != cudaSuccess) return cuda_fail("copying a batch slice to the device", (int)e);
+        Wkv7Args p = whole;
+        p.r = dev_six[0]; p.w = dev_six[1]; p.k = dev_six[2]; p.v = dev_six[3]; p.a = dev_six[4]; p.b = dev_six[5];
+        p.s0 = reinterpret_cast<const float *>(dev_s_in);
+        p.y = dev_y;
+        p.s_out = reinterpret_cast<float *>(dev_s_out);
+        p.B = rows;
+        p.device = device;
+        RWKV7_TRY(wkv7_dispatch(p, dev_ws, lay.ws, (rwkv7_stream)st));
+        e = cudaMemcpyAsync(static_cast<unsigned char *>(host_y->data) + (size_t)i * seq_bytes, dev_y, seq_bytes,
+                            cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(static_cast<unsigned char *>(host_s_out->data) + (size_t)i * state_bytes, dev_s_out,
+                                state_bytes, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return cuda_fail("copying a batch slice back to the host", (int)e);
+    }
+    if (flags & RWKV7_HOST_NO_JOIN) return RWKV7_OK;
+    return rwkv7_wkv7_host_join(device, streams, sets, caller_stream);
 }
 
 namespace {

@@ -214,3 +214,40 @@ def test_unaligned_views_are_refused_on_the_host(pkg):
         pkg.addcmul_custom(view.view(1, 64, 128), torch.zeros(1, 64, 128, dtype=torch.bfloat16),
                            torch.zeros(1, 1, 128, dtype=torch.bfloat16))
     assert e.value.kind == "Unsupported" and "16-byte aligned" in str(e.value)
+
+
+def test_host_statepass_contract(pkg):
+    """``rwkv7_wkv7_statepass_host``: the device-resident statepass's contract applied to host descriptors, plus
+    its own arguments (slices dividing the batch, device staging of the reported size); all checked on the host."""
+    L = pkg.lib()
+    L.rwkv7_wkv7_host_staging_bytes.restype = ctypes.c_size_t
+    L.rwkv7_wkv7_host_staging_bytes.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_int32] * 3
+    B, T, H, N = 4, 64, 2, 64
+    need = L.rwkv7_wkv7_host_staging_bytes(B, T, H, N, pkg.BF16, 2, 2)
+    seq_bytes, state_bytes = 2 * T * H * N * 2, 2 * H * N * N * 4
+    assert need >= 2 * (7 * seq_bytes + 2 * state_bytes)
+    assert L.rwkv7_wkv7_host_staging_bytes(B, T, H, N, pkg.BF16, 3, 2) == 0      # 3 slices do not divide B = 4
+    six = [torch.zeros(B, T, H, N, dtype=torch.bfloat16) for _ in range(6)]
+    y = torch.zeros(B, T, H, N, dtype=torch.bfloat16)
+    s = torch.zeros(B, H, N, N)
+    desc = [pkg.describe(t, device=-1) for t in six]
+    arr = (ctypes.POINTER(pkg.Tensor) * 6)(*[ctypes.pointer(d) for d in desc])
+    yd, sd = pkg.describe(y, device=-1), pkg.describe(s, device=-1)
+    streams = (ctypes.c_void_p * 1)(None)
+
+    def call(slices, staging_bytes, six_arr=arr):
+        return L.rwkv7_wkv7_statepass_host(None, six_arr, ctypes.c_int64(16), ctypes.byref(yd), ctypes.byref(sd),
+                                           ctypes.c_int32(0), ctypes.c_int32(slices), ctypes.c_void_p(256),
+                                           ctypes.c_size_t(staging_bytes), streams, ctypes.c_int32(1),
+                                           ctypes.c_void_p(None), ctypes.c_int32(0))
+
+    assert L.rwkv7_status_string(call(3, 1 << 30)) == b"ShapeMismatch"
+    assert L.rwkv7_status_string(call(2, 1024)) == b"WorkspaceTooSmall"
+    bad = [pkg.describe(t, device=-1) for t in six]
+    bad[3] = pkg.describe(torch.zeros(B, T, H, 32, dtype=torch.bfloat16), device=-1)
+    bad_arr = (ctypes.POINTER(pkg.Tensor) * 6)(*[ctypes.pointer(d) for d in bad])
+    assert L.rwkv7_status_string(call(2, 1 << 30, bad_arr)) == b"ShapeMismatch"
+    assert b"value" in L.rwkv7_last_error_message()
+    on_device = [pkg.describe(t, device=0) for t in six]
+    dev_arr = (ctypes.POINTER(pkg.Tensor) * 6)(*[ctypes.pointer(d) for d in on_device])
+    assert L.rwkv7_status_string(call(2, 1 << 30, dev_arr)) == b"DeviceMismatch"
