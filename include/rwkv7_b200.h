@@ -101,6 +101,12 @@ typedef enum rwkv7_wkv7_path {
 } rwkv7_wkv7_path;
 
 int rwkv7_abi_version(void);
+/* Bit 0: built with -DRWKV7_NVTX (every compute entry point opens an NVTX range named after the reference's
+ * tracing span of the calling module, e.g. "rwkv.infer.model.time_mixer.wkv7" for
+ * crates/rwkv-nn/src/modules/time_mixer/mod.rs:153-156).  Bit 1: built with -DRWKV7_CHECKED (device code
+ * verifies tile rows, output rows and workspace slots before using them and reports RWKV7_ERR_BAD_INDEX
+ * through rwkv7_read_device_status instead of performing a bad access).  The product build returns 0. */
+int rwkv7_build_features(void);
 const char *rwkv7_status_string(int status);
 /* Thread-local text of the last non-zero status returned on this thread. */
 const char *rwkv7_last_error_message(void);

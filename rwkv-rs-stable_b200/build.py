@@ -46,7 +46,21 @@ def _newer(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build_library(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None) -> str:
+# Named variants of the library: the same sources with extra preprocessor flags, built into their own object
+# directory and written beside the product library as librwkv7_b200_<variant>.so.
+VARIANTS = {
+    "checked": ["-DRWKV7_CHECKED", "-DRWKV7_NVTX"],   # device-side index checks + NVTX ranges (tests only)
+}
+
+
+def build_variant(name: str, force: bool = False) -> str:
+    return build_library(force=force, extra_flags=VARIANTS[name], variant=name)
+
+
+def build_library(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None,
+                  variant: str | None = None) -> str:
+    BUILD = os.path.join(HERE, "build", variant) if variant else os.path.join(HERE, "build")
+    LIB = os.path.join(HERE, f"librwkv7_b200_{variant}.so") if variant else os.path.join(HERE, "librwkv7_b200.so")
     os.makedirs(BUILD, exist_ok=True)
     nvcc = _nvcc()
     # nvcc's host compiler: the environment's CC/CXX may point at a compiler
@@ -77,7 +91,7 @@ def build_library(force: bool = False, verbose: bool = False, extra_flags: list[
             if res.returncode != 0:
                 raise RuntimeError(f"nvcc failed for {cmd[-3]}")
     if force or jobs or _newer(LIB, objs):
-        cmd = [nvcc, *host, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+        cmd = [nvcc, *host, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

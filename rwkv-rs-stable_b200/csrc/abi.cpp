@@ -11,6 +11,7 @@
 #include "check.h"
 #include "kernels.h"
 #include "rwkv7_b200.h"
+#include "trace.h"
 
 using namespace rwkv7;
 
@@ -253,6 +254,8 @@ extern "C" {
 
 int rwkv7_abi_version(void) { return RWKV7_ABI_VERSION; }
 
+int rwkv7_build_features(void) { return (RWKV7_TRACE_ENABLED ? 1 : 0) | (RWKV7_CHECKED_ENABLED ? 2 : 0); }
+
 const char *rwkv7_status_string(int status) {
     switch (status) {
         case RWKV7_OK: return "Ok";
@@ -334,6 +337,7 @@ int rwkv7_fused_wkv7_pretrain(const rwkv7_tensor *r, const rwkv7_tensor *w, cons
                               const rwkv7_tensor *v, const rwkv7_tensor *a, const rwkv7_tensor *b,
                               int64_t chunk_len, rwkv7_tensor *output, void *workspace,
                               size_t workspace_bytes, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.wkv7_pretrain");
     const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
     return wkv7_run(nullptr, six, chunk_len, output, nullptr, false, workspace, workspace_bytes, stream, false);
 }
@@ -342,6 +346,7 @@ int rwkv7_fused_wkv7_statetune(const rwkv7_tensor *s0, const rwkv7_tensor *r, co
                                const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
                                const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
                                void *workspace, size_t workspace_bytes, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer_statetune.wkv7");
     const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
     return wkv7_run(s0, six, chunk_len, output, nullptr, false, workspace, workspace_bytes, stream, true);
 }
@@ -351,6 +356,7 @@ int rwkv7_fused_wkv7_statepass(const rwkv7_tensor *s0, const rwkv7_tensor *r, co
                                const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
                                rwkv7_tensor *next_state, void *workspace, size_t workspace_bytes,
                                rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.wkv7");
     const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
     return wkv7_run(s0, six, chunk_len, output, next_state, true, workspace, workspace_bytes, stream, true);
 }
@@ -359,6 +365,7 @@ int rwkv7_fused_wkv7_statepass_noalloc(const rwkv7_tensor *s0, const rwkv7_tenso
                                        const rwkv7_tensor *k, const rwkv7_tensor *v, const rwkv7_tensor *a,
                                        const rwkv7_tensor *b, int64_t chunk_len, rwkv7_tensor *output,
                                        rwkv7_tensor *next_state, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.wkv7");
     // The reference-ordered contract checks come first, so that a malformed call reports the same
     // error here as through rwkv7_fused_wkv7_statepass; only then the capacity of the fixed array.
     const rwkv7_tensor *six[6] = {r, w, k, v, a, b};
@@ -430,6 +437,7 @@ int rwkv7_wkv7_statepass_host(const rwkv7_tensor *host_s0, const rwkv7_tensor *c
                               rwkv7_tensor *host_y, rwkv7_tensor *host_s_out, int32_t device, int32_t slices,
                               void *device_staging, size_t staging_bytes, const rwkv7_stream *streams,
                               int32_t n_streams, rwkv7_stream caller_stream, int32_t flags) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.wkv7_host");
     clear_error();
     if (host_six == nullptr) return fail(RWKV7_ERR_NULL_POINTER, "NullPointer: the array of sequence tensors is null");
     if (streams == nullptr || n_streams < 1)
@@ -536,6 +544,7 @@ int rwkv7_fused_wkv7_forward_saved(const rwkv7_tensor *s0, const rwkv7_tensor *r
                                    rwkv7_tensor *next_state, rwkv7_tensor *snapshots,
                                    rwkv7_tensor *state_replacement, void *workspace, size_t workspace_bytes,
                                    rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.train.model.time_mixer.wkv7_forward");
     clear_error();
     const rwkv7_tensor *six_t[6] = {r_t, w, k, v, a, b};
     TensorInfo six[6];
@@ -600,6 +609,7 @@ int rwkv7_fused_wkv7_backward(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, c
                               int64_t chunk_len, const rwkv7_tensor *output_grad,
                               const rwkv7_tensor *next_state_grad, rwkv7_tensor *const sequence_grads[6],
                               rwkv7_tensor *initial_state_grad, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.train.model.time_mixer.wkv7_backward");
     return wkv7_backward_impl(s0, r_t, w, k, v, a, b, snapshots, state_replacement, chunk_len, output_grad,
                               next_state_grad, sequence_grads, initial_state_grad, false, nullptr, 0, stream);
 }
@@ -611,6 +621,7 @@ int rwkv7_fused_wkv7_backward_parallel(const rwkv7_tensor *s0, const rwkv7_tenso
                                        const rwkv7_tensor *output_grad, const rwkv7_tensor *next_state_grad,
                                        rwkv7_tensor *const sequence_grads[6], rwkv7_tensor *initial_state_grad,
                                        void *workspace, size_t workspace_bytes, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.train.model.time_mixer.wkv7_backward");
     return wkv7_backward_impl(s0, r_t, w, k, v, a, b, snapshots, state_replacement, chunk_len, output_grad,
                               next_state_grad, sequence_grads, initial_state_grad, true, workspace, workspace_bytes,
                               stream);
@@ -683,6 +694,7 @@ static int wkv7_backward_impl(const rwkv7_tensor *s0, const rwkv7_tensor *r_t, c
 
 int rwkv7_fused_mix6(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6],
                      rwkv7_tensor *const outputs[6], rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.mix6");
     clear_error();
     MixArgs p{};
     RWKV7_TRY(mix6_common(x_t, scales, &p));
@@ -701,6 +713,7 @@ int rwkv7_fused_mix6(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6
 
 int rwkv7_fused_mix6_stacked(const rwkv7_tensor *x_t, const rwkv7_tensor *const scales[6],
                              rwkv7_tensor *stacked, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.mix6");
     clear_error();
     MixArgs p{};
     RWKV7_TRY(mix6_common(x_t, scales, &p));
@@ -763,6 +776,7 @@ static int addcmul_run(const rwkv7_tensor *base_t, const rwkv7_tensor *diff_t,
 
 int rwkv7_fused_addcmul(const rwkv7_tensor *base, const rwkv7_tensor *diff, const rwkv7_tensor *scale,
                         rwkv7_tensor *output, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.addcmul");
     static const char *sn[1] = {"scale"};
     static const char *on[1] = {"output"};
     const rwkv7_tensor *scales[1] = {scale};
@@ -773,11 +787,13 @@ int rwkv7_fused_addcmul(const rwkv7_tensor *base, const rwkv7_tensor *diff, cons
 int rwkv7_fused_addcmul5(const rwkv7_tensor *base, const rwkv7_tensor *diff,
                          const rwkv7_tensor *const scales[5], rwkv7_tensor *const outputs[5],
                          rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.addcmul5");
     return addcmul_run(base, diff, scales, outputs, 5, kMixScaleNames, kMixOutNames, stream);
 }
 
 int rwkv7_fused_token_shift_diff(const rwkv7_tensor *x_t, rwkv7_tensor *state_t,
                                  const rwkv7_tensor *ids_t, rwkv7_tensor *diff_t, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.time_mixer.token_shift_diff");
     clear_error();
     const TensorInfo x{"embedded_context", x_t}, state{"embedded_token_shift", state_t},
         ids{"batch_ids", ids_t};
@@ -866,6 +882,7 @@ int rwkv7_fused_weight_prepare(const rwkv7_tensor *k_t, const rwkv7_tensor *lr_t
                                const rwkv7_tensor *vp_t, const rwkv7_tensor *vf_t, const rwkv7_tensor *nu_t,
                                int64_t num_heads, rwkv7_tensor *w_t, rwkv7_tensor *kt_t, rwkv7_tensor *a_t,
                                rwkv7_tensor *b_t, rwkv7_tensor *v_t, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.weight_prepare");
     clear_error();
     const TensorInfo k{"key_precursor", k_t};
     RWKV7_TRY(check_sequence_tensor(k));
@@ -916,6 +933,7 @@ int rwkv7_fused_gated_readout(const rwkv7_tensor *y_t, const rwkv7_tensor *r_t, 
                               const rwkv7_tensor *v_t, const rwkv7_tensor *gate_t, const rwkv7_tensor *gamma_t,
                               const rwkv7_tensor *beta_t, const rwkv7_tensor *bonus_t, double epsilon,
                               int64_t num_heads, rwkv7_tensor *out_t, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.gated_readout");
     clear_error();
     const TensorInfo y{"wkv7_output", y_t};
     RWKV7_TRY(check_sequence_tensor(y));
@@ -956,6 +974,7 @@ size_t rwkv7_channel_mixer_workspace_bytes(int64_t B, int64_t T, int64_t C, int6
 int rwkv7_fused_channel_mixer(const rwkv7_tensor *x_t, const rwkv7_tensor *scale_t, const rwkv7_tensor *kw_t,
                               const rwkv7_tensor *vw_t, rwkv7_tensor *out_t, void *workspace,
                               size_t workspace_bytes, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.infer.model.channel_mixer");
     clear_error();
     const TensorInfo x{"embedded_context", x_t}, scale{"key_scale", scale_t}, kw{"key_weight", kw_t},
         vw{"value_weight", vw_t};
@@ -1012,6 +1031,7 @@ int rwkv7_fused_lm_head_ce_partial(const rwkv7_tensor *x_t, const rwkv7_tensor *
                                    const rwkv7_tensor *targets_t, int64_t vocab_offset,
                                    rwkv7_tensor *partials_t, void *workspace, size_t workspace_bytes,
                                    rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.train.lm_head_ce.partial");
     clear_error();
     const TensorInfo x{"x", x_t}, w{"weight_shard", w_t}, tg{"targets", targets_t},
         pt{"partials", partials_t};
@@ -1058,6 +1078,7 @@ int rwkv7_fused_lm_head_ce_partial(const rwkv7_tensor *x_t, const rwkv7_tensor *
 
 int rwkv7_lm_head_ce_finalize(const rwkv7_tensor *partials_all_t, const rwkv7_tensor *targets_t,
                               rwkv7_tensor *lse_t, rwkv7_tensor *loss_t, rwkv7_stream stream) {
+    RWKV7_TRACE("rwkv.train.lm_head_ce.finalize");
     clear_error();
     const TensorInfo pa{"partials_all", partials_all_t}, tg{"targets", targets_t}, lse{"lse", lse_t},
         loss{"loss", loss_t};

@@ -41,6 +41,7 @@
 
 #include "kernels.h"
 #include "sm100_umma.cuh"
+#include "trace.h"
 
 namespace rwkv7 {
 
@@ -178,6 +179,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
     auto issue_tma = [&](long long unit) {
         const int chain = (int)(unit / seg_chunks), chunk = chunk0 + (int)(unit % seg_chunks);
         const int bi = chain / H, h = chain % H;
+        if (!RWKV7_IN_RANGE(chain < nchains && chunk * kL < Tlen, status)) return;   // (the wait then expires)
         mbar_expect_tx(bar_tma, kRawBytes);
         const int trow = bi * Tlen + chunk * kL;
 #pragma unroll
@@ -244,8 +246,10 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                 if (tot0 < -kMaxLogDecay || tot1 < -kMaxLogDecay || !(tot0 <= 0.f) || !(tot1 <= 0.f))
                     atomicOr(&flags[chain], 1);
                 float *vec = vectors + (size_t)unit * kVecFloats;
-                *reinterpret_cast<float2 *>(vec + 2 * j2) = make_float2(__expf(tot0), __expf(tot1));
-                *reinterpret_cast<float2 *>(vec + 64 + 2 * j2) = make_float2(__expf(tot0 - m0), __expf(tot1 - m1));
+                if (RWKV7_IN_RANGE(unit < units && 2 * j2 + 1 < kN, status)) {
+                    *reinterpret_cast<float2 *>(vec + 2 * j2) = make_float2(__expf(tot0), __expf(tot1));
+                    *reinterpret_cast<float2 *>(vec + 64 + 2 * j2) = make_float2(__expf(tot0 - m0), __expf(tot1 - m1));
+                }
                 *reinterpret_cast<float2 *>(emv + 2 * j2) = make_float2(em0 * kInvOpScale, em1 * kInvOpScale);
             }
             float ep0 = __expf(base0 - m0) * kOpScale, ep1 = __expf(base1 - m1) * kOpScale;   // e^{c_{t-1} - m} * scale
@@ -258,6 +262,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                 const float i0 = __fdividef(kOpScale * kOpScale, e0), i1 = __fdividef(kOpScale * kOpScale, e1);
                 const float2 a2 = ld2(XA, u), r2 = ld2(XR, u), b2 = ld2(XB, u), k2 = ld2(XK, u);
                 const uint32_t o = off16(t, 2 * j2);
+                if (!RWKV7_IN_RANGE(o + 4 <= kPanel, status)) continue;
                 *reinterpret_cast<uint32_t *>(smem + kAR + o) = pack_h2(a2.x * ep0, a2.y * ep1);
                 *reinterpret_cast<uint32_t *>(smem + kAR + kPanel + o) = pack_h2(r2.x * e0, r2.y * e1);
                 *reinterpret_cast<uint32_t *>(smem + kBK + o) = pack_h2(b2.x * i0, b2.y * i1);
@@ -541,15 +546,16 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                         w[e2] = pack_h2(x0 * sc, x1 * sc);
                     }
                     // panel hf, row k = this thread's lane, 16-byte chunk of columns n
-                    *reinterpret_cast<uint4 *>(smem + kStage + hf * (2 * kPanel) + off16(row, half * 32 + e8 * 8)) =
-                        make_uint4(w[0], w[1], w[2], w[3]);
+                    const uint32_t so = hf * (2 * kPanel) + off16(row, half * 32 + e8 * 8);
+                    if (RWKV7_IN_RANGE(so + 16 <= kOperatorBytes, status))
+                        *reinterpret_cast<uint4 *>(smem + kStage + so) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
         tc_fence_before();
         fence_proxy_async();
         __syncthreads();
-        if (tid == 0) {
+        if (tid == 0 && RWKV7_IN_RANGE(unit >= 0 && unit < units, status)) {
             asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(operators + (size_t)unit * kOperatorBytes),
                          "r"(sb + kStage), "r"(kOperatorBytes)
                          : "memory");
@@ -657,6 +663,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 const int s = c % NS;
                 if (c >= NS && !mbar_wait(bar_empty + s, (uint32_t)((c / NS - 1) & 1))) { atomicOr(abort_flag, 1); break; }
                 if (*reinterpret_cast<volatile int *>(abort_flag)) break;
+                if (!RWKV7_IN_RANGE(c < seg_chunks && (chunk0 + c) * kL < Tlen, status)) break;
                 mbar_expect_tx(bar_full + s, kStageBytes);
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(sb + SM::kStages + s * kStageBytes), "l"(ops + (size_t)c * kOperatorBytes),
@@ -733,7 +740,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                     uint32_t w[4];
 #pragma unroll
                     for (int e2 = 0; e2 < 4; ++e2) w[e2] = pack_h2(Z[e8 * 8 + 2 * e2], Z[e8 * 8 + 2 * e2 + 1]);
-                    *reinterpret_cast<uint4 *>(smem + SM::kZ + off16(jp, i0 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (RWKV7_IN_RANGE(off16(jp, i0 + e8 * 8) + 16 <= kPanel, status))
+                        *reinterpret_cast<uint4 *>(smem + SM::kZ + off16(jp, i0 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 fence_proxy_async();
                 mbar_arrive(bar_zready);
@@ -768,7 +776,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             const bool skip = *chain_bad != 0 || (check_flags && flags[chain] != 0);   // flagged chains are recomputed from state_in
             if (state_out != nullptr && !skip && !*reinterpret_cast<volatile int *>(abort_flag)) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) state_out[((size_t)chain * kN + i0 + e) * kN + jp] = Z[e];
+                for (int e = 0; e < 32; ++e)
+                    if (RWKV7_IN_RANGE(i0 + e < kN && jp < kN, status)) state_out[((size_t)chain * kN + i0 + e) * kN + jp] = Z[e];
             }
         } else {
             // ---------------- output tokens t.  A chunk's y tile is staged in shared memory (one of two
@@ -805,7 +814,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                     asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll
                     for (int e8 = 0; e8 < 4; ++e8)
-                        *reinterpret_cast<uint4 *>(stage + off16(tq, i0 + e8 * 8)) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
+                        if (RWKV7_IN_RANGE(off16(tq, i0 + e8 * 8) + 16 <= kPanel, status))
+                            *reinterpret_cast<uint4 *>(stage + off16(tq, i0 + e8 * 8)) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
                     fence_proxy_async();
                     asm volatile("bar.sync 2, 128;" ::: "memory");
                     if (elected) {
