@@ -43,17 +43,21 @@ DECODE_BYTES_PER_BH = 2 * STATE_BYTES + 7 * 64 * 2
 
 def bench_config(B, T, H, N, path="auto"):
     """The `config` object of the JSON line (shared by both arms)."""
-    return {"workload": f"cfg1 WKV7 chunked prefill B={B} T={T} H={H} N={N} per GPU, S0=0, bf16 in/out, fp32 state",
+    return {"workload": f"cfg1 WKV7 chunked prefill B={B} T={T} H={H} N={N} per GPU, S0=0, bf16 in/out, fp32 state, "
+                        "64-token chunks: per-chunk operators (fp16 tensor-core tiles) + one scan per chain",
             "B": B, "T": T, "H": H, "N": N, "path": path,
             "l2": "inputs (302 MB per step) exceed the 126 MB L2; no flush needed",
             "sharding": "batch x head shard per rank, no collective on the data path"}
 
 
-# DRAM bytes of one prefill launch from an ncu capture of this very workload (configuration 1,
-# B=8: 303.6 MB read + 41.8 MB written; part of y is still in L2 when the kernel ends); traffic is
-# proportional to the number of chains.  A constant taken from that capture, not measured in the run.
-NCU_TRAFFIC_BYTES_CFG1 = 345.4e6   # ncu dram__bytes_read.sum + dram__bytes_write.sum, B=8
-NCU_TRAFFIC_SOURCE = "ncu capture of the chunked prefill kernel on configuration 1 (constant, scaled by B/8)"
+# DRAM bytes of one prefill step from an ncu capture of this very workload (configuration 1, B=8): the
+# operator kernel reads 251.7 MB (the five inputs it needs, once) and writes 160 MB (the per-chunk operators;
+# part of them is still in L2 when it ends), the scan reads 256.4 MB (operators and v) and writes 34 MB of y.
+# Traffic is proportional to the number of chains.  A constant taken from that capture, not measured in the run.
+NCU_TRAFFIC_BYTES_CFG1 = 702.6e6   # dram__bytes_read.sum + dram__bytes_write.sum over both kernels, B=8
+NCU_TRAFFIC_SOURCE = ("ncu capture of wkv7_chunk_operator_kernel + wkv7_state_scan_kernel on configuration 1 "
+                      "(constant, scaled by B/8); about twice the algorithmic bytes because the per-chunk "
+                      "operators (32.5 KB per 64 tokens of a chain) pass through memory between the two kernels")
 
 
 def sustained_tflops():
@@ -780,7 +784,9 @@ def main():
                 "traffic": NCU_TRAFFIC_BYTES_CFG1 * (B / 8.0) if args.path != "sequential" else None,
                 "traffic_source": NCU_TRAFFIC_SOURCE if args.path != "sequential" else None,
                 "peak_source": peak_kind,
-                "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kernel_ms}
+                "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kernel_ms,
+                "kernels": "one step = wkv7_chunk_operator_kernel (about 3/4 of the time) + wkv7_state_scan_kernel + two "
+                           "flagged-chain kernels that exit at once; kernel_ms is the device time of the whole step"}
     if decode is not None:
         # the metric names two figures: the second one (decode state GB/s against the HBM peak) rides here
         roofline["decode_gb_per_s"] = decode["state_gb_per_s"]

@@ -295,6 +295,11 @@ int rwkv7_set_wkv7_cluster(int cluster_size) {
     return RWKV7_OK;
 }
 
+int rwkv7_set_wkv7_overlap(int on) {
+    wkv7_set_split_overlap(on);
+    return RWKV7_OK;
+}
+
 int64_t rwkv7_kernel_launch_count(void) { return launch_count(); }
 
 int rwkv7_read_device_status(int device, rwkv7_stream stream) {
@@ -329,7 +334,14 @@ size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, in
     const int path = g_wkv7_path.load();
     if (path == RWKV7_WKV7_SEQUENTIAL) return 0;
     if ((path == RWKV7_WKV7_SPLIT || (path == RWKV7_WKV7_AUTO && T >= kSplitMinTokens)) && dtype == RWKV7_BF16 && N == 64)
-        return wkv7_split_workspace_bytes(B, T, H, N);
+    {
+        // (the size depends on whether the scan will overlap the operator kernel, i.e. on the SM count of
+        // the device the call will run on: the calling thread's current device is taken)
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || num_sms(dev, &sms) != RWKV7_OK) sms = 0;
+        (void)cudaGetLastError();
+        return wkv7_split_workspace_bytes(B, T, H, N, sms);
+    }
     return wkv7_chunked_workspace_bytes(B, T, H, N);
 }
 

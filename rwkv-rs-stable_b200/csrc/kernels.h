@@ -77,7 +77,11 @@ int launch_wkv7_chunked(const Wkv7Args &p, void *workspace, size_t workspace_byt
 // segment of chunks; `wkv7_split_workspace_bytes` is the size the launcher prefers (fewest segments
 // within its operator budget), `wkv7_split_min_workspace_bytes` the least it can work with.
 // Chains it cannot resolve (decay range, non-finite operators) are left flagged for the caller.
-size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
+size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int num_sms);
+// With at most as many chains as SMs the scan of a segment of chunks runs on a second stream beside the
+// operator kernel of the next segment (1, default) or after it on the caller's stream (0).
+int wkv7_split_overlap();
+void wkv7_set_split_overlap(int on);
 size_t wkv7_split_min_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N);
 bool wkv7_split_supported(const Wkv7Args &p);
 int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream);

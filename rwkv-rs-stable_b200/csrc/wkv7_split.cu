@@ -36,6 +36,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -128,7 +129,7 @@ enum { XR = 0, XW = 1, XK = 2, XA = 3, XB = 4 };
 __global__ void __launch_bounds__(kThreads1, 2)
 wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned char *__restrict__ operators,
                            float *__restrict__ vectors, int *__restrict__ flags, int Tlen, int H, int chunk0,
-                           int seg_chunks, int nchains, int *status) {
+                           int seg_chunks, int nchains, int *work_counter, int *status) {
     extern __shared__ __align__(1024) unsigned char smem[];
     if (smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
@@ -145,6 +146,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
     uint64_t *bar_mma = bar_tma + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kMisc1 + 32);
     int *abort_flag = reinterpret_cast<int *>(smem + kMisc1 + 48);
+    int *next_slot = abort_flag + 1;   // the chunk this CTA works on next (thread 0 draws it, all read it)
     float *grp = reinterpret_cast<float *>(smem + kMisc1 + 256);     // [8][64]
     float *emv = reinterpret_cast<float *>(smem + kMisc1 + 256 + 2048);   // e^{m_j} / kOpScale [64]
 
@@ -153,6 +155,9 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         mbar_init(bar_mma, 1);
         mbar_fence_init();
         *abort_flag = 0;
+        // Chunks are drawn from a counter (zeroed by the host), so that CTAs which start late - the scan of
+        // the previous segment may still hold their place on the SM - simply take fewer of them.
+        *next_slot = work_counter ? atomicAdd(work_counter, 1) : (int)blockIdx.x;
 #pragma unroll
         for (int i = 0; i < 5; ++i) tma_prefetch_desc(&maps.m[i]);
     }
@@ -185,13 +190,13 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
 #pragma unroll
         for (int i = 0; i < 5; ++i) tma_load_2d(raw + i * kPanel, &maps.m[i], h * kN, trow, bar_tma);
     };
-    long long unit = blockIdx.x;
+    long long unit = *next_slot;
     if (tid == 0 && unit < units) issue_tma(unit);
     uint32_t tma_phase = 0, mma_phase = 0;
     bool tma_pending = unit < units;   // a tile batch is in flight (thread 0's view is what matters)
     bool failed = false;
 
-    for (; unit < units; unit += gridDim.x) {
+    for (; unit < units; unit = *next_slot) {
         const int chain = (int)(unit / seg_chunks), chunk = chunk0 + (int)(unit % seg_chunks);
         const int valid = min(kL, Tlen - chunk * kL);
         if (!mbar_wait(bar_tma, tma_phase)) atomicOr(abort_flag, 1);
@@ -476,9 +481,14 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         mma_phase ^= 1;
         tc_fence_after();
         // T has been read: the raw-tile region (scratch of the inverse, T, W) is dead, request the next chunk's tiles
-        const long long next = unit + gridDim.x;
-        if (tid == 0 && next < units && !*abort_flag) issue_tma(next);
-        if (next < units) tma_pending = true;
+        if (tid == 0) {
+            const long long next = work_counter ? (long long)atomicAdd(work_counter, 1) : unit + gridDim.x;
+            *next_slot = next < units ? (int)next : 0x7fffffff;
+            if (next < units && !*abort_flag) {
+                issue_tma(next);
+                tma_pending = true;
+            }
+        }
         {
             uint32_t v[32];
             tmem_ld32(tmem + lane_base + hf * 32, v);
@@ -755,7 +765,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
                 float2 gg_next = gg;
                 if (c + 1 < n) gg_next = make_float2(vecs[(size_t)(c + 1) * kVecFloats + jp], vecs[(size_t)(c + 1) * kVecFloats + 64 + jp]);
-                if (!mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                // (polled without suspending: this wait is on the serial path of the chain)
+                if (!mbar_wait_spin(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
                 tc_fence_after();
                 uint32_t v[32];
                 tmem_ld32(tmem + lane_base + a * 64 + i0, v);
@@ -870,55 +881,162 @@ constexpr size_t kOperatorBudget = (size_t)768 << 20;
 
 }  // namespace
 
-// Workspace: one fallback flag per chain, a carried fp32 state per chain (used only when a call is
-// cut into segments), then per (chain, chunk of a segment) the two fp32 vectors and the operator.
+// ---- host side ------------------------------------------------------------------------------
+//
+// Workspace: [flags: one int per chain][kMaxSegments work counters][carried fp32 state per chain]
+//            [vectors of buffer 0][vectors of buffer 1][operators of buffer 0][operators of buffer 1].
+// A call is cut into segments of chunks.  With at most as many chains as SMs the scan of a segment
+// leaves most of the GPU idle (one latency-bound CTA per chain), so it runs on a second stream beside
+// the operator kernel of the next segment, which writes the other buffer.
+
+namespace {
+
+constexpr int kMaxSegments = 1024;
+
+struct WorkspaceLayout {
+    size_t flags, counters, carry, vectors[2], operators[2], total;
+    size_t seg;      // chunks per segment
+    int buffers;     // 1 or 2
+};
+
+size_t fixed_part(size_t chains) {
+    return align_up(chains * sizeof(int)) + align_up(kMaxSegments * sizeof(int)) + align_up(chains * kN * kN * sizeof(float));
+}
+
+WorkspaceLayout layout_for(size_t chains, size_t seg, int buffers) {
+    WorkspaceLayout l{};
+    l.seg = seg;
+    l.buffers = buffers;
+    l.flags = 0;
+    l.counters = align_up(chains * sizeof(int));
+    l.carry = l.counters + align_up(kMaxSegments * sizeof(int));
+    size_t off = l.carry + align_up(chains * kN * kN * sizeof(float));
+    for (int b = 0; b < 2; ++b) {
+        l.vectors[b] = off;
+        if (b < buffers) off += chains * seg * kVecFloats * sizeof(float);   // (512 bytes per chunk: stays aligned)
+    }
+    for (int b = 0; b < 2; ++b) {
+        l.operators[b] = off;
+        if (b < buffers) off += chains * seg * kOperatorBytes;
+    }
+    l.total = off;
+    return l;
+}
+
+// How a call is cut: the number of segments that balances the scan of the last segment (which nothing
+// overlaps) against the few microseconds a segment boundary costs, within the operator budget.
+// The operator kernel's CTAs are persistent and fill every SM twice over, so the scan only finds room if
+// the operator kernel leaves it one place per chain: 2 * SMs - chains CTAs instead of 2 * SMs.  That costs
+// the operator kernel chains / (2 * SMs) of its throughput, and a scan CTA that shares its SM with an
+// operator CTA takes about 1.3 us per chunk instead of 0.95 us.  Measured (B200, 148 SMs): 32 chains x 1024
+// chunks 1.39 ms overlapped against 1.68 ms in sequence; 32 chains x 128 chunks 257 against 236 us (segments
+// of 26 chunks give the operator kernel 3.2 chunks per CTA: a fourth round for 0.2 rounds of work); 96 chains
+// x 64 chunks 301 against 247 us.  Hence: at most half as many chains as SMs, and at least 256 chunks.
+bool overlap_applies(size_t chains, size_t nchunks, int num_sms) {
+    return wkv7_split_overlap() != 0 && num_sms > 0 && 2 * chains <= (size_t)num_sms && nchunks >= 256;
+}
+
+size_t preferred_segment(size_t chains, size_t nchunks, bool overlap) {
+    size_t seg = nchunks;
+    if (overlap) {
+        size_t nseg = 1;
+        while ((nseg + 1) * (nseg + 1) * 4 <= nchunks && nseg < 32) ++nseg;   // about sqrt(nchunks / 4)
+        seg = (nchunks + nseg - 1) / nseg;
+    }
+    const size_t per_chunk = chains * kOperatorBytes * (overlap ? 2 : 1);
+    if (seg * per_chunk > kOperatorBudget) seg = kOperatorBudget / per_chunk;
+    if ((nchunks + seg - 1) / (seg ? seg : 1) > (size_t)kMaxSegments) seg = (nchunks + kMaxSegments - 1) / kMaxSegments;
+    return seg < 1 ? 1 : seg;
+}
+
+// Second stream and events of a device, created on first use.
+struct DeviceStreams {
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork = nullptr, built[2] = {nullptr, nullptr}, scanned[2] = {nullptr, nullptr};
+    bool ok = false;
+};
+
+std::mutex g_streams_mu;
+DeviceStreams g_streams[64];
+
+// (the caller holds g_streams_mu and has made `device` current)
+DeviceStreams *device_streams(int device) {
+    if (device < 0 || device >= 64) return nullptr;
+    DeviceStreams &d = g_streams[device];
+    if (!d.ok) {
+        int least = 0, greatest = 0;
+        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
+        if (cudaStreamCreateWithPriority(&d.side, cudaStreamNonBlocking, greatest) != cudaSuccess) return nullptr;
+        cudaEvent_t *evs[5] = {&d.fork, &d.built[0], &d.built[1], &d.scanned[0], &d.scanned[1]};
+        for (cudaEvent_t *e : evs)
+            if (cudaEventCreateWithFlags(e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        d.ok = true;
+    }
+    return &d;
+}
+
+std::atomic<int> g_split_overlap{1};
+
+}  // namespace
+
+int wkv7_split_overlap() { return g_split_overlap.load(); }
+void wkv7_set_split_overlap(int on) { g_split_overlap.store(on ? 1 : 0); }
+
 size_t wkv7_split_min_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     (void)T;
     if (N != kN) return 0;
-    const size_t chains = (size_t)(B * H);
-    return align_up(chains * sizeof(int)) + align_up(chains * kN * kN * sizeof(float)) +
-           align_up(chains * kVecFloats * sizeof(float)) + chains * kOperatorBytes;
+    return layout_for((size_t)(B * H), 1, 1).total;
 }
 
-size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
+size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int num_sms) {
     if (N != kN) return 0;
     const size_t chains = (size_t)(B * H);
     const size_t nchunks = (size_t)((T + kL - 1) / kL);
-    size_t seg = nchunks;
-    if (chains * seg * kOperatorBytes > kOperatorBudget) seg = kOperatorBudget / (chains * kOperatorBytes);
-    if (seg < 1) seg = 1;
-    return align_up(chains * sizeof(int)) + align_up(chains * kN * kN * sizeof(float)) +
-           align_up(chains * seg * kVecFloats * sizeof(float)) + chains * seg * kOperatorBytes;
+    const bool overlap = overlap_applies(chains, nchunks, num_sms);
+    return layout_for(chains, preferred_segment(chains, nchunks, overlap), overlap ? 2 : 1).total;
 }
 
 bool wkv7_split_supported(const Wkv7Args &p) {
     auto aligned = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     return p.N == kN && p.bf16 && aligned(p.r) && aligned(p.w) && aligned(p.k) && aligned(p.v) && aligned(p.a) &&
-           aligned(p.b) && aligned(p.y) && p.B * p.T < (int64_t(1) << 31) && p.B * p.H < (int64_t(1) << 30);
+           aligned(p.b) && aligned(p.y) && p.B * p.T < (int64_t(1) << 31) && p.B * p.H < (int64_t(1) << 24);
 }
 
-// Enqueues the two kernels (once per segment of chunks) and leaves one flag per chain in the first
-// B*H ints of the workspace: 1 for chains that must be recomputed by the caller's next kernel.
-// `check_flags_for_state`: the final state of a flagged chain is not written (it may alias the initial state).
+// Enqueues the two kernels, once per segment of chunks, and leaves one flag per chain in the first
+// B*H ints of the workspace: 1 for chains that the caller's next kernel must recompute (their final
+// state is not written: it may alias the initial state that the recomputation starts from).
 int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
     EncodeTiledFn encode = encode_fn();
     if (encode == nullptr) return (int)cudaErrorNotSupported;
     const size_t chains = (size_t)(p.B * p.H);
     const int nchunks = (int)((p.T + kL - 1) / kL);
-    unsigned char *ws = static_cast<unsigned char *>(workspace);
-    int *flags = reinterpret_cast<int *>(ws);
-    size_t off = align_up(chains * sizeof(int));
-    float *carry = reinterpret_cast<float *>(ws + off);
-    off += align_up(chains * kN * kN * sizeof(float));
-    if (workspace_bytes < off) return (int)cudaErrorInvalidValue;
-    // segment length from the space that is left
+    // The plan: overlapped (two buffers) when it applies and the workspace holds two segments of a useful
+    // length, else one buffer with the longest segment that fits.
+    bool overlap = overlap_applies(chains, (size_t)nchunks, p.num_sms);
+    size_t seg = preferred_segment(chains, (size_t)nchunks, overlap);
+    const size_t fixed = fixed_part(chains);
+    if (workspace_bytes < fixed) return (int)cudaErrorInvalidValue;
     const size_t per_chunk = chains * ((size_t)kVecFloats * sizeof(float) + kOperatorBytes);
-    size_t seg = (workspace_bytes - off) / per_chunk;   // (a chunk's vectors are 512 bytes: no padding between them)
-    if (seg < 1) return (int)cudaErrorInvalidValue;
+    if (overlap && layout_for(chains, seg, 2).total > workspace_bytes) {
+        const size_t fit = (workspace_bytes - fixed) / (2 * per_chunk);
+        if (fit >= 8) seg = fit;
+        else overlap = false;
+    }
+    if (!overlap) {
+        seg = preferred_segment(chains, (size_t)nchunks, false);
+        const size_t fit = (workspace_bytes - fixed) / per_chunk;
+        if (fit < 1) return (int)cudaErrorInvalidValue;
+        if (seg > fit) seg = fit;
+    }
     if (seg > (size_t)nchunks) seg = (size_t)nchunks;
-    float *vectors = reinterpret_cast<float *>(ws + off);
-    off += align_up(chains * seg * kVecFloats * sizeof(float));
-    unsigned char *operators = ws + off;
+    const int nsegments = (int)(((size_t)nchunks + seg - 1) / seg);
+    if (nsegments > kMaxSegments) return (int)cudaErrorInvalidValue;
+    if (nsegments < 2) overlap = false;
+    const WorkspaceLayout lay = layout_for(chains, seg, overlap ? 2 : 1);
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    int *flags = reinterpret_cast<int *>(ws + lay.flags);
+    int *counters = reinterpret_cast<int *>(ws + lay.counters);
+    float *carry = reinterpret_cast<float *>(ws + lay.carry);
 
     OperatorMaps omaps;
     ScanMaps smaps;
@@ -947,41 +1065,82 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     }
     int *status = nullptr;
     if (int e = device_status_ptr(p.device, &status)) return e;
-    cudaError_t e = cudaMemsetAsync(flags, 0, chains * sizeof(int), stream);
-    if (e != cudaSuccess) return (int)e;
 
     auto k1 = wkv7_chunk_operator_kernel;
-    e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem1);
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem1);
     if (e != cudaSuccess) return (int)e;
-    const bool many = (int64_t)chains > (int64_t)p.num_sms;   // more chains than SMs: two scan CTAs per SM
-    auto launch_scan = [&](auto kern, size_t smem_bytes, const float *s_in, float *s_out, int c0, int n,
-                           int check) -> cudaError_t {
-        cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-        if (err != cudaSuccess) return err;
-        kern<<<(unsigned)chains, kThreads2, smem_bytes, stream>>>(
-            smaps, operators, vectors, s_in, s_out, reinterpret_cast<__nv_bfloat16 *>(p.y), flags, (int)p.T, (int)p.H,
-            c0, n, n, check, status);
+    // Beside an operator CTA only the two-stage scan fits on an SM; it is also the one for more chains than SMs.
+    const bool small_scan = overlap || (int64_t)chains > (int64_t)p.num_sms;
+    auto launch_scan = [&](cudaStream_t st, int buf, const float *s_in, float *s_out, int c0, int n, int check) -> cudaError_t {
+        const unsigned char *ops = ws + lay.operators[buf];
+        const float *vecs = reinterpret_cast<const float *>(ws + lay.vectors[buf]);
+        auto go = [&](auto kern, size_t smem_bytes) -> cudaError_t {
+            cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+            if (err != cudaSuccess) return err;
+            kern<<<(unsigned)chains, kThreads2, smem_bytes, st>>>(smaps, ops, vecs, s_in, s_out,
+                                                                  reinterpret_cast<__nv_bfloat16 *>(p.y), flags, (int)p.T,
+                                                                  (int)p.H, c0, n, n, check, status);
+            count_launch();
+            return cudaGetLastError();
+        };
+        return small_scan ? go(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes) : go(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes);
+    };
+    auto launch_operators = [&](int buf, int segment, int c0, int n) -> cudaError_t {
+        const long long units = (long long)chains * n;
+        const long long places = 2LL * p.num_sms - (overlap ? (long long)chains : 0);   // (see overlap_applies)
+        const unsigned grid = (unsigned)(units < places ? units : places);
+        // (the operator of (chain, chunk) sits at index chain * n + chunk - c0 of the buffer in both kernels)
+        k1<<<grid, kThreads1, kSmem1, stream>>>(omaps, ws + lay.operators[buf], reinterpret_cast<float *>(ws + lay.vectors[buf]),
+                                                flags, (int)p.T, (int)p.H, c0, n, (int)chains, counters + segment, status);
         count_launch();
         return cudaGetLastError();
     };
-    for (int c0 = 0; c0 < nchunks; c0 += (int)seg) {
+    // flags and work counters start at zero
+    e = cudaMemsetAsync(ws, 0, lay.carry, stream);
+    if (e != cudaSuccess) return (int)e;
+
+    if (!overlap) {
+        int segment = 0;
+        for (int c0 = 0; c0 < nchunks; c0 += (int)seg, ++segment) {
+            const int n = (int)((size_t)(nchunks - c0) < seg ? (size_t)(nchunks - c0) : seg);
+            e = launch_operators(0, segment, c0, n);
+            if (e != cudaSuccess) return (int)e;
+            const bool first = c0 == 0, last = c0 + n >= nchunks;
+            e = launch_scan(stream, 0, first ? p.s0 : carry, last ? p.s_out : carry, c0, n, last ? 1 : 0);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return 0;
+    }
+    // Overlapped: operator kernels on the caller's stream, scans on the device's second (high-priority)
+    // stream; events order a scan after its operators, and an operator kernel after the scan that last
+    // read the buffer it is about to overwrite.  The enqueueing is serialised per process: the second
+    // stream and the events are shared by all calls on a device.
+    std::lock_guard<std::mutex> lock(g_streams_mu);
+    DeviceStreams *ds = device_streams(p.device);
+    if (ds == nullptr) return (int)cudaErrorUnknown;
+    e = cudaEventRecord(ds->fork, stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ds->side, ds->fork, 0);
+    if (e != cudaSuccess) return (int)e;
+    int segment = 0;
+    for (int c0 = 0; c0 < nchunks; c0 += (int)seg, ++segment) {
         const int n = (int)((size_t)(nchunks - c0) < seg ? (size_t)(nchunks - c0) : seg);
-        const long long units = (long long)chains * n;
-        const unsigned grid = (unsigned)(units < 2LL * p.num_sms ? units : 2LL * p.num_sms);
-        k1<<<grid, kThreads1, kSmem1, stream>>>(omaps, operators, vectors, flags, (int)p.T, (int)p.H, c0, n, (int)chains,
-                                                status);
-        count_launch();
-        e = cudaGetLastError();
+        const int buf = segment & 1;
+        if (segment >= 2) {
+            e = cudaStreamWaitEvent(stream, ds->scanned[buf], 0);
+            if (e != cudaSuccess) return (int)e;
+        }
+        e = launch_operators(buf, segment, c0, n);
+        if (e == cudaSuccess) e = cudaEventRecord(ds->built[buf], stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ds->side, ds->built[buf], 0);
         if (e != cudaSuccess) return (int)e;
         const bool first = c0 == 0, last = c0 + n >= nchunks;
-        const float *s_in = first ? p.s0 : carry;
-        float *s_out = last ? p.s_out : carry;
-        // (the operator of (chain, chunk) sits at index chain * n + chunk - c0 in both kernels)
-        if (many) e = launch_scan(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes, s_in, s_out, c0, n, last ? 1 : 0);
-        else e = launch_scan(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes, s_in, s_out, c0, n, last ? 1 : 0);
+        e = launch_scan(ds->side, buf, first ? p.s0 : carry, last ? p.s_out : carry, c0, n, last ? 1 : 0);
+        if (e == cudaSuccess) e = cudaEventRecord(ds->scanned[buf], ds->side);
         if (e != cudaSuccess) return (int)e;
     }
-    return 0;
+    // join: the caller's stream continues after the last scan (scans run in order on their stream)
+    e = cudaStreamWaitEvent(stream, ds->scanned[(segment - 1) & 1], 0);
+    return (int)e;
 }
 
 }  // namespace rwkv7

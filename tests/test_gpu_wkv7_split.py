@@ -144,7 +144,7 @@ def test_split_in_segments_is_bitwise_the_single_pass(pkg, workloads, cuda, alia
     finally:
         pkg.set_wkv7_path(pkg.WKV7_AUTO)
     chains = B * H
-    least = 256 + chains * 64 * 64 * 4 + chains * (512 + 32768)   # flags, carried state, one chunk of operators
+    least = 256 + 4096 + chains * 64 * 64 * 4 + chains * (512 + 32768)   # flags, work counters, carried state, one chunk of operators
     assert least < full
     y1, s1 = _statepass(pkg, cuda, inp, pkg.WKV7_SPLIT)
     for nbytes in (least, least + 3 * chains * (512 + 32768) + 100):   # segments of 1 and of 4 chunks
@@ -198,3 +198,33 @@ def test_split_shard_equals_single(pkg, workloads, cuda):
                                         reference_contract=False)
         torch.cuda.synchronize()
         assert torch.equal(out.output, full.output[bs, :, hs]) and torch.equal(out.next_state, full.next_state[bs, hs])
+
+
+@pytest.mark.parametrize("alias", [False, True])
+def test_split_overlapped_scan_is_bitwise_the_serial_one(pkg, oracle, workloads, cuda, alias):
+    """Few chains and a long sequence: the call is cut into segments, and the scan of a segment runs on the
+    library's second stream beside the operator kernel of the next one.  Same kernels on the same data: the
+    result must be bitwise that of the single-stream schedule, and both must match the oracle."""
+    B, T, H = 1, 16384, 3
+    inp = workloads.wkv7_inputs(B, T, H, 64, seed=81, dtype=torch.bfloat16, state="normal")
+    y_ref, s_ref = _oracle(oracle, inp)
+    before = pkg.kernel_launch_count()
+    y1, s1 = _statepass(pkg, cuda, inp, pkg.WKV7_SPLIT, alias=alias)
+    assert pkg.kernel_launch_count() - before == 2 * 8 + 2      # 256 chunks in eight segments, then the two flagged-chain kernels
+    try:
+        pkg.set_wkv7_overlap(False)
+        before = pkg.kernel_launch_count()
+        y2, s2 = _statepass(pkg, cuda, inp, pkg.WKV7_SPLIT, alias=alias)
+        assert pkg.kernel_launch_count() - before == 2 + 2      # one segment
+    finally:
+        pkg.set_wkv7_overlap(True)
+    assert np.array_equal(y1, y2) and np.array_equal(s1, s2)
+    parity.assert_close_bf16_store(y1, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s1, s_ref, 1e-3, "state")
+    # back-to-back calls on the same buffers reuse the second stream and its events
+    gpu = {k: v.to(cuda) for k, v in inp.items()}
+    seq = pkg.Wkv7PretrainForwardInputs(*[gpu[n] for n in "rwkvab"])
+    outs = [pkg.wkv7_statepass_custom(gpu["s0"], seq, reference_contract=False) for _ in range(4)]
+    torch.cuda.synchronize()
+    for o in outs:
+        assert np.array_equal(o.next_state.cpu().numpy(), s1)
