@@ -717,7 +717,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         const int i0 = hf * 32;                       // this thread's 32 value channels
         // The V tile arrives as bf16 and the tensor core wants both operands of a product in one format:
         // the 256 compute threads turn it into fp16 in place (element by element, the layout is untouched),
-        // 32 bytes each, one chunk ahead of the product that reads it.
+        // 32 bytes each, one chunk ahead of the product that reads it.  (Left to the output warps alone the
+        // conversion made them the slowest stage: 264 against 236 us on 32 chains x 128 chunks.)
         auto convert_v = [&](int c) -> bool {
             const int s = c % NS;
             if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
@@ -757,14 +758,18 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 mbar_arrive(bar_zready);
             };
             put_tile();
-            float2 gg = n > 0 ? make_float2(vecs[jp], vecs[64 + jp]) : make_float2(1.f, 0.f);
+            // this row's two decay factors per chunk, fetched two chunks ahead of their use
+            auto load_gg = [&](int c) {
+                return c < n ? make_float2(__ldg(vecs + (size_t)c * kVecFloats + jp), __ldg(vecs + (size_t)c * kVecFloats + 64 + jp))
+                             : make_float2(1.f, 0.f);
+            };
+            float2 gg = load_gg(0), gg_next = load_gg(1);
             if (n > 0 && !convert_v(0)) atomicOr(abort_flag, 1);
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
-                // (the tensor core is busy with this chunk's state product: time for the next V tile)
+                const float2 gg_after = load_gg(c + 2);
+                // (the tensor core is busy with this chunk's state product: time for half of the next V tile)
                 if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
-                float2 gg_next = gg;
-                if (c + 1 < n) gg_next = make_float2(vecs[(size_t)(c + 1) * kVecFloats + jp], vecs[(size_t)(c + 1) * kVecFloats + 64 + jp]);
                 // (polled without suspending: this wait is on the serial path of the chain)
                 if (!mbar_wait_spin(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
                 tc_fence_after();
@@ -777,6 +782,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 for (int e = 0; e < 32; ++e) Z[e] = fmaf(gg.y, __uint_as_float(v[e]), gg.x * Z[e]);
                 if (c + 1 < n) put_tile();
                 gg = gg_next;
+                gg_next = gg_after;
             }
             // A non-finite operator (fp16 overflow upstream) shows in the state for good: flag the chain.
             bool bad = false;
