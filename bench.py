@@ -563,7 +563,7 @@ def main():
         Lf, Cf, Hf, Ff, Vf, Bf, Tf = (2, 512, 8, 2048, 4096, 2, 1024) if args.small else (24, 2048, 32, 8192, 65536, 16, 8192)
         Bl = max(Bf // world, 1)
         with torch.no_grad():
-            cells = [cf.random_cell(i, Cf, Hf, Ff, device=dev, seed=9) for i in range(Lf)]
+            cells = [cf.random_cell(i, Cf, Hf, Ff, device=dev, seed=9, num_cells=Lf) for i in range(Lf)]
             gf = torch.Generator(device=dev)
             gf.manual_seed(99 + rank)
             emb = (torch.randn((Vf, Cf), generator=gf, device=dev) * 0.02).to(torch.bfloat16)

@@ -57,9 +57,25 @@ class CellWeights:
     cm_value_weight: torch.Tensor  # [C,F]
 
 
-def random_cell(cell_id: int, C: int, H: int, Fdim: int, *, device, seed: int = 0, std: float = 0.02) -> CellWeights:
+def decay_speed_bias(num_cells: int, C: int, head_size: int, cell_id: int) -> torch.Tensor:
+    """The reference's initial bias of the weight-decay LoRA (``calculate_decay_speed``,
+    ``functions/init_weights.rs:54-75``, applied in ``layers/lora.rs:73-84``): per channel
+    ``-6 + 6 (n/(C-1))^(1 + layer_ratio^0.3) + 0.5 + 2.5 z|z|`` with ``z`` running from -1 to 1 inside every head.
+    It spreads the per-token decay ``exp(-exp(-softplus(-bias) - 0.5))`` from 0.998 (first channels) to the
+    strongest value the model allows, 0.55 (last channels of the later heads)."""
+    layer_ratio = cell_id / (num_cells - 1) if num_cells > 1 else 0.0
+    n = torch.arange(C, dtype=torch.float64)
+    base = -6.0 + 6.0 * (n / max(C - 1, 1)) ** (1.0 + layer_ratio ** 0.3)
+    half = (head_size - 1.0) / 2.0
+    z = ((n % head_size) - half) / max(half, 1.0)
+    return (base + 0.5 + 2.5 * z * z.abs()).to(torch.float32)
+
+
+def random_cell(cell_id: int, C: int, H: int, Fdim: int, *, device, seed: int = 0, std: float = 0.02,
+                num_cells: int = 1) -> CellWeights:
     """bf16 weights ``N(0, std)``; norm scales 1, biases 0; the two key parameters at their
-    initial values 0.71 / 1.02 (``weight_prepare.rs:200-201``)."""
+    initial values 0.71 / 1.02 (``weight_prepare.rs:200-201``); the weight-decay LoRA's bias at the
+    reference's initial decay speeds (:func:`decay_speed_bias`)."""
     g = torch.Generator(device=device)
     g.manual_seed(7 * 1000003 + 131 * seed + cell_id)
     bf = torch.bfloat16
@@ -77,7 +93,8 @@ def random_cell(cell_id: int, C: int, H: int, Fdim: int, *, device, seed: int = 
         ln1=(ones.clone(), zeros.clone()), ln2=(ones.clone(), zeros.clone()),
         mix6_scales=[torch.rand((1, 1, C), generator=g, device=device, dtype=torch.float32).to(bf) for _ in range(6)],
         w_receptance=mat(C, C), w_key=mat(C, C), w_value=mat(C, C), w_output=mat(C, C),
-        lora_weight_decay=lora(LORA_RANKS["weight_decay"]), lora_learning_rate=lora(LORA_RANKS["learning_rate"]),
+        lora_weight_decay=lora(LORA_RANKS["weight_decay"])[:2] + (decay_speed_bias(num_cells, C, N, cell_id).to(device).to(bf),),
+        lora_learning_rate=lora(LORA_RANKS["learning_rate"]),
         lora_value_residual=lora(LORA_RANKS["value_residual"]) if cell_id > 0 else None,
         lora_gate=lora(LORA_RANKS["gate"], bias=False),
         key_removal=torch.full((1, 1, C), 0.71, device=device, dtype=bf),

@@ -278,7 +278,21 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             }
         }
         fence_proxy_async();
-        __syncthreads();
+        // A chain that is flagged (by this chunk's decay just now, or by an earlier chunk) is recomputed by
+        // the next kernel in line whatever happens here: skip the rest of its chunks.  (Another CTA may set
+        // the flag at any moment: the barrier makes one decision of what the threads read.)
+        if (__syncthreads_or(*reinterpret_cast<volatile int *>(&flags[chain]) != 0)) {
+            if (tid == 0) {
+                const long long next = work_counter ? (long long)atomicAdd(work_counter, 1) : unit + gridDim.x;
+                *next_slot = next < units ? (int)next : 0x7fffffff;
+                if (next < units && !*abort_flag) {
+                    issue_tma(next);
+                    tma_pending = true;
+                }
+            }
+            __syncthreads();
+            continue;
+        }
         // ---------------- G = [At;Rt] [Bh;Kh]^T   (128 x 128, contraction over the 64 channels)
         if (tid == 0) {
             tc_fence_after();
@@ -658,9 +672,17 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     }
     if (warp == 0) tmem_alloc(tmem_slot, 128);
     tc_fence_before();
-    __syncthreads();
+    // A chain that is already flagged (by the operator kernel, or by the scan of an earlier segment) is
+    // recomputed by the next kernel in line: nothing to do here.
+    const bool skip_chain = __syncthreads_or(*reinterpret_cast<volatile int *>(&flags[chain]) != 0) != 0;
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    if (skip_chain) {
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 0) tmem_dealloc(tmem, 128);
+        return;
+    }
     const uint32_t sb = smem_u32(smem);
     const unsigned char *ops = operators + ((size_t)chain * seg_chunks) * kOperatorBytes;
     const float *vecs = vectors + ((size_t)chain * seg_chunks) * kVecFloats;
