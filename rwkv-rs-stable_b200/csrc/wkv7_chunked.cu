@@ -226,7 +226,10 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     }
     if constexpr (K == 1 && !SAVE) {
         // Second in line after the two-kernel prefill: only the chains that one left flagged are computed.
-        if (only_flagged && flags[chain0 + blockIdx.x] == 0) return;
+        if (only_flagged) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // (may have been launched before the flags' writer finished)
+            if (flags[chain0 + blockIdx.x] == 0) return;
+        }
     }
     unsigned char *raw = smem + kOffRaw, *tAR = smem + kOffAR, *tBK = smem + kOffBK, *tZT = smem + kOffZT,
                   *tS = smem + kOffS, *tVT = smem + kOffVT, *tAKRK = smem + kOffAKRK, *tXU = smem + kOffXU;
@@ -1142,6 +1145,11 @@ static int launch_chunked_impl(const Wkv7Args &p, void *workspace, float *snapsh
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = k > 1 ? 1 : 0;
+        if (only_flagged) {   // behind the scan on the same stream: its launch may overlap the scan's tail
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.numAttrs = 1;
+        }
         err = cudaLaunchKernelEx(&cfg, kern, maps, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, flags,
                                  (int)p.T, (int)p.H, status, snapshots,
                                  reinterpret_cast<__nv_bfloat16 *>(state_replacement), (int)first,

@@ -92,7 +92,12 @@ wkv7_seq64_kernel(SeqPtrs ptrs, const float *s0, T *__restrict__ y,
 
     const int bh = blockIdx.x / SPLITS;
     // Fallback mode: only the chains another kernel flagged are (re)computed.
-    if (flags != nullptr && flags[bh] == 0) return;
+    if (flags != nullptr) {
+        // (launched right behind the kernel that writes the flags, possibly before it has finished:
+        // wait for its memory; a no-op for an ordinary launch)
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (flags[bh] == 0) return;
+    }
     const int split = blockIdx.x % SPLITS;
     const int bi = bh / H, h = bh % H;
     const int row0 = split * ROWS;
@@ -308,6 +313,24 @@ int launch_seq64(const Wkv7Args &p, cudaStream_t stream, const int *flags = null
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const unsigned grid = (unsigned)(p.B * p.H * (kN / ROWS));
+    if (flags != nullptr) {
+        // The flagged-chain pass follows the kernel that wrote the flags on the same stream: programmatic
+        // dependent launch lets its launch overlap that kernel's tail (the kernel itself waits for the flags).
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(ROWS * 4);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, kern, ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out, (int)p.T, (int)p.H, flags,
+                               SavePtrs{});
+        if (e == cudaSuccess) count_launch();
+        return (int)e;
+    }
     kern<<<grid, ROWS * 4, smem, stream>>>(ptrs, p.s0, reinterpret_cast<T *>(p.y), p.s_out,
                                            (int)p.T, (int)p.H, flags, SavePtrs{});
     count_launch();

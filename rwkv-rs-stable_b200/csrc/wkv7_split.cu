@@ -501,6 +501,9 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             if (next < units && !*abort_flag) {
                 issue_tma(next);
                 tma_pending = true;
+            } else {
+                // this CTA is on its last chunk: the kernel launched behind this one may be set up now
+                asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             }
         }
         {
@@ -639,6 +642,9 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         return;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // (launched behind the operator kernel with programmatic stream serialization: this kernel may start while
+    // that one is still finishing; everything below reads what it wrote)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + SM::kBars);   // [NS] stage landed (bytes)
     uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (256 arrivals)
     uint64_t *bar_empty = bar_vready + NS;     // [NS] the stage's MMAs are done
@@ -1105,11 +1111,20 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
         auto go = [&](auto kern, size_t smem_bytes) -> cudaError_t {
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
             if (err != cudaSuccess) return err;
-            kern<<<(unsigned)chains, kThreads2, smem_bytes, st>>>(smaps, ops, vecs, s_in, s_out,
-                                                                  reinterpret_cast<__nv_bfloat16 *>(p.y), flags, (int)p.T,
-                                                                  (int)p.H, c0, n, n, check, status);
-            count_launch();
-            return cudaGetLastError();
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)chains);
+            cfg.blockDim = dim3(kThreads2);
+            cfg.dynamicSmemBytes = smem_bytes;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = st == stream ? 1 : 0;   // directly behind its operator kernel on the caller's stream
+            err = cudaLaunchKernelEx(&cfg, kern, smaps, ops, vecs, s_in, s_out, reinterpret_cast<__nv_bfloat16 *>(p.y), flags,
+                                     (int)p.T, (int)p.H, c0, n, n, check, status);
+            if (err == cudaSuccess) count_launch();
+            return err;
         };
         return small_scan ? go(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes) : go(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes);
     };
