@@ -14,6 +14,7 @@
 #define RWKV7_B200_HPP_
 
 #include <array>
+#include <vector>
 #include <cstdint>
 #include <initializer_list>
 #include <stdexcept>
@@ -121,6 +122,36 @@ inline void wkv7_statepass_custom(const Wkv7StatepassForwardInputs &in, Wkv7Stat
                                             s.replacement_key.c(), s.value.c(), s.removal_key_normalized.c(),
                                             s.replacement.c(), s.chunk_len, out.output.m(), out.next_state.m(),
                                             ws.data, ws.bytes, stream));
+}
+
+// Statepass over tensors in pinned HOST memory (views with device = RWKV7_HOST): rwkv7_wkv7_statepass_host.
+// `staging` is device memory of wkv7_host_staging_bytes(...) bytes, `streams` the caller's worker streams;
+// with join = false the caller issues several passes back to back and calls wkv7_host_join once.
+struct Wkv7HostPipeline {
+    int32_t device = 0, slices = 1;
+    Workspace staging;
+    std::vector<rwkv7_stream> streams;
+};
+inline size_t wkv7_host_staging_bytes(const Wkv7PretrainForwardInputs &in, int32_t slices, int32_t n_streams) {
+    const rwkv7_tensor &r = in.receptance.t;
+    return r.ndim == 4 ? rwkv7_wkv7_host_staging_bytes(r.shape[0], r.shape[1], r.shape[2], r.shape[3], r.dtype, slices,
+                                                       n_streams)
+                       : 0;
+}
+inline void wkv7_statepass_host(const Wkv7StatepassForwardInputs &in, Wkv7StatepassForwardOutput &out,
+                                const Wkv7HostPipeline &pipe, rwkv7_stream caller_stream = nullptr, bool join = true,
+                                bool reference_contract = true) {
+    in.sequence.check(reference_contract);
+    const auto &s = in.sequence;
+    const rwkv7_tensor *six[6] = {s.receptance.c(), s.weight_decay.c(), s.replacement_key.c(),
+                                  s.value.c(), s.removal_key_normalized.c(), s.replacement.c()};
+    check_status(rwkv7_wkv7_statepass_host(in.initial_state.c(), six, s.chunk_len, out.output.m(), out.next_state.m(),
+                                           pipe.device, pipe.slices, pipe.staging.data, pipe.staging.bytes,
+                                           pipe.streams.data(), (int32_t)pipe.streams.size(), caller_stream,
+                                           join ? 0 : RWKV7_HOST_NO_JOIN));
+}
+inline void wkv7_host_join(const Wkv7HostPipeline &pipe, rwkv7_stream caller_stream = nullptr) {
+    check_status(rwkv7_wkv7_host_join(pipe.device, pipe.streams.data(), (int32_t)pipe.streams.size(), caller_stream));
 }
 
 // ---- training: the tensors the autodiff nodes keep, and the backward pass ---------------------
