@@ -607,20 +607,23 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
 // ------------------------------------------------------------------------------------------
 // Kernel 2: the scan.  One CTA per chain.  Warps 0-7 own the 128 TMEM lanes twice over (two
 // column halves): lanes 0-63 are the state rows j' (fp32 state Z[j'][i] = S[i][j'] in registers),
-// lanes 64-127 the output tokens t.  Warp 8 streams operators and V tiles into a ring of stages,
-// warp 9 issues the MMAs.  Per chunk D[(j' | t)][i] = sum_k O[k][(j' | t)] [Z ; V][k][i]: the V half
-// is issued as soon as a stage has landed, only the Z half waits for the previous chunk.
+// lanes 64-127 the output tokens t.  Warp 8 streams operators, V tiles and the decay vectors into a
+// ring of stages, warp 9 issues the MMAs, warp 10 turns each V tile into fp16 as it lands.  Per chunk
+// D[(j' | t)][i] = sum_k O[k][(j' | t)] [Z ; V][k][i]: the V half is issued as soon as a stage is
+// ready, only the Z half waits for the previous chunk.
 // ------------------------------------------------------------------------------------------
 constexpr int kComputeWarps = 8;
-constexpr int kThreads2 = (kComputeWarps + 2) * 32;
+constexpr int kThreads2 = (kComputeWarps + 3) * 32;
 constexpr uint32_t kStageBytes = kOperatorBytes + kPanel;   // operator + V tile
+constexpr uint32_t kVecBytes = kVecFloats * 4;              // the chunk's two decay vectors
 
 template <int NS>
 struct ScanSmem {
     static constexpr uint32_t kStages = 0;
     static constexpr uint32_t kZ = NS * kStageBytes;       // fp16 state tile Z[j][i]
     static constexpr uint32_t kY = kZ + kPanel;            // two bf16 output tiles [t][i] (128-byte swizzle) on their way out
-    static constexpr uint32_t kBars = kY + 2 * kPanel;
+    static constexpr uint32_t kVecs = kY + 2 * kPanel;     // per stage: e^{c_L}[64], e^{c_L - m}[64]
+    static constexpr uint32_t kBars = kVecs + NS * kVecBytes;
     static constexpr uint32_t kBytes = kBars + 512 + 1024;   // + alignment slack
 };
 
@@ -646,7 +649,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     // that one is still finishing; everything below reads what it wrote)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + SM::kBars);   // [NS] stage landed (bytes)
-    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (256 arrivals)
+    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (32 arrivals)
     uint64_t *bar_empty = bar_vready + NS;     // [NS] the stage's MMAs are done
     uint64_t *bar_accfull = bar_empty + NS;    // [2] accumulator complete
     uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (256 arrivals)
@@ -662,7 +665,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(bar_full + s, 1);
-            mbar_init(bar_vready + s, 256);
+            mbar_init(bar_vready + s, 32);
             mbar_init(bar_empty + s, 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -702,10 +705,14 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (c >= NS && !mbar_wait(bar_empty + s, (uint32_t)((c / NS - 1) & 1))) { atomicOr(abort_flag, 1); break; }
                 if (*reinterpret_cast<volatile int *>(abort_flag)) break;
                 if (!RWKV7_IN_RANGE(c < seg_chunks && (chunk0 + c) * kL < Tlen, status)) break;
-                mbar_expect_tx(bar_full + s, kStageBytes);
+                mbar_expect_tx(bar_full + s, kStageBytes + kVecBytes);
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(sb + SM::kStages + s * kStageBytes), "l"(ops + (size_t)c * kOperatorBytes),
                                "r"(kOperatorBytes), "r"(smem_u32(bar_full + s))
+                             : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(sb + SM::kVecs + s * kVecBytes), "l"(vecs + (size_t)c * kVecFloats),
+                               "r"(kVecBytes), "r"(smem_u32(bar_full + s))
                              : "memory");
                 tma_load_2d(smem + SM::kStages + s * kStageBytes + kOperatorBytes, &maps.v, h * kN,
                             bi * Tlen + (chunk0 + c) * kL, bar_full + s);
@@ -739,33 +746,34 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 umma_commit(bar_empty + s);
             }
         }
-    } else {
-        const int quarter = warp & 3, hf = warp >> 2;
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const int i0 = hf * 32;                       // this thread's 32 value channels
-        // The V tile arrives as bf16 and the tensor core wants both operands of a product in one format:
-        // the 256 compute threads turn it into fp16 in place (element by element, the layout is untouched),
-        // 32 bytes each, one chunk ahead of the product that reads it.  (Left to the output warps alone the
-        // conversion made them the slowest stage: 264 against 236 us on 32 chains x 128 chunks.)
-        auto convert_v = [&](int c) -> bool {
+    } else if (warp == kComputeWarps + 2) {
+        // ---------------- V converter.  The V tile arrives as bf16 and the tensor core wants both operands
+        // of a product in one format: this warp turns it into fp16 in place (element by element, the layout
+        // is untouched) as soon as the stage has landed, well ahead of the product that reads it.  (Done by
+        // the compute warps between their other work, the conversion sat on the chain's serial path.)
+        for (int c = 0; c < n; ++c) {
             const int s = c % NS;
-            if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
-            uint4 *p = reinterpret_cast<uint4 *>(smem + SM::kStages + s * kStageBytes + kOperatorBytes + tid * 32);
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint4 x = p[q];
+            if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) { atomicOr(abort_flag, 1); break; }
+            if (*reinterpret_cast<volatile int *>(abort_flag)) break;
+            uint4 *p = reinterpret_cast<uint4 *>(smem + SM::kStages + s * kStageBytes + kOperatorBytes);
+#pragma unroll 4
+            for (int q = 0; q < (int)(kPanel / 16 / 32); ++q) {
+                uint4 x = p[q * 32 + lane];
                 uint32_t *xs = &x.x;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const float2 f = unpack_bf2(xs[e]);
                     xs[e] = pack_h2(f.x, f.y);
                 }
-                p[q] = x;
+                p[q * 32 + lane] = x;
             }
             fence_proxy_async();
             mbar_arrive(bar_vready + s);
-            return true;
-        };
+        }
+    } else {
+        const int quarter = warp & 3, hf = warp >> 2;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int i0 = hf * 32;                       // this thread's 32 value channels
         if (quarter < 2) {
             // ---------------- state rows j'
             const int jp = quarter * 32 + lane;
@@ -786,18 +794,21 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 mbar_arrive(bar_zready);
             };
             put_tile();
-            // this row's two decay factors per chunk, fetched two chunks ahead of their use
-            auto load_gg = [&](int c) {
-                return c < n ? make_float2(__ldg(vecs + (size_t)c * kVecFloats + jp), __ldg(vecs + (size_t)c * kVecFloats + 64 + jp))
-                             : make_float2(1.f, 0.f);
+            // this row's two decay factors per chunk come with the stage; they are read one chunk ahead (the
+            // stage of chunk c + 1 cannot be refilled before this thread has handed over that chunk's state)
+            const float *ring = reinterpret_cast<const float *>(smem + SM::kVecs);
+            auto load_gg = [&](int c, float2 &out) -> bool {
+                if (c >= n) { out = make_float2(1.f, 0.f); return true; }
+                const int s = c % NS;
+                if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+                out = make_float2(ring[s * kVecFloats + jp], ring[s * kVecFloats + 64 + jp]);
+                return true;
             };
-            float2 gg = load_gg(0), gg_next = load_gg(1);
-            if (n > 0 && !convert_v(0)) atomicOr(abort_flag, 1);
+            float2 gg, gg_next = make_float2(1.f, 0.f);
+            if (!load_gg(0, gg)) atomicOr(abort_flag, 1);
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
-                const float2 gg_after = load_gg(c + 2);
-                // (the tensor core is busy with this chunk's state product: time for half of the next V tile)
-                if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
+                if (!load_gg(c + 1, gg_next)) { atomicOr(abort_flag, 1); break; }
                 // (polled without suspending: this wait is on the serial path of the chain)
                 if (!mbar_wait_spin(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
                 tc_fence_after();
@@ -810,7 +821,6 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 for (int e = 0; e < 32; ++e) Z[e] = fmaf(gg.y, __uint_as_float(v[e]), gg.x * Z[e]);
                 if (c + 1 < n) put_tile();
                 gg = gg_next;
-                gg_next = gg_after;
             }
             // A non-finite operator (fp16 overflow upstream) shows in the state for good: flag the chain.
             bool bad = false;
@@ -833,10 +843,9 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             bool ybad = false;   // a non-finite output: the chain is flagged for recomputation
             // After an expired wait this thread stops waiting but still walks the loop, so that the four
             // warps keep meeting at the named barrier below (the call then reports a time-out).
-            bool dead = n > 0 && !convert_v(0);
+            bool dead = false;
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
-                if (!dead && c + 1 < n && !convert_v(c + 1)) dead = true;
                 if (!dead && !mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) dead = true;
                 tc_fence_after();
                 uint32_t v[32];
