@@ -120,17 +120,22 @@ static_assert(kWm + 32 * 20 * 4 <= kT16, "inverse scratch runs into the fp16 til
 static_assert(kW2 + kPanel / 2 <= kRaw + kRawBytes, "scratch exceeds the raw-tile region");
 static_assert(kStage + kOperatorBytes == kBK, "operator staging must cover AR, A_rb, A_rk exactly");
 static_assert(2 * (kSmem1 + 1024) <= 232448, "two CTAs per SM");
+constexpr uint32_t kSmem1F32 = kSmem1 + kRawBytes;   // fp32 tensors: raw tiles of 16 KB, one CTA per SM
+static_assert(kSmem1F32 + 1024 <= 232448, "the fp32 variant must fit an SM");
 
 struct OperatorMaps {
-    CUtensorMap m[5];   // r, w, k, a, b as [B*T, H*N] bf16, box 64 x 64, no swizzle
+    CUtensorMap m[5];   // r, w, k, a, b as [B*T, H*N] (bf16 or fp32), box 64 x 64, no swizzle
 };
 enum { XR = 0, XW = 1, XK = 2, XA = 3, XB = 4 };
 
+template <typename TIn>
 __global__ void __launch_bounds__(kThreads1, 2)
 wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned char *__restrict__ operators,
                            float *__restrict__ vectors, int *__restrict__ flags, int Tlen, int H, int chunk0,
                            int seg_chunks, int nchains, int *work_counter, int *status) {
     extern __shared__ __align__(1024) unsigned char smem[];
+    // fp32 tensors: the five raw tiles are twice as large, everything behind them moves up by X
+    constexpr uint32_t kRawTile = kL * kN * sizeof(TIn), kRawBytesT = 5 * kRawTile, X = kRawBytesT - kRawBytes;
     if (smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
         return;
@@ -142,13 +147,13 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
     float *Am = reinterpret_cast<float *>(smem + kAm);
     float *Tm = reinterpret_cast<float *>(smem + kTm);
     float *Wm = reinterpret_cast<float *>(smem + kWm);
-    uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + kMisc1);
+    uint64_t *bar_tma = reinterpret_cast<uint64_t *>(smem + (kMisc1 + X));
     uint64_t *bar_mma = bar_tma + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kMisc1 + 32);
-    int *abort_flag = reinterpret_cast<int *>(smem + kMisc1 + 48);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (kMisc1 + X) + 32);
+    int *abort_flag = reinterpret_cast<int *>(smem + (kMisc1 + X) + 48);
     int *next_slot = abort_flag + 1;   // the chunk this CTA works on next (thread 0 draws it, all read it)
-    float *grp = reinterpret_cast<float *>(smem + kMisc1 + 256);     // [8][64]
-    float *emv = reinterpret_cast<float *>(smem + kMisc1 + 256 + 2048);   // e^{m_j} / kOpScale [64]
+    float *grp = reinterpret_cast<float *>(smem + (kMisc1 + X) + 256);     // [8][64]
+    float *emv = reinterpret_cast<float *>(smem + (kMisc1 + X) + 256 + 2048);   // e^{m_j} / kOpScale [64]
 
     if (tid == 0) {
         mbar_init(bar_tma, 1);
@@ -170,7 +175,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             uint32_t *w = &z.x;
             w[(r & 7) >> 1] = one;
         }
-        *reinterpret_cast<uint4 *>(smem + kI64 + r * 128 + ((ch ^ (r & 7)) << 4)) = z;
+        *reinterpret_cast<uint4 *>(smem + (kI64 + X) + r * 128 + ((ch ^ (r & 7)) << 4)) = z;
     }
     if (warp == 0) tmem_alloc(tmem_slot, 128);
     tc_fence_before();
@@ -185,10 +190,10 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         const int chain = (int)(unit / seg_chunks), chunk = chunk0 + (int)(unit % seg_chunks);
         const int bi = chain / H, h = chain % H;
         if (!RWKV7_IN_RANGE(chain < nchains && chunk * kL < Tlen, status)) return;   // (the wait then expires)
-        mbar_expect_tx(bar_tma, kRawBytes);
+        mbar_expect_tx(bar_tma, kRawBytesT);
         const int trow = bi * Tlen + chunk * kL;
 #pragma unroll
-        for (int i = 0; i < 5; ++i) tma_load_2d(raw + i * kPanel, &maps.m[i], h * kN, trow, bar_tma);
+        for (int i = 0; i < 5; ++i) tma_load_2d(raw + i * kRawTile, &maps.m[i], h * kN, trow, bar_tma);
     };
     long long unit = *next_slot;
     if (tid == 0 && unit < units) issue_tma(unit);
@@ -207,17 +212,24 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             for (int idx = tid; idx < (kL - valid) * kN; idx += kThreads1) {
                 const int t = valid + idx / kN, jj = idx % kN;
 #pragma unroll
-                for (int x = 0; x < 5; ++x)
-                    *reinterpret_cast<unsigned short *>(raw + x * kPanel + (t * kN + jj) * 2) =
-                        (x == XW) ? (unsigned short)0xFF80 : (unsigned short)0;
+                for (int x = 0; x < 5; ++x) {
+                    if constexpr (sizeof(TIn) == 2)
+                        *reinterpret_cast<unsigned short *>(raw + x * kRawTile + (t * kN + jj) * 2) =
+                            (x == XW) ? (unsigned short)0xFF80 : (unsigned short)0;
+                    else
+                        *reinterpret_cast<uint32_t *>(raw + x * kRawTile + (t * kN + jj) * 4) = (x == XW) ? 0xFF800000u : 0u;
+                }
             }
             __syncthreads();
         }
         // ---------------- phase A: decay prefix sums, scaled fp16 operands
         const int j2 = lane, tg = warp;            // channel pair (2 j2, 2 j2 + 1), tokens 8 tg .. 8 tg + 7
-        const unsigned char *rp = raw + (tg * 8 * kN + 2 * j2) * 2;
+        const unsigned char *rp = raw + (tg * 8 * kN + 2 * j2) * sizeof(TIn);
         auto ld2 = [&](int tensor, int u) {
-            return unpack_bf2(*reinterpret_cast<const uint32_t *>(rp + tensor * kPanel + u * (kN * 2)));
+            if constexpr (sizeof(TIn) == 2)
+                return unpack_bf2(*reinterpret_cast<const uint32_t *>(rp + tensor * kRawTile + u * (kN * 2)));
+            else
+                return *reinterpret_cast<const float2 *>(rp + tensor * kRawTile + u * (kN * 4));
         };
         float c0[8], c1[8];
         {
@@ -268,11 +280,11 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                 const float2 a2 = ld2(XA, u), r2 = ld2(XR, u), b2 = ld2(XB, u), k2 = ld2(XK, u);
                 const uint32_t o = off16(t, 2 * j2);
                 if (!RWKV7_IN_RANGE(o + 4 <= kPanel, status)) continue;
-                *reinterpret_cast<uint32_t *>(smem + kAR + o) = pack_h2(a2.x * ep0, a2.y * ep1);
-                *reinterpret_cast<uint32_t *>(smem + kAR + kPanel + o) = pack_h2(r2.x * e0, r2.y * e1);
-                *reinterpret_cast<uint32_t *>(smem + kBK + o) = pack_h2(b2.x * i0, b2.y * i1);
-                *reinterpret_cast<uint32_t *>(smem + kBK + kPanel + o) = pack_h2(k2.x * i0, k2.y * i1);
-                *reinterpret_cast<uint32_t *>(smem + kRtrue + o) = pack_h2(r2.x * e0 * rs0, r2.y * e1 * rs1);
+                *reinterpret_cast<uint32_t *>(smem + (kAR + X) + o) = pack_h2(a2.x * ep0, a2.y * ep1);
+                *reinterpret_cast<uint32_t *>(smem + (kAR + X) + kPanel + o) = pack_h2(r2.x * e0, r2.y * e1);
+                *reinterpret_cast<uint32_t *>(smem + (kBK + X) + o) = pack_h2(b2.x * i0, b2.y * i1);
+                *reinterpret_cast<uint32_t *>(smem + (kBK + X) + kPanel + o) = pack_h2(k2.x * i0, k2.y * i1);
+                *reinterpret_cast<uint32_t *>(smem + (kRtrue + X) + o) = pack_h2(r2.x * e0 * rs0, r2.y * e1 * rs1);
                 ep0 = e0;
                 ep1 = e1;
             }
@@ -298,7 +310,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-                umma_f16(tmem, dK(sb + kAR, ks), dK(sb + kBK, ks), idesc16(128, 128, false, false), ks > 0);
+                umma_f16(tmem, dK(sb + (kAR + X), ks), dK(sb + (kBK + X), ks), idesc16(128, 128, false, false), ks > 0);
             umma_commit(bar_mma);
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
@@ -343,7 +355,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                         }
                     }
                 } else {
-                    const uint32_t tile = !rt_rows ? (kAR + kPanel) : (hf == 0 ? kArb : kArk);   // A_ak takes Rt's place
+                    const uint32_t tile = !rt_rows ? ((kAR + X) + kPanel) : (hf == 0 ? (kArb + X) : (kArk + X));   // A_ak takes Rt's place
                     uint32_t v[32];
                     if (!zero_half) {
                         tmem_ld32(tmem + lane_base + hf * 64 + half * 32, v);
@@ -488,7 +500,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-                umma_f16(tmem, dMN(sb + kAR, kPanel, ks), dK(sb + kT16, ks), idesc16(128, 64, true, false), ks > 0);
+                umma_f16(tmem, dMN(sb + (kAR + X), kPanel, ks), dK(sb + kT16, ks), idesc16(128, 64, true, false), ks > 0);
             umma_commit(bar_mma);
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
@@ -517,7 +529,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
 #pragma unroll
                 for (int e2 = 0; e2 < 4; ++e2)
                     w[e2] = pack_h2(__uint_as_float(v[e8 * 8 + 2 * e2]) * scale, __uint_as_float(v[e8 * 8 + 2 * e2 + 1]) * scale);
-                *reinterpret_cast<uint4 *>(smem + kAf + off16(row, hf * 32 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4 *>(smem + (kAf + X) + off16(row, hf * 32 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
         tc_fence_before();
@@ -529,13 +541,13 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)   // columns j': contraction over t with Bh[t][j'] (MN-major B)
-                umma_f16(tmem, dK(sb + kAf, ks), dMN(sb + kBK, kPanel, ks), idesc16(128, 64, false, true), ks > 0);
+                umma_f16(tmem, dK(sb + (kAf + X), ks), dMN(sb + (kBK + X), kPanel, ks), idesc16(128, 64, false, true), ks > 0);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)   // columns t': contraction over t with A_rb[t'][t]
-                umma_f16(tmem + 64, dK(sb + kAf, ks), dK(sb + kArb, ks), idesc16(128, 64, false, false), ks > 0);
+                umma_f16(tmem + 64, dK(sb + (kAf + X), ks), dK(sb + (kArb + X), ks), idesc16(128, 64, false, false), ks > 0);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)   // + R[t'][j] and A_rk[t'][s], through the identity
-                umma_f16(tmem + 64, dMN(sb + kRtrue, kArk - kRtrue, ks), dK(sb + kI64, ks), idesc16(128, 64, true, false), true);
+                umma_f16(tmem + 64, dMN(sb + (kRtrue + X), (kArk + X) - (kRtrue + X), ks), dK(sb + (kI64 + X), ks), idesc16(128, 64, true, false), true);
             umma_commit(bar_mma);
         }
         if (!mbar_wait(bar_mma, mma_phase)) atomicOr(abort_flag, 1);
@@ -553,7 +565,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                 if (kt_rows) {
 #pragma unroll
                     for (int e8 = 0; e8 < 4; ++e8) {
-                        const uint4 q = *reinterpret_cast<const uint4 *>(smem + kBK + kPanel + off16(row - 64, half * 32 + e8 * 8));
+                        const uint4 q = *reinterpret_cast<const uint4 *>(smem + (kBK + X) + kPanel + off16(row - 64, half * 32 + e8 * 8));
                         const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                         for (int e2 = 0; e2 < 4; ++e2) {
@@ -575,7 +587,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
                     // panel hf, row k = this thread's lane, 16-byte chunk of columns n
                     const uint32_t so = hf * (2 * kPanel) + off16(row, half * 32 + e8 * 8);
                     if (RWKV7_IN_RANGE(so + 16 <= kOperatorBytes, status))
-                        *reinterpret_cast<uint4 *>(smem + kStage + so) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4 *>(smem + (kStage + X) + so) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
@@ -584,7 +596,7 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
         __syncthreads();
         if (tid == 0 && RWKV7_IN_RANGE(unit >= 0 && unit < units, status)) {
             asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(operators + (size_t)unit * kOperatorBytes),
-                         "r"(sb + kStage), "r"(kOperatorBytes)
+                         "r"(sb + (kStage + X)), "r"(kOperatorBytes)
                          : "memory");
             bulk_commit_group();
         }
@@ -608,12 +620,19 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
 // Kernel 2: the scan.  One CTA per chain.  Warps 0-7 own the 128 TMEM lanes twice over (two
 // column halves): lanes 0-63 are the state rows j' (fp32 state Z[j'][i] = S[i][j'] in registers),
 // lanes 64-127 the output tokens t.  Warp 8 streams operators, V tiles and the decay vectors into a
-// ring of stages, warp 9 issues the MMAs, warp 10 turns each V tile into fp16 as it lands.  Per chunk
+// ring of stages, warp 9 issues the MMAs, warp 10 (four-stage variant) turns each V tile into fp16 as it
+// lands.  Per chunk
 // D[(j' | t)][i] = sum_k O[k][(j' | t)] [Z ; V][k][i]: the V half is issued as soon as a stage is
 // ready, only the Z half waits for the previous chunk.
 // ------------------------------------------------------------------------------------------
 constexpr int kComputeWarps = 8;
-constexpr int kThreads2 = (kComputeWarps + 3) * 32;
+// The four-stage variant (one CTA per SM) has a warp of its own for the V conversion; in the two-stage variant
+// (two CTAs per SM, or beside an operator CTA) the compute warps do it between their other work, which measured
+// faster there (32 chains x 1024 chunks overlapped with the operator kernel: 1.41 against 1.53 ms).
+template <int NS> struct ScanWarps {
+    static constexpr bool kConvWarp = NS > 2;
+    static constexpr int kThreads = (kComputeWarps + 2 + (kConvWarp ? 1 : 0)) * 32;
+};
 constexpr uint32_t kStageBytes = kOperatorBytes + kPanel;   // operator + V tile
 constexpr uint32_t kVecBytes = kVecFloats * 4;              // the chunk's two decay vectors
 
@@ -633,7 +652,7 @@ struct ScanMaps {
 };
 
 template <int NS>
-__global__ void __launch_bounds__(kThreads2, NS <= 2 ? 2 : 1)
+__global__ void __launch_bounds__(ScanWarps<NS>::kThreads, NS <= 2 ? 2 : 1)
 wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned char *__restrict__ operators,
                        const float *__restrict__ vectors, const float *state_in, float *state_out,
                        __nv_bfloat16 *__restrict__ y, int *flags, int Tlen, int H, int chunk0,
@@ -649,7 +668,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     // that one is still finishing; everything below reads what it wrote)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + SM::kBars);   // [NS] stage landed (bytes)
-    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (32 arrivals)
+    constexpr bool kConvWarp = ScanWarps<NS>::kConvWarp;
+    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (one arrival per converting thread)
     uint64_t *bar_empty = bar_vready + NS;     // [NS] the stage's MMAs are done
     uint64_t *bar_accfull = bar_empty + NS;    // [2] accumulator complete
     uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (256 arrivals)
@@ -665,7 +685,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(bar_full + s, 1);
-            mbar_init(bar_vready + s, 32);
+            mbar_init(bar_vready + s, kConvWarp ? 32 : 256);
             mbar_init(bar_empty + s, 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -746,7 +766,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 umma_commit(bar_empty + s);
             }
         }
-    } else if (warp == kComputeWarps + 2) {
+    } else if (kConvWarp && warp == kComputeWarps + 2) {
         // ---------------- V converter.  The V tile arrives as bf16 and the tensor core wants both operands
         // of a product in one format: this warp turns it into fp16 in place (element by element, the layout
         // is untouched) as soon as the stage has landed, well ahead of the product that reads it.  (Done by
@@ -774,6 +794,28 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         const int quarter = warp & 3, hf = warp >> 2;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int i0 = hf * 32;                       // this thread's 32 value channels
+        // Two-stage variant: the 256 compute threads turn the V tile into fp16 in place, 32 bytes each, one
+        // chunk ahead of the product that reads it.
+        auto convert_v = [&](int c) -> bool {
+            if constexpr (kConvWarp) return true;
+            const int s = c % NS;
+            if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+            uint4 *p = reinterpret_cast<uint4 *>(smem + SM::kStages + s * kStageBytes + kOperatorBytes + tid * 32);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint4 x = p[q];
+                uint32_t *xs = &x.x;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf2(xs[e]);
+                    xs[e] = pack_h2(f.x, f.y);
+                }
+                p[q] = x;
+            }
+            fence_proxy_async();
+            mbar_arrive(bar_vready + s);
+            return true;
+        };
         if (quarter < 2) {
             // ---------------- state rows j'
             const int jp = quarter * 32 + lane;
@@ -800,14 +842,18 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             auto load_gg = [&](int c, float2 &out) -> bool {
                 if (c >= n) { out = make_float2(1.f, 0.f); return true; }
                 const int s = c % NS;
-                if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+                // (in the two-stage variant this thread has just waited for the stage in convert_v)
+                if (kConvWarp && !mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
                 out = make_float2(ring[s * kVecFloats + jp], ring[s * kVecFloats + 64 + jp]);
                 return true;
             };
             float2 gg, gg_next = make_float2(1.f, 0.f);
+            if (n > 0 && !convert_v(0)) atomicOr(abort_flag, 1);
             if (!load_gg(0, gg)) atomicOr(abort_flag, 1);
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
+                // (the tensor core is busy with this chunk's state product: time for the next chunk's vectors and tile)
+                if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
                 if (!load_gg(c + 1, gg_next)) { atomicOr(abort_flag, 1); break; }
                 // (polled without suspending: this wait is on the serial path of the chain)
                 if (!mbar_wait_spin(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
@@ -843,9 +889,10 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             bool ybad = false;   // a non-finite output: the chain is flagged for recomputation
             // After an expired wait this thread stops waiting but still walks the loop, so that the four
             // warps keep meeting at the named barrier below (the call then reports a time-out).
-            bool dead = false;
+            bool dead = n > 0 && !convert_v(0);
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
+                if (!dead && c + 1 < n && !convert_v(c + 1)) dead = true;
                 if (!dead && !mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) dead = true;
                 tc_fence_after();
                 uint32_t v[32];
@@ -1109,7 +1156,7 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     int *status = nullptr;
     if (int e = device_status_ptr(p.device, &status)) return e;
 
-    auto k1 = wkv7_chunk_operator_kernel;
+    auto k1 = wkv7_chunk_operator_kernel<__nv_bfloat16>;
     cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem1);
     if (e != cudaSuccess) return (int)e;
     // Beside an operator CTA only the two-stage scan fits on an SM; it is also the one for more chains than SMs.
@@ -1117,12 +1164,12 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     auto launch_scan = [&](cudaStream_t st, int buf, const float *s_in, float *s_out, int c0, int n, int check) -> cudaError_t {
         const unsigned char *ops = ws + lay.operators[buf];
         const float *vecs = reinterpret_cast<const float *>(ws + lay.vectors[buf]);
-        auto go = [&](auto kern, size_t smem_bytes) -> cudaError_t {
+        auto go = [&](auto kern, size_t smem_bytes, unsigned threads) -> cudaError_t {
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
             if (err != cudaSuccess) return err;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)chains);
-            cfg.blockDim = dim3(kThreads2);
+            cfg.blockDim = dim3(threads);
             cfg.dynamicSmemBytes = smem_bytes;
             cfg.stream = st;
             cudaLaunchAttribute attr[1];
@@ -1135,7 +1182,8 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
             if (err == cudaSuccess) count_launch();
             return err;
         };
-        return small_scan ? go(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes) : go(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes);
+        return small_scan ? go(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes, ScanWarps<2>::kThreads)
+                          : go(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes, ScanWarps<4>::kThreads);
     };
     auto launch_operators = [&](int buf, int segment, int c0, int n) -> cudaError_t {
         const long long units = (long long)chains * n;
