@@ -159,14 +159,16 @@ int wkv7_dispatch(Wkv7Args &p, void *workspace, size_t workspace_bytes, rwkv7_st
     if (path == RWKV7_WKV7_SPLIT && !split_fits) {
         if (!wkv7_split_supported(p))
             return fail(RWKV7_ERR_UNSUPPORTED,
-                        "Unsupported: the two-kernel WKV7 prefill needs N == 64 and BF16 tensors (got N=%lld)", (long long)p.N);
+                        "Unsupported: the two-kernel WKV7 prefill needs N == 64 and 16-byte aligned tensors (got N=%lld)", (long long)p.N);
         return fail(RWKV7_ERR_WORKSPACE_TOO_SMALL, "WorkspaceTooSmall: wkv7 needs %zu workspace bytes, got %zu",
                     wkv7_split_min_workspace_bytes(p.B, p.T, p.H, p.N), workspace == nullptr ? (size_t)0 : workspace_bytes);
     }
     if (path == RWKV7_WKV7_SPLIT || (path == RWKV7_WKV7_AUTO && split_fits && p.T >= kSplitMinTokens)) {
         if (int e = launch_wkv7_split(p, workspace, workspace_bytes, (cudaStream_t)stream))
             return cuda_fail("wkv7 split launch", e);
-        if (int e = launch_wkv7_chunked_flagged(p, workspace, (cudaStream_t)stream))
+        // (the tf32 chunked kernel reads bf16 tiles: flagged chains of fp32 tensors go straight to the sequential scan)
+        if (int e = p.bf16 ? launch_wkv7_chunked_flagged(p, workspace, (cudaStream_t)stream)
+                           : launch_wkv7_sequential_flagged(p, static_cast<const int *>(workspace), (cudaStream_t)stream))
             return cuda_fail("wkv7 flagged-chain launch", e);
         return RWKV7_OK;
     }
@@ -333,7 +335,8 @@ int rwkv7_selftest_bounded_wait(int device, int64_t max_polls, rwkv7_stream stre
 size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype) {
     const int path = g_wkv7_path.load();
     if (path == RWKV7_WKV7_SEQUENTIAL) return 0;
-    if ((path == RWKV7_WKV7_SPLIT || (path == RWKV7_WKV7_AUTO && T >= kSplitMinTokens)) && dtype == RWKV7_BF16 && N == 64)
+    if ((path == RWKV7_WKV7_SPLIT || (path == RWKV7_WKV7_AUTO && T >= kSplitMinTokens)) &&
+        (dtype == RWKV7_BF16 || dtype == RWKV7_F32) && N == 64)
     {
         // (the size depends on whether the scan will overlap the operator kernel, i.e. on the SM count of
         // the device the call will run on: the calling thread's current device is taken)

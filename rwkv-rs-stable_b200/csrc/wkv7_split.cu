@@ -1,4 +1,4 @@
-// Two-kernel WKV7 prefill for sm_100a (N == 64, bf16 tensors, 64-token chunks, fp16 tensor-core
+// Two-kernel WKV7 prefill for sm_100a (N == 64, bf16 or fp32 tensors, 64-token chunks, fp16 tensor-core
 // operands): everything that does not depend on the running state is computed for all chunks in
 // parallel by `wkv7_chunk_operator_kernel`, which folds a chunk into one linear operator, and
 // `wkv7_state_scan_kernel` then walks each (b,h) chain with one dependent tensor-core product per
@@ -39,6 +39,7 @@
 #include <atomic>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "kernels.h"
 #include "sm100_umma.cuh"
@@ -633,31 +634,41 @@ template <int NS> struct ScanWarps {
     static constexpr bool kConvWarp = NS > 2;
     static constexpr int kThreads = (kComputeWarps + 2 + (kConvWarp ? 1 : 0)) * 32;
 };
-constexpr uint32_t kStageBytes = kOperatorBytes + kPanel;   // operator + V tile
 constexpr uint32_t kVecBytes = kVecFloats * 4;              // the chunk's two decay vectors
 
-template <int NS>
+// A stage: the operator, the fp16 V tile the tensor core reads and, for fp32 tensors, the fp32 tile as
+// it lands (bf16 tiles are converted in place).
+template <int NS, typename TIO>
 struct ScanSmem {
+    static constexpr bool kF32 = sizeof(TIO) == 4;
+    static constexpr uint32_t kVLand = kOperatorBytes + (kF32 ? kPanel : 0u);      // where the V tile lands in a stage
+    static constexpr uint32_t kVBytes = kL * kN * sizeof(TIO);
+    static constexpr uint32_t kStage = kOperatorBytes + kPanel + (kF32 ? kVBytes : 0u);
     static constexpr uint32_t kStages = 0;
-    static constexpr uint32_t kZ = NS * kStageBytes;       // fp16 state tile Z[j][i]
-    static constexpr uint32_t kY = kZ + kPanel;            // two bf16 output tiles [t][i] (128-byte swizzle) on their way out
-    static constexpr uint32_t kVecs = kY + 2 * kPanel;     // per stage: e^{c_L}[64], e^{c_L - m}[64]
+    static constexpr uint32_t kZ = NS * kStage;            // fp16 state tile Z[j][i]
+    static constexpr uint32_t kY = kZ + kPanel;            // two output tiles [t][i] on their way out (128-byte swizzle; fp32: two panels of 32 channels each)
+    static constexpr uint32_t kYTile = kL * kN * sizeof(TIO);
+    static constexpr uint32_t kVecs = kY + 2 * kYTile;     // per stage: e^{c_L}[64], e^{c_L - m}[64]
     static constexpr uint32_t kBars = kVecs + NS * kVecBytes;
     static constexpr uint32_t kBytes = kBars + 512 + 1024;   // + alignment slack
 };
+static_assert(ScanSmem<4, __nv_bfloat16>::kBytes <= 232448 && ScanSmem<3, float>::kBytes <= 232448, "scan stages exceed an SM");
 
 struct ScanMaps {
-    CUtensorMap v;   // [B*T, H*N] bf16, box 64 x 64, 128-byte swizzle
-    CUtensorMap y;   // the output, same view and box
+    CUtensorMap v;   // [B*T, H*N]: bf16, box 64 x 64, 128-byte swizzle; fp32, box 64 x 64, no swizzle
+    CUtensorMap y;   // the output, same view: bf16, box 64 x 64; fp32, box 32 channels x 64 tokens; 128-byte swizzle
 };
 
-template <int NS>
+template <int NS, typename TIO>
 __global__ void __launch_bounds__(ScanWarps<NS>::kThreads, NS <= 2 ? 2 : 1)
 wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned char *__restrict__ operators,
                        const float *__restrict__ vectors, const float *state_in, float *state_out,
-                       __nv_bfloat16 *__restrict__ y, int *flags, int Tlen, int H, int chunk0,
+                       TIO *__restrict__ y, int *flags, int Tlen, int H, int chunk0,
                        int seg_chunks, int nseg, int check_flags, int *status) {
-    using SM = ScanSmem<NS>;
+    using SM = ScanSmem<NS, TIO>;
+    constexpr bool kF32 = SM::kF32;
+    constexpr uint32_t kStageBytes = SM::kStage;
+    static_assert(!kF32 || ScanWarps<NS>::kConvWarp, "fp32 tiles need the converter warp");
     extern __shared__ __align__(1024) unsigned char smem[];
     if (smem_u32(smem) & 1023u) {
         if (threadIdx.x == 0) atomicExch(status, (int)kDevInternal);
@@ -725,7 +736,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (c >= NS && !mbar_wait(bar_empty + s, (uint32_t)((c / NS - 1) & 1))) { atomicOr(abort_flag, 1); break; }
                 if (*reinterpret_cast<volatile int *>(abort_flag)) break;
                 if (!RWKV7_IN_RANGE(c < seg_chunks && (chunk0 + c) * kL < Tlen, status)) break;
-                mbar_expect_tx(bar_full + s, kStageBytes + kVecBytes);
+                mbar_expect_tx(bar_full + s, kOperatorBytes + SM::kVBytes + kVecBytes);
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                              ::"r"(sb + SM::kStages + s * kStageBytes), "l"(ops + (size_t)c * kOperatorBytes),
                                "r"(kOperatorBytes), "r"(smem_u32(bar_full + s))
@@ -734,7 +745,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                              ::"r"(sb + SM::kVecs + s * kVecBytes), "l"(vecs + (size_t)c * kVecFloats),
                                "r"(kVecBytes), "r"(smem_u32(bar_full + s))
                              : "memory");
-                tma_load_2d(smem + SM::kStages + s * kStageBytes + kOperatorBytes, &maps.v, h * kN,
+                tma_load_2d(smem + SM::kStages + s * kStageBytes + SM::kVLand, &maps.v, h * kN,
                             bi * Tlen + (chunk0 + c) * kL, bar_full + s);
                 ++issued;
             }
@@ -775,17 +786,31 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             const int s = c % NS;
             if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) { atomicOr(abort_flag, 1); break; }
             if (*reinterpret_cast<volatile int *>(abort_flag)) break;
-            uint4 *p = reinterpret_cast<uint4 *>(smem + SM::kStages + s * kStageBytes + kOperatorBytes);
+            unsigned char *vt = smem + SM::kStages + s * kStageBytes + kOperatorBytes;
+            if constexpr (!kF32) {
+                uint4 *p = reinterpret_cast<uint4 *>(vt);
 #pragma unroll 4
-            for (int q = 0; q < (int)(kPanel / 16 / 32); ++q) {
-                uint4 x = p[q * 32 + lane];
-                uint32_t *xs = &x.x;
+                for (int q = 0; q < (int)(kPanel / 16 / 32); ++q) {
+                    uint4 x = p[q * 32 + lane];
+                    uint32_t *xs = &x.x;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = unpack_bf2(xs[e]);
-                    xs[e] = pack_h2(f.x, f.y);
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 f = unpack_bf2(xs[e]);
+                        xs[e] = pack_h2(f.x, f.y);
+                    }
+                    p[q * 32 + lane] = x;
                 }
-                p[q * 32 + lane] = x;
+            } else {
+                // fp32 tile [t][i] (rows of 256 bytes) -> fp16 panel: eight channels of one token per step
+                const unsigned char *land = smem + SM::kStages + s * kStageBytes + SM::kVLand;
+#pragma unroll 4
+                for (int q = 0; q < kL * kN / 8 / 32; ++q) {
+                    const int idx = q * 32 + lane, t = idx >> 3, cg = idx & 7;
+                    const float4 x0 = *reinterpret_cast<const float4 *>(land + t * (kN * 4) + cg * 32);
+                    const float4 x1 = *reinterpret_cast<const float4 *>(land + t * (kN * 4) + cg * 32 + 16);
+                    *reinterpret_cast<uint4 *>(vt + off16(t, cg * 8)) =
+                        make_uint4(pack_h2(x0.x, x0.y), pack_h2(x0.z, x0.w), pack_h2(x1.x, x1.y), pack_h2(x1.z, x1.w));
+                }
             }
             fence_proxy_async();
             mbar_arrive(bar_vready + s);
@@ -900,34 +925,64 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 tmem_ld_wait();
                 tc_fence_before();
                 mbar_arrive(bar_accfree + a);
-                uint32_t w[16];
-#pragma unroll
-                for (int e2 = 0; e2 < 16; ++e2) {
-                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1]));
-                    w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
-                    ybad |= ((w[e2] & 0x7f80u) == 0x7f80u) || ((w[e2] & 0x7f800000u) == 0x7f800000u);
-                }
                 const int t0 = (chunk0 + c) * kL;
-                if (t0 + kL <= Tlen) {
-                    unsigned char *stage = smem + SM::kY + a * kPanel;
-                    // the store that last read this buffer (two chunks ago) must be done with it
-                    if (elected) bulk_wait_group_read<1>();
-                    asm volatile("bar.sync 2, 128;" ::: "memory");
+                if constexpr (!kF32) {
+                    uint32_t w[16];
 #pragma unroll
-                    for (int e8 = 0; e8 < 4; ++e8)
-                        if (RWKV7_IN_RANGE(off16(tq, i0 + e8 * 8) + 16 <= kPanel, status))
-                            *reinterpret_cast<uint4 *>(stage + off16(tq, i0 + e8 * 8)) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
-                    fence_proxy_async();
-                    asm volatile("bar.sync 2, 128;" ::: "memory");
-                    if (elected) {
-                        tma_store_2d(&maps.y, h * kN, bi * Tlen + t0, stage);
-                        bulk_commit_group();
+                    for (int e2 = 0; e2 < 16; ++e2) {
+                        const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1]));
+                        w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
+                        ybad |= ((w[e2] & 0x7f80u) == 0x7f80u) || ((w[e2] & 0x7f800000u) == 0x7f800000u);
                     }
-                } else if (t0 + tq < Tlen) {
-                    __nv_bfloat16 *dst = y + (((size_t)bi * Tlen + t0 + tq) * H + h) * kN + i0;
+                    if (t0 + kL <= Tlen) {
+                        unsigned char *stage = smem + SM::kY + a * SM::kYTile;
+                        // the store that last read this buffer (two chunks ago) must be done with it
+                        if (elected) bulk_wait_group_read<1>();
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
 #pragma unroll
-                    for (int e8 = 0; e8 < 4; ++e8)
-                        *reinterpret_cast<uint4 *>(dst + e8 * 8) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
+                        for (int e8 = 0; e8 < 4; ++e8)
+                            if (RWKV7_IN_RANGE(off16(tq, i0 + e8 * 8) + 16 <= kPanel, status))
+                                *reinterpret_cast<uint4 *>(stage + off16(tq, i0 + e8 * 8)) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
+                        fence_proxy_async();
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (elected) {
+                            tma_store_2d(&maps.y, h * kN, bi * Tlen + t0, stage);
+                            bulk_commit_group();
+                        }
+                    } else if (t0 + tq < Tlen) {
+                        TIO *dst = y + (((size_t)bi * Tlen + t0 + tq) * H + h) * kN + i0;
+#pragma unroll
+                        for (int e8 = 0; e8 < 4; ++e8)
+                            *reinterpret_cast<uint4 *>(dst + e8 * 8) = make_uint4(w[4 * e8], w[4 * e8 + 1], w[4 * e8 + 2], w[4 * e8 + 3]);
+                    }
+                } else {
+                    // fp32 output: this thread's 32 channels are one 128-byte row of panel `hf` of the staged tile
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) ybad |= !(fabsf(__uint_as_float(v[e])) <= 3.0e38f);
+                    if (t0 + kL <= Tlen) {
+                        unsigned char *stage = smem + SM::kY + a * SM::kYTile + hf * (SM::kYTile / 2);
+                        if (elected) bulk_wait_group_read<1>();   // (a chunk's two stores form one group)
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+                        for (int e4 = 0; e4 < 8; ++e4) {
+                            const uint32_t o = (uint32_t)tq * 128u + (((uint32_t)e4 ^ ((uint32_t)tq & 7u)) << 4);
+                            if (RWKV7_IN_RANGE(o + 16 <= SM::kYTile / 2, status))
+                                *reinterpret_cast<uint4 *>(stage + o) = make_uint4(v[4 * e4], v[4 * e4 + 1], v[4 * e4 + 2], v[4 * e4 + 3]);
+                        }
+                        fence_proxy_async();
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (elected) {
+                            unsigned char *tile = smem + SM::kY + a * SM::kYTile;
+                            tma_store_2d(&maps.y, h * kN, bi * Tlen + t0, tile);
+                            tma_store_2d(&maps.y, h * kN + 32, bi * Tlen + t0, tile + SM::kYTile / 2);
+                            bulk_commit_group();
+                        }
+                    } else if (t0 + tq < Tlen) {
+                        TIO *dst = y + (((size_t)bi * Tlen + t0 + tq) * H + h) * kN + i0;
+#pragma unroll
+                        for (int e4 = 0; e4 < 8; ++e4)
+                            *reinterpret_cast<uint4 *>(dst + e4 * 4) = make_uint4(v[4 * e4], v[4 * e4 + 1], v[4 * e4 + 2], v[4 * e4 + 3]);
+                    }
                 }
             }
             if (elected) bulk_wait_group<0>();   // the stores read this CTA's shared memory
@@ -1088,7 +1143,7 @@ size_t wkv7_split_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, in
 
 bool wkv7_split_supported(const Wkv7Args &p) {
     auto aligned = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
-    return p.N == kN && p.bf16 && aligned(p.r) && aligned(p.w) && aligned(p.k) && aligned(p.v) && aligned(p.a) &&
+    return p.N == kN && aligned(p.r) && aligned(p.w) && aligned(p.k) && aligned(p.v) && aligned(p.a) &&
            aligned(p.b) && aligned(p.y) && p.B * p.T < (int64_t(1) << 31) && p.B * p.H < (int64_t(1) << 24);
 }
 
@@ -1102,7 +1157,8 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     const int nchunks = (int)((p.T + kL - 1) / kL);
     // The plan: overlapped (two buffers) when it applies and the workspace holds two segments of a useful
     // length, else one buffer with the longest segment that fits.
-    bool overlap = overlap_applies(chains, (size_t)nchunks, p.num_sms);
+    // (fp32 tensors: one operator CTA per SM and the three-stage scan, which does not fit beside it)
+    bool overlap = p.bf16 && overlap_applies(chains, (size_t)nchunks, p.num_sms);
     size_t seg = preferred_segment(chains, (size_t)nchunks, overlap);
     const size_t fixed = fixed_part(chains);
     if (workspace_bytes < fixed) return (int)cudaErrorInvalidValue;
@@ -1132,23 +1188,26 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     ScanMaps smaps;
     const void *ptrs[5] = {p.r, p.w, p.k, p.a, p.b};
     const cuuint64_t dims[2] = {(cuuint64_t)(p.H * p.N), (cuuint64_t)(p.B * p.T)};
-    const cuuint64_t strides[1] = {(cuuint64_t)(p.H * p.N * 2)};
+    const size_t esize = p.bf16 ? 2 : 4;
+    const CUtensorMapDataType etype = p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const cuuint64_t strides[1] = {(cuuint64_t)(p.H * p.N * esize)};
     const cuuint32_t box[2] = {(cuuint32_t)kN, (cuuint32_t)kL};
     const cuuint32_t estr[2] = {1, 1};
     for (int i = 0; i < 5; ++i) {
-        CUresult r = encode(&omaps.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptrs[i]), dims, strides,
+        CUresult r = encode(&omaps.m[i], etype, 2, const_cast<void *>(ptrs[i]), dims, strides,
                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
     }
-    {
-        CUresult r = encode(&smaps.v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(p.v), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    {   // V: bf16 tiles land swizzled and are converted in place; fp32 tiles land row-major beside their fp16 copy
+        CUresult r = encode(&smaps.v, etype, 2, const_cast<void *>(p.v), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, p.bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
     }
-    {
-        CUresult r = encode(&smaps.y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.y, dims, strides, box, estr,
+    {   // y: rows of 128 bytes in shared memory (64 bf16 channels, or 32 fp32 channels: two stores per chunk)
+        const cuuint32_t ybox[2] = {(cuuint32_t)(p.bf16 ? kN : kN / 2), (cuuint32_t)kL};
+        CUresult r = encode(&smaps.y, etype, 2, p.y, dims, strides, ybox, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
@@ -1156,15 +1215,16 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     int *status = nullptr;
     if (int e = device_status_ptr(p.device, &status)) return e;
 
-    auto k1 = wkv7_chunk_operator_kernel<__nv_bfloat16>;
-    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem1);
+    auto k1 = p.bf16 ? wkv7_chunk_operator_kernel<__nv_bfloat16> : wkv7_chunk_operator_kernel<float>;
+    const size_t smem1 = p.bf16 ? kSmem1 : kSmem1F32;
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (e != cudaSuccess) return (int)e;
     // Beside an operator CTA only the two-stage scan fits on an SM; it is also the one for more chains than SMs.
     const bool small_scan = overlap || (int64_t)chains > (int64_t)p.num_sms;
     auto launch_scan = [&](cudaStream_t st, int buf, const float *s_in, float *s_out, int c0, int n, int check) -> cudaError_t {
         const unsigned char *ops = ws + lay.operators[buf];
         const float *vecs = reinterpret_cast<const float *>(ws + lay.vectors[buf]);
-        auto go = [&](auto kern, size_t smem_bytes, unsigned threads) -> cudaError_t {
+        auto go = [&](auto kern, auto ytype, size_t smem_bytes, unsigned threads) -> cudaError_t {
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
             if (err != cudaSuccess) return err;
             cudaLaunchConfig_t cfg = {};
@@ -1177,20 +1237,23 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
             cfg.numAttrs = st == stream ? 1 : 0;   // directly behind its operator kernel on the caller's stream
-            err = cudaLaunchKernelEx(&cfg, kern, smaps, ops, vecs, s_in, s_out, reinterpret_cast<__nv_bfloat16 *>(p.y), flags,
+            using YPtr = std::remove_pointer_t<decltype(ytype)> *;
+            err = cudaLaunchKernelEx(&cfg, kern, smaps, ops, vecs, s_in, s_out, reinterpret_cast<YPtr>(p.y), flags,
                                      (int)p.T, (int)p.H, c0, n, n, check, status);
             if (err == cudaSuccess) count_launch();
             return err;
         };
-        return small_scan ? go(wkv7_state_scan_kernel<2>, ScanSmem<2>::kBytes, ScanWarps<2>::kThreads)
-                          : go(wkv7_state_scan_kernel<4>, ScanSmem<4>::kBytes, ScanWarps<4>::kThreads);
+        using bf = __nv_bfloat16;
+        if (!p.bf16) return go(wkv7_state_scan_kernel<3, float>, (float *)nullptr, ScanSmem<3, float>::kBytes, ScanWarps<3>::kThreads);
+        return small_scan ? go(wkv7_state_scan_kernel<2, bf>, (bf *)nullptr, ScanSmem<2, bf>::kBytes, ScanWarps<2>::kThreads)
+                          : go(wkv7_state_scan_kernel<4, bf>, (bf *)nullptr, ScanSmem<4, bf>::kBytes, ScanWarps<4>::kThreads);
     };
     auto launch_operators = [&](int buf, int segment, int c0, int n) -> cudaError_t {
         const long long units = (long long)chains * n;
-        const long long places = 2LL * p.num_sms - (overlap ? (long long)chains : 0);   // (see overlap_applies)
+        const long long places = (p.bf16 ? 2LL : 1LL) * p.num_sms - (overlap ? (long long)chains : 0);   // (see overlap_applies)
         const unsigned grid = (unsigned)(units < places ? units : places);
         // (the operator of (chain, chunk) sits at index chain * n + chunk - c0 of the buffer in both kernels)
-        k1<<<grid, kThreads1, kSmem1, stream>>>(omaps, ws + lay.operators[buf], reinterpret_cast<float *>(ws + lay.vectors[buf]),
+        k1<<<grid, kThreads1, smem1, stream>>>(omaps, ws + lay.operators[buf], reinterpret_cast<float *>(ws + lay.vectors[buf]),
                                                 flags, (int)p.T, (int)p.H, c0, n, (int)chains, counters + segment, status);
         count_launch();
         return cudaGetLastError();

@@ -159,7 +159,7 @@ def test_split_in_segments_is_bitwise_the_single_pass(pkg, workloads, cuda, alia
 def test_automatic_choice(pkg, workloads, cuda):
     """bf16, N = 64, T >= 512 with a workspace of the reported size: the two-kernel path (operators, scan,
     and the two flagged-chain kernels that exit at once: four launches).  A workspace that only holds the
-    flags, a short sequence or fp32 tensors keep the earlier kernels."""
+    flags or a short sequence keep the earlier kernels."""
     inp = workloads.wkv7_inputs(2, 512, 2, 64, seed=78, dtype=torch.bfloat16, device=cuda, state="normal")
     seq = pkg.Wkv7PretrainForwardInputs(*[inp[n] for n in "rwkvab"])
     before = pkg.kernel_launch_count()
@@ -228,3 +228,58 @@ def test_split_overlapped_scan_is_bitwise_the_serial_one(pkg, oracle, workloads,
     torch.cuda.synchronize()
     for o in outs:
         assert np.array_equal(o.next_state.cpu().numpy(), s1)
+
+
+@pytest.mark.parametrize("shape,state", [
+    ((2, 128, 3, 64), "normal"), ((1, 100, 2, 64), "normal"), ((2, 65, 2, 64), None),   # partial last chunks
+    ((1, 1024, 4, 64), "normal"), ((1, 256, 200, 64), None),                             # 200 chains: more than SMs
+])
+def test_split_fp32_tensors_against_oracle(pkg, oracle, workloads, cuda, shape, state):
+    """fp32 sequence tensors (the dtype of every test of the reference, wkv7/mod.rs:386-398) take the same two
+    kernels: fp32 tiles in, fp16 operands on the tensor cores, fp32 y out.  The oracle sees the unrounded
+    fp32 inputs; y and the final state within 1e-3 of the largest reference value."""
+    inp = workloads.wkv7_inputs(*shape, seed=91, dtype=torch.float32, state=state)
+    y_ref, s_ref = _oracle(oracle, inp)
+    if state is None:
+        inp["s0"] = torch.zeros(shape[0], shape[2], 64, 64)
+    before = pkg.kernel_launch_count()
+    y, s = _statepass(pkg, cuda, inp, pkg.WKV7_SPLIT)
+    assert pkg.kernel_launch_count() - before == 3      # operators, scan, flagged chains by the sequential scan (none)
+    print("split fp32 parity", shape, parity.headline(y, y_ref), parity.headline(s, s_ref))
+    parity.assert_close_f32(y, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s, s_ref, 1e-3, "state")
+
+
+@pytest.mark.parametrize("alias", [False, True])
+def test_split_fp32_flagged_chains_take_the_sequential_scan(pkg, oracle, workloads, cuda, alias):
+    """fp32 tensors, one chain with the strongest decay and one with keys that overflow fp16: both are flagged
+    and recomputed by the sequential scan from the untouched initial state; the others come from the tensor cores."""
+    inp = workloads.wkv7_inputs(2, 320, 3, 64, seed=92, dtype=torch.float32, state="normal")
+    inp["w"][1, :, 0] = -0.5
+    inp["k"][0, :, 2] *= 1.0e4
+    y_ref, s_ref = _oracle(oracle, inp)
+    y_seq, s_seq = _statepass(pkg, cuda, inp, pkg.WKV7_SEQUENTIAL)
+    y, s = _statepass(pkg, cuda, inp, pkg.WKV7_SPLIT, alias=alias)
+    assert np.isfinite(y).all() and np.isfinite(s).all()
+    for b in range(2):
+        for h in range(3):
+            parity.assert_close_f32(y[b, :, h], y_ref[b, :, h], 1e-3, f"y, chain {b},{h}")
+            parity.assert_close_f32(s[b, h], s_ref[b, h], 1e-3, f"state, chain {b},{h}")
+    for b, h in ((1, 0), (0, 2)):
+        assert np.array_equal(s[b, h], s_seq[b, h]) and np.array_equal(y[b, :, h], y_seq[b, :, h])
+    assert not np.array_equal(s[0, 0], s_seq[0, 0])
+
+
+def test_split_fp32_automatic_choice_and_long_context(pkg, oracle, workloads, cuda):
+    """Under the automatic choice fp32 tensors of T >= 512 take the two-kernel path too (a pair of launches per
+    segment of chunks, then the flagged-chain scan), and one chain over T = 16 384 stays within the tolerance."""
+    inp = workloads.wkv7_inputs(1, 16384, 1, 64, seed=93, dtype=torch.float32)
+    y_ref, s_ref = _oracle(oracle, inp)
+    inp["s0"] = torch.zeros(1, 1, 64, 64)
+    before = pkg.kernel_launch_count()
+    y, s = _statepass(pkg, cuda, inp, pkg.WKV7_AUTO)
+    launches = pkg.kernel_launch_count() - before
+    assert launches >= 3 and launches % 2 == 1
+    print(f"split fp32 long context: y {parity.headline(y, y_ref):.3e} state {parity.headline(s, s_ref):.3e}")
+    parity.assert_close_f32(y, y_ref, 1e-3, "y")
+    parity.assert_close_f32(s, s_ref, 1e-3, "state")
