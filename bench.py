@@ -349,13 +349,16 @@ def main():
     if not args.no_prefill_other and rank == 0 and not args.small:
         peak_gbs, _ = measured_peaks()
         prefill_other = {}
-        for name, (Bo, To, Ho) in (("cfg2_layer_1gpu", (16, 8192, 32)), ("cfg4_layer_shard_of_8", (4, 65536, 8)),
-                                   ("single_sequence_cfg2_model", (1, 8192, 32))):
-            oin = workloads.wkv7_inputs(Bo, To, Ho, 64, seed=11, dtype=torch.bfloat16, device=dev)
+        for name, (Bo, To, Ho, odt) in (("cfg2_layer_1gpu", (16, 8192, 32, torch.bfloat16)),
+                                        ("cfg4_layer_shard_of_8", (4, 65536, 8, torch.bfloat16)),
+                                        ("single_sequence_cfg2_model", (1, 8192, 32, torch.bfloat16)),
+                                        ("cfg1_fp32_tensors", (CFG1["B"], CFG1["T"], CFG1["H"], torch.float32))):
+            oin = workloads.wkv7_inputs(Bo, To, Ho, 64, seed=11, dtype=odt, device=dev)
             oseq = pkg.Wkv7PretrainForwardInputs(*[oin[n] for n in "rwkvab"])
             os0 = torch.zeros(Bo, Ho, 64, 64, device=dev)
             oy, oso = torch.empty_like(oin["r"]), torch.empty_like(os0)
-            ows_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bo, To, Ho, 64, pkg.BF16))
+            esize = oin["r"].element_size()
+            ows_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bo, To, Ho, 64, pkg.BF16 if esize == 2 else pkg.F32))
             ows = torch.empty(max(ows_bytes, 1), dtype=torch.uint8, device=dev)
             ocall = pkg.Wkv7StatepassCall(os0, oseq, oy, oso, ows)
             for _ in range(2):
@@ -368,23 +371,9 @@ def main():
             o1.record()
             torch.cuda.synchronize()
             oms = o0.elapsed_time(o1) / 3
-            obytes = Bo * To * Ho * BYTES_PER_TOKEN_HEAD + Bo * Ho * STATE_BYTES
-            # few chains: the library gives each chain a cluster of CTAs; time the one-CTA kernel beside it
-            one_cta_ms = None
-            if Bo * Ho * 2 <= 148:
-                pkg.set_wkv7_cluster(1)
-                ocall()
-                torch.cuda.synchronize()
-                o0.record()
-                for _ in range(3):
-                    ocall()
-                o1.record()
-                torch.cuda.synchronize()
-                one_cta_ms = o0.elapsed_time(o1) / 3
-                pkg.set_wkv7_cluster(0)
-            prefill_other[name] = {"shape": f"B={Bo} T={To} H={Ho} N=64 bf16 ({Bo * Ho} chains)", "ms": oms,
-                                   "ms_one_cta_per_chain": one_cta_ms,
-                                   "tokens_per_s": Bo * To / (oms * 1e-3), "gb_per_s": obytes / (oms * 1e-3) / 1e9,
+            obytes = Bo * To * Ho * 64 * 7 * esize + Bo * Ho * STATE_BYTES
+            prefill_other[name] = {"shape": f"B={Bo} T={To} H={Ho} N=64 {'bf16' if esize == 2 else 'fp32'} ({Bo * Ho} chains)",
+                                   "ms": oms, "tokens_per_s": Bo * To / (oms * 1e-3), "gb_per_s": obytes / (oms * 1e-3) / 1e9,
                                    "frac_of_hbm_peak": obytes / (oms * 1e-3) / 1e9 / peak_gbs,
                                    "algorithmic_bytes": obytes}
             del oin, oseq, os0, oy, oso, ows, ocall
