@@ -627,12 +627,13 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
 // ready, only the Z half waits for the previous chunk.
 // ------------------------------------------------------------------------------------------
 constexpr int kComputeWarps = 8;
-// The four-stage variant (one CTA per SM) has a warp of its own for the V conversion; in the two-stage variant
+// The four-stage variant (one CTA per SM) has a warp of its own for the V conversion and one for issuing the V half
+// of the products; in the two-stage variant
 // (two CTAs per SM, or beside an operator CTA) the compute warps do it between their other work, which measured
 // faster there (32 chains x 1024 chunks overlapped with the operator kernel: 1.41 against 1.53 ms).
 template <int NS> struct ScanWarps {
     static constexpr bool kConvWarp = NS > 2;
-    static constexpr int kThreads = (kComputeWarps + 2 + (kConvWarp ? 1 : 0)) * 32;
+    static constexpr int kThreads = (kComputeWarps + 2 + (kConvWarp ? 2 : 0)) * 32;   // + converter, + issuer of the V half
 };
 constexpr uint32_t kVecBytes = kVecFloats * 4;              // the chunk's two decay vectors
 
@@ -685,7 +686,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     uint64_t *bar_accfull = bar_empty + NS;    // [2] accumulator complete
     uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (256 arrivals)
     uint64_t *bar_zready = bar_accfree + 2;    // state tile written (128 arrivals)
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_zready + 1);
+    uint64_t *bar_vdone = bar_zready + 1;      // [2] (four-stage variant) the V half of the accumulator is complete
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_vdone + 2);
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
     int *chain_bad = abort_flag + 1;
 
@@ -704,6 +706,8 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             mbar_init(bar_accfree + a, 256);
         }
         mbar_init(bar_zready, 128);
+        mbar_init(bar_vdone + 0, 1);
+        mbar_init(bar_vdone + 1, 1);
         mbar_fence_init();
         *abort_flag = 0;
         *chain_bad = 0;
@@ -756,7 +760,37 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             }
         }
     } else if (warp == kComputeWarps + 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer.  Two-stage variant: both halves of the chunk's product.  Four-stage variant:
+        // the Z half only (k = j: rows 0..63 of the operator against Z[j][i]); the V half is issued ahead of time by
+        // another thread into the same accumulator, and since products issued by different threads are ordered
+        // only through a barrier, this thread waits until that half is complete before it adds to it.
+        if (lane == 0) {
+            constexpr uint32_t id = idesc16(128, 64, true, true);
+            for (int c = 0; c < n; ++c) {
+                const int s = c % NS, a = c & 1;
+                const uint32_t op = sb + SM::kStages + s * kStageBytes, vt = op + kOperatorBytes;
+                if constexpr (kConvWarp) {
+                    if (!mbar_wait(bar_vdone + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                } else {
+                    if (!mbar_wait(bar_vready + s, (uint32_t)((c / NS) & 1))) { atomicOr(abort_flag, 1); break; }
+                    if (!mbar_wait(bar_accfree + a, (uint32_t)(((c >> 1) & 1) ^ 1))) { atomicOr(abort_flag, 1); break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)   // k = 64 + s: rows 64.. of both operator panels against V[s][i]
+                        umma_f16(tmem + a * 64, dMN(op, 2 * kPanel, 4 + ks), dMN(vt, kPanel, ks), id, ks > 0);
+                }
+                if (!mbar_wait_spin(bar_zready, (uint32_t)(c & 1))) { atomicOr(abort_flag, 1); break; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // k = j: rows 0..63 against Z[j][i]
+                    umma_f16(tmem + a * 64, dMN(op, 2 * kPanel, ks), dMN(sb + SM::kZ, kPanel, ks), id, true);
+                umma_commit(bar_accfull + a);
+                umma_commit(bar_empty + s);
+            }
+        }
+    } else if (kConvWarp && warp == kComputeWarps + 3) {
+        // ---------------- issuer of the V half (four-stage variant): O[64 + s][(j' | t)] against V[s][i], as soon as
+        // the tile is converted and the accumulator has been read back, one chunk ahead of the chain.
         if (lane == 0) {
             constexpr uint32_t id = idesc16(128, 64, true, true);
             for (int c = 0; c < n; ++c) {
@@ -766,15 +800,9 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (!mbar_wait(bar_accfree + a, (uint32_t)(((c >> 1) & 1) ^ 1))) { atomicOr(abort_flag, 1); break; }
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // k = 64 + s: rows 64.. of both operator panels against V[s][i]
+                for (int ks = 0; ks < 4; ++ks)
                     umma_f16(tmem + a * 64, dMN(op, 2 * kPanel, 4 + ks), dMN(vt, kPanel, ks), id, ks > 0);
-                if (!mbar_wait_spin(bar_zready, (uint32_t)(c & 1))) { atomicOr(abort_flag, 1); break; }
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // k = j: rows 0..63 against Z[j][i]
-                    umma_f16(tmem + a * 64, dMN(op, 2 * kPanel, ks), dMN(sb + SM::kZ, kPanel, ks), id, true);
-                umma_commit(bar_accfull + a);
-                umma_commit(bar_empty + s);
+                umma_commit(bar_vdone + a);
             }
         }
     } else if (kConvWarp && warp == kComputeWarps + 2) {
