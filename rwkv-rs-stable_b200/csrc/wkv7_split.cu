@@ -681,11 +681,11 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + SM::kBars);   // [NS] stage landed (bytes)
     constexpr bool kConvWarp = ScanWarps<NS>::kConvWarp;
-    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (one arrival per converting thread)
+    uint64_t *bar_vready = bar_full + NS;      // [NS] V tile converted to fp16 (one arrival per converting warp)
     uint64_t *bar_empty = bar_vready + NS;     // [NS] the stage's MMAs are done
     uint64_t *bar_accfull = bar_empty + NS;    // [2] accumulator complete
-    uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (256 arrivals)
-    uint64_t *bar_zready = bar_accfree + 2;    // state tile written (128 arrivals)
+    uint64_t *bar_accfree = bar_accfull + 2;   // [2] accumulator read back (8 arrivals)
+    uint64_t *bar_zready = bar_accfree + 2;    // state tile written (4 arrivals)
     uint64_t *bar_vdone = bar_zready + 1;      // [2] (four-stage variant) the V half of the accumulator is complete
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar_vdone + 2);
     int *abort_flag = reinterpret_cast<int *>(tmem_slot + 1);
@@ -698,14 +698,14 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(bar_full + s, 1);
-            mbar_init(bar_vready + s, kConvWarp ? 32 : 256);
+            mbar_init(bar_vready + s, kConvWarp ? 1 : 8);      // one arrival per converting warp
             mbar_init(bar_empty + s, 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_accfull + a, 1);
-            mbar_init(bar_accfree + a, 256);
+            mbar_init(bar_accfree + a, 8);                     // one arrival per compute warp
         }
-        mbar_init(bar_zready, 128);
+        mbar_init(bar_zready, 4);                              // one arrival per state warp
         mbar_init(bar_vdone + 0, 1);
         mbar_init(bar_vdone + 1, 1);
         mbar_fence_init();
@@ -727,6 +727,19 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         if (warp == 0) tmem_dealloc(tmem, 128);
         return;
     }
+    // A warp's threads meet, then its first lane arrives for all of them: an mbarrier takes one arrival at a time,
+    // and 128 or 256 of them in a row were a visible part of the chain's serial step.
+    auto warp_arrive = [&](uint64_t *bar) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+    };
+    // A wait of a whole warp: every lane polls (one polling lane and a broadcast measured far slower: 264 against
+    // 231 us at 96 chains x 64 chunks), then a vote makes the outcome the same in all lanes, so that every lane takes
+    // the same way out of a loop whose lanes meet at warp barriers.
+    auto warp_wait = [&](uint64_t *bar, uint32_t parity, bool spin) -> bool {
+        const bool ok = spin ? mbar_wait_spin(bar, parity) : mbar_wait(bar, parity);
+        return __all_sync(0xffffffffu, ok) != 0;
+    };
     const uint32_t sb = smem_u32(smem);
     const unsigned char *ops = operators + ((size_t)chain * seg_chunks) * kOperatorBytes;
     const float *vecs = vectors + ((size_t)chain * seg_chunks) * kVecFloats;
@@ -812,8 +825,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         // the compute warps between their other work, the conversion sat on the chain's serial path.)
         for (int c = 0; c < n; ++c) {
             const int s = c % NS;
-            if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) { atomicOr(abort_flag, 1); break; }
-            if (*reinterpret_cast<volatile int *>(abort_flag)) break;
+            if (!warp_wait(bar_full + s, (uint32_t)((c / NS) & 1), false)) { atomicOr(abort_flag, 1); break; }
             unsigned char *vt = smem + SM::kStages + s * kStageBytes + kOperatorBytes;
             if constexpr (!kF32) {
                 uint4 *p = reinterpret_cast<uint4 *>(vt);
@@ -841,7 +853,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 }
             }
             fence_proxy_async();
-            mbar_arrive(bar_vready + s);
+            warp_arrive(bar_vready + s);
         }
     } else {
         const int quarter = warp & 3, hf = warp >> 2;
@@ -852,7 +864,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
         auto convert_v = [&](int c) -> bool {
             if constexpr (kConvWarp) return true;
             const int s = c % NS;
-            if (!mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+            if (!warp_wait(bar_full + s, (uint32_t)((c / NS) & 1), false)) return false;
             uint4 *p = reinterpret_cast<uint4 *>(smem + SM::kStages + s * kStageBytes + kOperatorBytes + tid * 32);
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
@@ -866,7 +878,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 p[q] = x;
             }
             fence_proxy_async();
-            mbar_arrive(bar_vready + s);
+            warp_arrive(bar_vready + s);
             return true;
         };
         if (quarter < 2) {
@@ -886,7 +898,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                         *reinterpret_cast<uint4 *>(smem + SM::kZ + off16(jp, i0 + e8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 fence_proxy_async();
-                mbar_arrive(bar_zready);
+                warp_arrive(bar_zready);
             };
             put_tile();
             // this row's two decay factors per chunk come with the stage; they are read one chunk ahead (the
@@ -896,7 +908,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (c >= n) { out = make_float2(1.f, 0.f); return true; }
                 const int s = c % NS;
                 // (in the two-stage variant this thread has just waited for the stage in convert_v)
-                if (kConvWarp && !mbar_wait(bar_full + s, (uint32_t)((c / NS) & 1))) return false;
+                if (kConvWarp && !warp_wait(bar_full + s, (uint32_t)((c / NS) & 1), false)) return false;
                 out = make_float2(ring[s * kVecFloats + jp], ring[s * kVecFloats + 64 + jp]);
                 return true;
             };
@@ -909,13 +921,13 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 if (c + 1 < n && !convert_v(c + 1)) { atomicOr(abort_flag, 1); break; }
                 if (!load_gg(c + 1, gg_next)) { atomicOr(abort_flag, 1); break; }
                 // (polled without suspending: this wait is on the serial path of the chain)
-                if (!mbar_wait_spin(bar_accfull + a, (uint32_t)((c >> 1) & 1))) { atomicOr(abort_flag, 1); break; }
+                if (!warp_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1), true)) { atomicOr(abort_flag, 1); break; }
                 tc_fence_after();
                 uint32_t v[32];
                 tmem_ld32(tmem + lane_base + a * 64 + i0, v);
                 tmem_ld_wait();
                 tc_fence_before();
-                mbar_arrive(bar_accfree + a);
+                warp_arrive(bar_accfree + a);
 #pragma unroll
                 for (int e = 0; e < 32; ++e) Z[e] = fmaf(gg.y, __uint_as_float(v[e]), gg.x * Z[e]);
                 if (c + 1 < n) put_tile();
@@ -946,13 +958,13 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             for (int c = 0; c < n; ++c) {
                 const int a = c & 1;
                 if (!dead && c + 1 < n && !convert_v(c + 1)) dead = true;
-                if (!dead && !mbar_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1))) dead = true;
+                if (!dead && !warp_wait(bar_accfull + a, (uint32_t)((c >> 1) & 1), false)) dead = true;
                 tc_fence_after();
                 uint32_t v[32];
                 tmem_ld32(tmem + lane_base + a * 64 + i0, v);
                 tmem_ld_wait();
                 tc_fence_before();
-                mbar_arrive(bar_accfree + a);
+                warp_arrive(bar_accfree + a);
                 const int t0 = (chunk0 + c) * kL;
                 if constexpr (!kF32) {
                     uint32_t w[16];
