@@ -627,13 +627,15 @@ wkv7_chunk_operator_kernel(const __grid_constant__ OperatorMaps maps, unsigned c
 // ready, only the Z half waits for the previous chunk.
 // ------------------------------------------------------------------------------------------
 constexpr int kComputeWarps = 8;
-// The four-stage variant (one CTA per SM) has a warp of its own for the V conversion and one for issuing the V half
+// The four-stage variant (one CTA per SM) has warps of its own for the V conversion and one for issuing the V half
 // of the products; in the two-stage variant
 // (two CTAs per SM, or beside an operator CTA) the compute warps do it between their other work, which measured
 // faster there (32 chains x 1024 chunks overlapped with the operator kernel: 1.41 against 1.53 ms).
 template <int NS> struct ScanWarps {
     static constexpr bool kConvWarp = NS > 2;
-    static constexpr int kThreads = (kComputeWarps + 2 + (kConvWarp ? 2 : 0)) * 32;   // + converter, + issuer of the V half
+    static constexpr int kConv = 4;   // converter warps (one alone needs about 770 cycles per tile: as long as the whole serial step)
+    // warps 8 loader, 9 MMA issuer; then 10 converter, 11 issuer of the V half, 12.. the other converters
+    static constexpr int kThreads = (kComputeWarps + 2 + (kConvWarp ? 1 + kConv : 0)) * 32;
 };
 constexpr uint32_t kVecBytes = kVecFloats * 4;              // the chunk's two decay vectors
 
@@ -698,7 +700,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(bar_full + s, 1);
-            mbar_init(bar_vready + s, kConvWarp ? 1 : 8);      // one arrival per converting warp
+            mbar_init(bar_vready + s, kConvWarp ? ScanWarps<NS>::kConv : 8);      // one arrival per converting warp
             mbar_init(bar_empty + s, 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -818,34 +820,41 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 umma_commit(bar_vdone + a);
             }
         }
-    } else if (kConvWarp && warp == kComputeWarps + 2) {
-        // ---------------- V converter.  The V tile arrives as bf16 and the tensor core wants both operands
-        // of a product in one format: this warp turns it into fp16 in place (element by element, the layout
-        // is untouched) as soon as the stage has landed, well ahead of the product that reads it.  (Done by
-        // the compute warps between their other work, the conversion sat on the chain's serial path.)
+    } else if (kConvWarp && (warp == kComputeWarps + 2 || warp >= kComputeWarps + 4)) {
+        // ---------------- V converters.  The V tile arrives as bf16 and the tensor core wants both operands
+        // of a product in one format: these warps turn it into fp16 in place (element by element, the layout
+        // is untouched; each a quarter of the tile) as soon as the stage has landed, well ahead of the product
+        // that reads it.  (Done by the compute warps between their other work, the conversion sat on the chain's
+        // serial path.)
+        constexpr int kConv = ScanWarps<NS>::kConv;
+        const int ci = warp == kComputeWarps + 2 ? 0 : warp - (kComputeWarps + 3);   // 0 .. kConv - 1
         for (int c = 0; c < n; ++c) {
             const int s = c % NS;
             if (!warp_wait(bar_full + s, (uint32_t)((c / NS) & 1), false)) { atomicOr(abort_flag, 1); break; }
             unsigned char *vt = smem + SM::kStages + s * kStageBytes + kOperatorBytes;
             if constexpr (!kF32) {
                 uint4 *p = reinterpret_cast<uint4 *>(vt);
-#pragma unroll 4
-                for (int q = 0; q < (int)(kPanel / 16 / 32); ++q) {
-                    uint4 x = p[q * 32 + lane];
-                    uint32_t *xs = &x.x;
+                constexpr int kShare = (int)(kPanel / 16 / 32) / kConv;
+                uint4 x[kShare];
+#pragma unroll
+                for (int q = 0; q < kShare; ++q) x[q] = p[(ci * kShare + q) * 32 + lane];
+#pragma unroll
+                for (int q = 0; q < kShare; ++q) {
+                    uint32_t *xs = &x[q].x;
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const float2 f = unpack_bf2(xs[e]);
                         xs[e] = pack_h2(f.x, f.y);
                     }
-                    p[q * 32 + lane] = x;
+                    p[(ci * kShare + q) * 32 + lane] = x[q];
                 }
             } else {
                 // fp32 tile [t][i] (rows of 256 bytes) -> fp16 panel: eight channels of one token per step
                 const unsigned char *land = smem + SM::kStages + s * kStageBytes + SM::kVLand;
-#pragma unroll 4
-                for (int q = 0; q < kL * kN / 8 / 32; ++q) {
-                    const int idx = q * 32 + lane, t = idx >> 3, cg = idx & 7;
+                constexpr int kShare = kL * kN / 8 / 32 / kConv;
+#pragma unroll
+                for (int q = 0; q < kShare; ++q) {
+                    const int idx = (ci * kShare + q) * 32 + lane, t = idx >> 3, cg = idx & 7;
                     const float4 x0 = *reinterpret_cast<const float4 *>(land + t * (kN * 4) + cg * 32);
                     const float4 x1 = *reinterpret_cast<const float4 *>(land + t * (kN * 4) + cg * 32 + 16);
                     *reinterpret_cast<uint4 *>(vt + off16(t, cg * 8)) =
