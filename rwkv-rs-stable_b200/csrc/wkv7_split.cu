@@ -960,7 +960,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             // by the threads themselves.
             const int tq = (quarter - 2) * 32 + lane;     // token within the chunk
             const bool elected = warp == 2 && lane == 0;
-            bool ybad = false;   // a non-finite output: the chain is flagged for recomputation
+            float ysum = 0.f;    // a non-finite output (or one too large for bf16) flags the chain for recomputation
             // After an expired wait this thread stops waiting but still walks the loop, so that the four
             // warps keep meeting at the named barrier below (the call then reports a time-out).
             bool dead = n > 0 && !convert_v(0);
@@ -979,9 +979,10 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                     uint32_t w[16];
 #pragma unroll
                     for (int e2 = 0; e2 < 16; ++e2) {
-                        const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(v[2 * e2]), __uint_as_float(v[2 * e2 + 1]));
+                        const float x0 = __uint_as_float(v[2 * e2]), x1 = __uint_as_float(v[2 * e2 + 1]);
+                        ysum += fabsf(x0) + fabsf(x1);   // (a non-finite output makes the sum non-finite for good)
+                        const __nv_bfloat162 b2 = __floats2bfloat162_rn(x0, x1);
                         w[e2] = *reinterpret_cast<const uint32_t *>(&b2);
-                        ybad |= ((w[e2] & 0x7f80u) == 0x7f80u) || ((w[e2] & 0x7f800000u) == 0x7f800000u);
                     }
                     if (t0 + kL <= Tlen) {
                         unsigned char *stage = smem + SM::kY + a * SM::kYTile;
@@ -1007,7 +1008,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
                 } else {
                     // fp32 output: this thread's 32 channels are one 128-byte row of panel `hf` of the staged tile
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) ybad |= !(fabsf(__uint_as_float(v[e])) <= 3.0e38f);
+                    for (int e = 0; e < 32; ++e) ysum += fabsf(__uint_as_float(v[e]));
                     if (t0 + kL <= Tlen) {
                         unsigned char *stage = smem + SM::kY + a * SM::kYTile + hf * (SM::kYTile / 2);
                         if (elected) bulk_wait_group_read<1>();   // (a chunk's two stores form one group)
@@ -1036,7 +1037,7 @@ wkv7_state_scan_kernel(const __grid_constant__ ScanMaps maps, const unsigned cha
             }
             if (elected) bulk_wait_group<0>();   // the stores read this CTA's shared memory
             if (dead) atomicOr(abort_flag, 1);
-            if (ybad) atomicOr(chain_bad, 1);
+            if (!(ysum <= 3.0e38f)) atomicOr(chain_bad, 1);
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
     }
