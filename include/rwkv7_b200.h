@@ -91,12 +91,13 @@ typedef struct rwkv7_tensor {
 } rwkv7_tensor;
 
 /* Which kernel the WKV7 entry points dispatch to.  AUTO picks the decode sweep for T <= 4; for N == 64 and
- * BF16 tensors the two-kernel tensor-core prefill (SPLIT: per-chunk operators in fp16, then one scan per chain)
- * from 512 tokens on when the workspace holds at least one chunk of operators per chain, and the fused tf32
- * chunked kernel (CHUNKED) from 64 tokens on otherwise; the sequential kernel for everything else.  Chains
- * that the fp16 operators of SPLIT cannot resolve (a chunk's log-decay beyond 18 in some channel, or a
- * non-finite operator) are recomputed by CHUNKED, and chains beyond its range (80) by SEQUENTIAL, inside the
- * same call; a final state that aliases the initial state is only written once a chain's result is final. */
+ * BF16 or F32 tensors the two-kernel tensor-core prefill (SPLIT: per-chunk operators in fp16, then one scan per
+ * chain) from 512 tokens on when the workspace holds at least one chunk of operators per chain; for BF16 tensors
+ * otherwise the fused tf32 chunked kernel (CHUNKED) from 64 tokens on; the sequential kernel for everything else
+ * (F32 tensors under 512 tokens, other head sizes).  Chains that the fp16 operators of SPLIT cannot resolve (a
+ * chunk's log-decay beyond 18 in some channel, or a non-finite operator) are recomputed by CHUNKED (BF16 tensors),
+ * and chains beyond its range (80), or flagged chains of F32 tensors, by SEQUENTIAL, inside the same call; a final
+ * state that aliases the initial state is only written once a chain's result is final. */
 typedef enum rwkv7_wkv7_path {
     RWKV7_WKV7_AUTO = 0,
     RWKV7_WKV7_SEQUENTIAL = 1,
@@ -174,7 +175,8 @@ int rwkv7_selftest_bounded_wait(int device, int64_t max_polls, rwkv7_stream stre
  * for the tf32 chunked kernel; for the two-kernel prefill the flags, 1024 work counters, a carried state per
  * chain and 32.5 KB per 64-token chunk of a segment of the call, at most 768 MB of operators).  A smaller
  * workspace is accepted: the call is cut into more segments, and below one chunk per chain the tf32 kernel
- * runs instead.  The size depends on the SM count of the calling thread's current device. */
+ * (BF16 tensors) or the sequential scan runs instead.  The size depends on the SM count of the calling thread's
+ * current device. */
 size_t rwkv7_wkv7_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N, int32_t dtype);
 
 /* Replaces Wkv7Backend::fused_wkv7_pretrain (wkv7/mod.rs:31, impl :55-79;

@@ -35,21 +35,24 @@ def main():
     from rwkv_rs_stable_b200 import workloads
     assert pkg.lib().rwkv7_build_features() == 3, "not the checked build"
     dev = torch.device("cuda:0")
-    cases = [(pkg.WKV7_SPLIT, (2, 192, 3, 64)), (pkg.WKV7_SPLIT, (1, 100, 2, 64)), (pkg.WKV7_SPLIT, (1, 130, 150, 64)),
-             (pkg.WKV7_CHUNKED, (2, 128, 2, 64)), (pkg.WKV7_SEQUENTIAL, (2, 37, 3, 64)), (pkg.WKV7_SEQUENTIAL, (3, 1, 5, 64))]
-    for path, shape in cases:
+    bf, f32 = torch.bfloat16, torch.float32
+    cases = [(pkg.WKV7_SPLIT, (2, 192, 3, 64), bf), (pkg.WKV7_SPLIT, (1, 100, 2, 64), bf), (pkg.WKV7_SPLIT, (1, 130, 150, 64), bf),
+             (pkg.WKV7_SPLIT, (2, 192, 3, 64), f32), (pkg.WKV7_SPLIT, (1, 100, 2, 64), f32),
+             (pkg.WKV7_CHUNKED, (2, 128, 2, 64), bf), (pkg.WKV7_SEQUENTIAL, (2, 37, 3, 64), bf), (pkg.WKV7_SEQUENTIAL, (3, 1, 5, 64), bf)]
+    for path, shape, dtype in cases:
         B, T, H, N = shape
-        inp = workloads.wkv7_inputs(*shape, seed=91, dtype=torch.bfloat16, state="normal")
+        esize = 2 if dtype == bf else 4
+        inp = workloads.wkv7_inputs(*shape, seed=91, dtype=dtype, state="normal")
         f = {k: v.float().numpy() for k, v in inp.items()}
         y_ref, s_ref = oracle.wkv7(f["r"], f["w"], f["k"], f["v"], f["a"], f["b"], f["s0"])
         gpu = {k: v.to(dev) for k, v in inp.items()}
         seq = pkg.Wkv7PretrainForwardInputs(*[gpu[n] for n in "rwkvab"])
         pkg.set_wkv7_path(path)
-        ws_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(B, T, H, N, pkg.BF16))
-        y_whole, y_buf = padded(B * T * H * N * 2, dev)
+        ws_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(B, T, H, N, pkg.BF16 if dtype == bf else pkg.F32))
+        y_whole, y_buf = padded(B * T * H * N * esize, dev)
         s_whole, s_buf = padded(B * H * N * N * 4, dev)
         w_whole, w_buf = padded(max(ws_bytes, 256), dev)
-        y = y_buf.view(torch.bfloat16).view(B, T, H, N)
+        y = y_buf.view(dtype).view(B, T, H, N)
         s = s_buf.view(torch.float32).view(B, H, N, N)
         out = pkg.wkv7_statepass_custom(gpu["s0"], seq, reference_contract=False, next_state=s, output=y,
                                         workspace=w_buf if ws_bytes else None)
@@ -57,9 +60,9 @@ def main():
         pkg.set_wkv7_path(pkg.WKV7_AUTO)
         status = pkg.read_device_status(0)
         assert status == 0, f"device status {status} for {shape}"
-        assert intact(y_whole, B * T * H * N * 2) and intact(s_whole, B * H * N * N * 4), f"canary around an output overwritten, {shape}"
+        assert intact(y_whole, B * T * H * N * esize) and intact(s_whole, B * H * N * N * 4), f"canary around an output overwritten, {shape}"
         assert intact(w_whole, max(ws_bytes, 256)), f"canary around the workspace overwritten, {shape}"
-        parity.assert_close_bf16_store(out.output.float().cpu().numpy(), y_ref, 1e-3, f"y {shape}")
+        (parity.assert_close_bf16_store if dtype == bf else parity.assert_close_f32)(out.output.float().cpu().numpy(), y_ref, 1e-3, f"y {shape}")
         parity.assert_close_f32(out.next_state.cpu().numpy(), s_ref, 1e-3, f"state {shape}")
     # streaming kernels on the same build
     x, mus = workloads.mix_inputs(2, 8, 32, seed=5, dtype=torch.bfloat16, device=dev)
