@@ -106,24 +106,6 @@ constexpr uint32_t kOffIdent = kOffRaw + 17408;
 static_assert(kScratchEnd <= kOffIdent && kOffIdent % 1024 == 0 && kOffIdent + 16384 + 8192 <= kOffRaw + kRawBytes,
               "identity tile (read as a 128-row operand) must stay inside the raw-tile region");
 
-// Optional per-phase cycle counters (development builds only): thread 0 of CTA 0
-// adds the cycles spent since the previous mark to the slot of the phase that
-// just ended.
-#ifdef RWKV7_PHASE_CLOCKS
-__device__ long long g_phase_clocks[16];
-#define PHASE(k)                                                        \
-    do {                                                                \
-        if (blockIdx.x == 0 && threadIdx.x == 0) {                      \
-            const long long now_ = clock64();                           \
-            g_phase_clocks[phase_prev_] += now_ - phase_t_;             \
-            phase_t_ = now_;                                            \
-            phase_prev_ = (k);                                          \
-        }                                                               \
-    } while (0)
-#else
-#define PHASE(k) do {} while (0)
-#endif
-
 struct TmaMaps {
     CUtensorMap m[6];  // r, w, k, v, a, b as [B*T, H*N] bf16, box 64 x 64
     CUtensorMap snap;  // SAVE: snapshots as [B*H*(T/16)*64, 64] fp32, box 64 rows x 32 columns, 128-byte swizzle
@@ -305,10 +287,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         }
     }
 
-#ifdef RWKV7_PHASE_CLOCKS
-    long long phase_t_ = clock64();
-    int phase_prev_ = 15;
-#endif
     // K-step-0 descriptors of every operand tile (constant for the whole kernel).
     const uint64_t dAR = desc_kmajor(smem_u32(tAR), 128, 0), dBK = desc_kmajor(smem_u32(tBK), 128, 0),
                    dZT = desc_kmajor(smem_u32(tZT), 128, 0),
@@ -330,13 +308,11 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             if (tid == 0 && chunk > 0) mbar_expect_tx(bar_state, kN * kN * 6);
         }
         // ---------------- wait for this chunk's six input tiles
-        PHASE(0);
         // A wait that expires sets a sticky flag; every thread sees it after the next
         // CTA barrier and leaves the loop there, so no extra barrier is spent on it.
         if (!mbar_wait(bar_tma, (uint32_t)(iter & 1))) atomicOr(unsafe, 2);
         ++tma_consumed;
         // ---------------- phase A: decay prefix sums and scaled operands
-        PHASE(1);
         if (valid < kL) {
             // Last, partial chunk: turn the rows past the end into no-op tokens
             // (w = -inf gives a log-decay of -0, every other vector is zero).
@@ -420,7 +396,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         // that left here would keep its successors waiting for a state.
         if (K > 1 ? (*unsafe & 2) : *unsafe) { failed = true; break; }
         // ---------------- M1: G = [At;Rt] [Bh;Kh]^T
-        PHASE(3);
         if (tid == 0) {
             tc_fence_after();
             mma_k64<128, 128, 128>(tmem + kColG, dAR, dBK, false);
@@ -436,7 +411,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         mma_phase ^= 1;
         tc_fence_after();
         // ---------------- hop 1: G -> masked A_ab (fp32 scratch), A_ak, A_rb, A_rk (tf32 tiles)
-        PHASE(4);
         {
             const bool upper = quarter >= 2;          // Rt rows: inclusive lower triangle
             const int t = (quarter & 1) * 32 + lane;
@@ -515,7 +489,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         // chain below.  16 x 16 blocks by forward substitution in fp32 (one column per thread);
         // with 32-token solve blocks two of them are then joined by all threads,
         // [[T_00, 0], [T_11 A_10 T_00, T_11]], which halves the dependent steps of the chain.
-        PHASE(5);
         if (tid >= 64 && tid < 128) {   // warps 2 and 3: warp 0 is busy issuing
             const int b = (tid - 64) >> 4, cc = tid & 15;
             const float *Ab = Am + (16 * b) * kPitchA;
@@ -591,7 +564,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         } else {
             // ---------------- T^T = I (I - A_ab)^-T by the same block substitution, before the state is
             // needed; the raw-tile region is refilled once the identity tile has been read.
-            PHASE(7);
             if (tid == 0) {
                 auto dep_commit = [&]() { umma_commit(bar_dep); };
                 auto dep_wait = [&]() {
@@ -626,7 +598,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
             if (!mbar_wait(bar_mma, mma_phase)) atomicOr(unsafe, 2);
             mma_phase ^= 1;
             tc_fence_after();
-            PHASE(8);
             // T^T (lane s, column t) -> rows t of the [T;A_rb] tile, replacing A_ab and the block inverses.
             // No debias factor here: the identity is exact as a TMEM operand, so the factor carried by
             // the block inverses and by A_ab has come through once, which is what U^T = X^T T^T needs.
@@ -645,7 +616,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         if constexpr (K > 1) {
             // ---------------- the state arrives from the previous CTA of the cluster (the very
             // first chunk of the chain starts from the initial state, staged above by rank 0)
-            PHASE(2);
             if (chunk > 0) {
                 if (!mbar_wait_cluster(bar_state, state_phase)) atomicOr(unsafe, 2);
                 state_phase ^= 1;
@@ -676,7 +646,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         // commit and a wait (MMAs with different accumulators are not guaranteed to execute
         // in issue order); MMAs that do not depend on the pending result are issued between
         // the commit and the wait so that the tensor core stays busy.
-        PHASE(6);
         if (tid == 0) {
             auto dep_commit = [&]() { umma_commit(bar_dep); };
             auto dep_wait = [&]() {
@@ -738,7 +707,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
         mma_phase ^= 1;
         tc_fence_after();
         // ---------------- hop: state update and y, by the 8 warps that own lanes 0..63
-        PHASE(11);
         if (quarter < 2) {
             uint32_t v[16];
             // SAVE: a snapshot leaves by TMA.  The thread's 16 values go into a staging tile in the
@@ -854,7 +822,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
                 }
             }
             if constexpr (kFullInv) {   // Y^T was issued after the state update and completes here
-                PHASE(9);
                 if (!mbar_wait(bar_y, y_phase)) atomicOr(unsafe, 2);
                 tc_fence_after();
                 tmem_ld16(tmem + lane_base + kColYT + cgrp * 16, yv);
@@ -888,7 +855,6 @@ wkv7_chunked_kernel(const __grid_constant__ TmaMaps maps, const float *s0,
     if (*unsafe) failed = true;   // also catches a flag raised during the last chunk
 
     // ---------------- epilogue
-    PHASE(12);
     if constexpr (SAVE || K == 1) {
         if (tid == 0) bulk_wait_group<0>();   // snapshot / y copies still in flight read this CTA's shared memory
     }
@@ -946,17 +912,6 @@ EncodeTiledFn encode_fn() {
 }
 
 }  // namespace
-
-#ifdef RWKV7_PHASE_CLOCKS
-extern "C" int rwkv7_debug_phase_clocks(long long *out16, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out16, g_phase_clocks, sizeof(long long) * 16);
-    if (e == cudaSuccess && reset) {
-        long long zero[16] = {};
-        e = cudaMemcpyToSymbol(g_phase_clocks, zero, sizeof(zero));
-    }
-    return (int)e;
-}
-#endif
 
 // ---- scratch that lives in the library image ----------------------------------------
 //
