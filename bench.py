@@ -378,6 +378,60 @@ def main():
                                    "algorithmic_bytes": obytes}
             del oin, oseq, os0, oy, oso, ows, ocall
 
+    # ---- configuration 4 as a configuration: heads sharded over the ranks -----------------
+    # 7B shape (H = 64 heads of 64, C = 4096), B = 4 sequences of T = 65 536 tokens.  One layer's WKV7
+    # call on this rank's heads (modules/time_mixer/mod.rs:187-198 makes one call per layer over
+    # [B,T,H,N]), the all-gather of the head-split y into [B,T,H,N] on every rank (C1), and the
+    # vocabulary-sharded LM head with the log-sum-exp combine over NCCL (C2) on a bounded number of rows.
+    # (The WKV7 call and the gather run here, before the tensor-core legs: after those the SM clock stays held down
+    # by the power cap for some tens of milliseconds, which a latency-bound kernel feels one to one.)
+    cfg4 = None
+    cfg4_run = world > 1 and 64 % world == 0 and not args.small and not args.no_cfg4
+    if cfg4_run:
+        from rwkv_rs_stable_b200 import dist as rdist4
+        torch.cuda.empty_cache()
+        B4, T4, H4 = 4, 65536, 64
+        bs, hs = rdist4.shard_ranges(B4, H4, world)[rank]
+        Bl4, Hl4 = bs.stop - bs.start, hs.stop - hs.start
+        in4 = workloads.wkv7_inputs(Bl4, T4, Hl4, 64, seed=400 + rank, dtype=torch.bfloat16, device=dev)
+        seq4 = pkg.Wkv7PretrainForwardInputs(*[in4[n] for n in "rwkvab"])
+        s04 = torch.zeros(Bl4, Hl4, 64, 64, device=dev)
+        y4, so4 = torch.empty_like(in4["r"]), torch.empty_like(s04)
+        ws4_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bl4, T4, Hl4, 64, pkg.BF16))
+        ws4 = torch.empty(max(ws4_bytes, 1), dtype=torch.uint8, device=dev)
+        call4 = pkg.Wkv7StatepassCall(s04, seq4, y4, so4, ws4)
+
+        def timed_all(fn, reps):
+            fn()
+            sync_all()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(reps):
+                r_ = fn()
+            b_.record()
+            sync_all()
+            t_ = torch.tensor([a_.elapsed_time(b_) / reps], device=dev, dtype=torch.float64)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            return float(t_.item()), r_
+
+        wkv4_ms, _ = timed_all(call4, 3)
+        gather_ms, full4 = timed_all(lambda: rdist4.gather_outputs(y4, B4, H4), 2)
+        gather_ok = bool(torch.equal(full4[bs, :, hs], y4))
+        # every rank's slot must hold that rank's tensor: compare a checksum of each slot with its owner's
+        sums = torch.stack([full4[b_, :, h_].float().sum() for b_, h_ in rdist4.shard_ranges(B4, H4, world)])
+        own = torch.zeros(world, device=dev)
+        own[rank] = y4.float().sum()
+        dist.all_reduce(own)
+        gather_ok = gather_ok and bool(torch.equal(sums, own))
+        okt = torch.tensor([1.0 if gather_ok else 0.0], device=dev)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        gather_ok = bool(okt.item() == 1.0)
+        y_bytes = B4 * T4 * H4 * 64 * 2
+        del full4, in4, seq4, y4, call4, s04, so4, ws4
+        torch.cuda.empty_cache()
+        if not gather_ok:
+            raise SystemExit("cfg4 leg: the gathered y differs from the rank-local shards")
+
     # ---- training forward (with saved tensors) and backward at configuration 1 ------------
     train = None
     if not args.no_train and rank == 0:
@@ -669,54 +723,9 @@ def main():
                          "output_abs_mean": float(cout.float().abs().mean().item())}
         del cx, ckw, cvw, cws, cout
 
-    # ---- configuration 4 as a configuration: heads sharded over the ranks -----------------
-    # 7B shape (H = 64 heads of 64, C = 4096), B = 4 sequences of T = 65 536 tokens.  One layer's WKV7
-    # call on this rank's heads (modules/time_mixer/mod.rs:187-198 makes one call per layer over
-    # [B,T,H,N]), the all-gather of the head-split y into [B,T,H,N] on every rank (C1), and the
-    # vocabulary-sharded LM head with the log-sum-exp combine over NCCL (C2) on a bounded number of rows.
-    cfg4 = None
-    if world > 1 and 64 % world == 0 and not args.small and not args.no_cfg4:
+    # ---- configuration 4, second part: the vocabulary-sharded LM head (C2 on NCCL) ---------
+    if cfg4_run:
         from rwkv_rs_stable_b200 import dist as rdist4
-        torch.cuda.empty_cache()
-        B4, T4, H4 = 4, 65536, 64
-        bs, hs = rdist4.shard_ranges(B4, H4, world)[rank]
-        Bl4, Hl4 = bs.stop - bs.start, hs.stop - hs.start
-        in4 = workloads.wkv7_inputs(Bl4, T4, Hl4, 64, seed=400 + rank, dtype=torch.bfloat16, device=dev)
-        seq4 = pkg.Wkv7PretrainForwardInputs(*[in4[n] for n in "rwkvab"])
-        s04 = torch.zeros(Bl4, Hl4, 64, 64, device=dev)
-        y4, so4 = torch.empty_like(in4["r"]), torch.empty_like(s04)
-        ws4_bytes = int(pkg.lib().rwkv7_wkv7_workspace_bytes(Bl4, T4, Hl4, 64, pkg.BF16))
-        ws4 = torch.empty(max(ws4_bytes, 1), dtype=torch.uint8, device=dev)
-        call4 = pkg.Wkv7StatepassCall(s04, seq4, y4, so4, ws4)
-
-        def timed_all(fn, reps):
-            fn()
-            sync_all()
-            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a_.record()
-            for _ in range(reps):
-                r_ = fn()
-            b_.record()
-            sync_all()
-            t_ = torch.tensor([a_.elapsed_time(b_) / reps], device=dev, dtype=torch.float64)
-            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-            return float(t_.item()), r_
-
-        wkv4_ms, _ = timed_all(call4, 3)
-        gather_ms, full4 = timed_all(lambda: rdist4.gather_outputs(y4, B4, H4), 2)
-        gather_ok = bool(torch.equal(full4[bs, :, hs], y4))
-        # every rank's slot must hold that rank's tensor: compare a checksum of each slot with its owner's
-        sums = torch.stack([full4[b_, :, h_].float().sum() for b_, h_ in rdist4.shard_ranges(B4, H4, world)])
-        own = torch.zeros(world, device=dev)
-        own[rank] = y4.float().sum()
-        dist.all_reduce(own)
-        gather_ok = gather_ok and bool(torch.equal(sums, own))
-        okt = torch.tensor([1.0 if gather_ok else 0.0], device=dev)
-        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
-        gather_ok = bool(okt.item() == 1.0)
-        y_bytes = B4 * T4 * H4 * 64 * 2
-        del full4, in4, seq4, y4, call4
-        torch.cuda.empty_cache()
         R4, C4, V4 = 32768, 4096, 65536
         x4, _, t4 = workloads.lm_head_inputs(R4, C4, 8, seed=4, device=dev)        # same rows on every rank
         t4 = torch.randint(0, V4, (R4,), generator=torch.Generator(device=dev).manual_seed(44), device=dev)
@@ -740,7 +749,7 @@ def main():
                 "wkv7_gb_per_s": wkv4_bytes / (wkv4_ms * 1e-3) / 1e9,
                 "wkv7_frac_of_hbm_peak": wkv4_bytes / (wkv4_ms * 1e-3) / 1e9 / (peak4 * world),
                 "wkv7_hbm_roof_ms": wkv4_bytes / (peak4 * world * 1e9) * 1e3,
-                "gather": "NCCL all-gather of the head-split y into [B,T,H,N] on every rank + one strided copy per rank",
+                "gather": "NCCL all-gather of the head-split y into [world,B,T,H_loc,N] on every rank + one strided copy into [B,T,H,N]",
                 "gather_ms": gather_ms, "gather_bytes_full_tensor": y_bytes,
                 "gather_bus_gb_per_s": y_bytes * (world - 1) / world / (gather_ms * 1e-3) / 1e9,
                 "gather_checked": gather_ok,
@@ -750,10 +759,9 @@ def main():
                 "lm_head_frac_of_bf16_peak": lm4_flops / (lm4_ms * 1e-3) / 1e12 / (tfp4 * world),
                 "lm_head_frac_of_bf16_sustained_peak": lm4_flops / (lm4_ms * 1e-3) / 1e12 / (sustained_tflops() * world),
                 "lm_head_mean_loss": float(loss4.mean().item())}
-        if not gather_ok:
-            raise SystemExit("cfg4 leg: the gathered y differs from the rank-local shards")
-        del x4, w4, t4, s04, so4, ws4
+        del x4, w4, t4
         torch.cuda.empty_cache()
+
 
     if world > 1:
         dist.barrier()

@@ -35,8 +35,8 @@ def gather_outputs(y_local: torch.Tensor, B: int, H: int, group=None) -> torch.T
     """All-gathers the per-rank y shards (``[B_loc, T, H_loc, N]``, cut as :func:`shard_ranges`
     cuts them) into the full ``[B, T, H, N]`` tensor on every rank.  Only for consumers that
     need the whole tensor; the WKV7 path itself never calls it.  A batch split is one
-    all-gather into place; a head split gathers ``[world, B_loc, T, H_loc, N]`` and scatters
-    the head blocks into their slots with one strided copy per rank."""
+    all-gather into place; a head split gathers ``[world, B_loc, T, H_loc, N]`` and moves the
+    head blocks into their slots with one strided copy (whole-head shards) or one per rank."""
     world = dist.get_world_size(group)
     ranges = shard_ranges(B, H, world)
     T, N = y_local.shape[1], y_local.shape[3]
@@ -45,6 +45,9 @@ def gather_outputs(y_local: torch.Tensor, B: int, H: int, group=None) -> torch.T
     if ranges[0][1] == slice(0, H):      # whole-batch shards: the gather already is [B, T, H, N]
         return gathered.view(B, T, H, N)
     full = torch.empty((B, T, H, N), dtype=y_local.dtype, device=y_local.device)
+    if ranges[0][0] == slice(0, B):      # whole-head shards: one strided copy [world,B,T,H_loc,N] -> [B,T,world,H_loc,N]
+        full.view(B, T, world, H // world, N).copy_(gathered.permute(1, 2, 0, 3, 4))
+        return full
     for r, (bs, hs) in enumerate(ranges):
         full[bs, :, hs] = gathered[r]
     return full
