@@ -138,7 +138,7 @@ def set_wkv7_cluster(cluster_size: int) -> None:
 def set_wkv7_overlap(on: bool) -> None:
     """``rwkv7_set_wkv7_overlap``: scans of the two-kernel prefill beside the next segment's operator kernel
     on the library's second stream (default) or everything on the caller's stream."""
-    _check(lib().rwkv7_set_wkv7_overlap(1 if on else 0))
+    _check(lib().rwkv7_set_wkv7_overlap(int(on)))
 
 
 def get_wkv7_path() -> int:

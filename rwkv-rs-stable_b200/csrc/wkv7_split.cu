@@ -1120,22 +1120,30 @@ WorkspaceLayout layout_for(size_t chains, size_t seg, int buffers) {
 
 // How a call is cut: the number of segments that balances the scan of the last segment (which nothing
 // overlaps) against the few microseconds a segment boundary costs, within the operator budget.
-// The operator kernel's CTAs are persistent and fill every SM twice over, so the scan only finds room if
-// the operator kernel leaves it one place per chain: 2 * SMs - chains CTAs instead of 2 * SMs.  That costs
-// the operator kernel chains / (2 * SMs) of its throughput, and a scan CTA that shares its SM with an
-// operator CTA takes about 1.3 us per chunk instead of 0.95 us.  Measured (B200, 148 SMs): 32 chains x 1024
-// chunks 1.39 ms overlapped against 1.68 ms in sequence; 32 chains x 128 chunks 257 against 236 us (segments
-// of 26 chunks give the operator kernel 3.2 chunks per CTA: a fourth round for 0.2 rounds of work); 96 chains
-// x 64 chunks 301 against 247 us.  Hence: at most half as many chains as SMs, and at least 256 chunks.
+//
+// When the scan of a segment may run beside the operator kernel of the next one.  The scan is one latency-bound
+// CTA per chain (0.7 us per chunk with an SM to itself), the operator kernel throughput work that fills every SM
+// twice over (8.7 us per chunk and CTA): with x = chains x 8.7 / (2 SMs x 0.7) the two in sequence take (x + 1)
+// scan times.  On SM partitions (the scans on `chains` SMs rounded up to eight, the operator kernel on the rest)
+// they take max(x SMs / (SMs - R), 1): a gain while x SMs / (SMs - R) < x + 1, which on 148 SMs is up to about
+// 40 chains.  Measured (B200, 148 SMs; in sequence / on partitions, us): 12 chains x 1024 chunks 945 / 799;
+// 32 x 1024 1489 / 1336; 64 x 512 1195 / 1638.  Without partitions the scan CTAs sit beside operator CTAs (the
+// operator kernel then launches 2 SMs - chains CTAs) and run at half their pace: 32 x 1024 1381-1411, but 12 x 1024
+// 1204 and 64 x 512 1424, both worse than in sequence; that schedule is kept for 24 to 40 chains where the driver
+// offers no partitions.  Short sequences do not pay either way (32 chains x 128 chunks 257 against 236 us: the
+// first operator kernel and the last scan overlap nothing).  Hence: at most 27 % as many chains as SMs, at least
+// 256 chunks.
 bool overlap_applies(size_t chains, size_t nchunks, int num_sms) {
-    return wkv7_split_overlap() != 0 && num_sms > 0 && 2 * chains <= (size_t)num_sms && nchunks >= 256;
+    return wkv7_split_overlap() != 0 && num_sms > 0 && chains * 100 <= (size_t)num_sms * 27 && nchunks >= 256;
 }
+// (the schedule beside operator CTAs, where partitions are not to be had)
+bool shared_sm_overlap_pays(size_t chains, int num_sms) { return chains * 100 >= (size_t)num_sms * 16; }
 
 size_t preferred_segment(size_t chains, size_t nchunks, bool overlap) {
     size_t seg = nchunks;
     if (overlap) {
         size_t nseg = 1;
-        while ((nseg + 1) * (nseg + 1) * 4 <= nchunks && nseg < 32) ++nseg;   // about sqrt(nchunks / 4)
+        while ((nseg + 1) * (nseg + 1) * 16 <= nchunks && nseg < 32) ++nseg;   // about sqrt(nchunks / 16): measured best (1024 chunks: 8 segments)
         seg = (nchunks + nseg - 1) / nseg;
     }
     const size_t per_chunk = chains * kOperatorBytes * (overlap ? 2 : 1);
@@ -1170,12 +1178,107 @@ DeviceStreams *device_streams(int device) {
     return &d;
 }
 
+// ---- SM partitions (green contexts) for the overlapped schedule ----------------------------------
+// The scan of a segment and the operator kernel of the next one want different things from an SM: a scan CTA is
+// one latency-bound chain that must not be slowed down, an operator CTA is throughput work.  Sharing SMs (a scan
+// CTA beside an operator CTA) costs the scan about half its pace.  Where the driver offers it, the device's SMs
+// are therefore split once into two partitions, each with a stream of its own: the scans run two to an SM on
+// the small one, the operator kernels two to an SM on the rest, and neither sees the other's CTAs.
+struct GreenApi {
+    CUresult (*deviceGet)(CUdevice *, int) = nullptr;
+    CUresult (*getRes)(CUdevice, CUdevResource *, CUdevResourceType) = nullptr;
+    CUresult (*split)(CUdevResource *, unsigned int *, const CUdevResource *, CUdevResource *, unsigned int, unsigned int) = nullptr;
+    CUresult (*genDesc)(CUdevResourceDesc *, CUdevResource *, unsigned int) = nullptr;
+    CUresult (*create)(CUgreenCtx *, CUdevResourceDesc, CUdevice, unsigned int) = nullptr;
+    CUresult (*streamCreate)(CUstream *, CUgreenCtx, unsigned int, int) = nullptr;
+    CUresult (*ctxFromGreen)(CUcontext *, CUgreenCtx) = nullptr;
+    CUresult (*ctxPush)(CUcontext) = nullptr;
+    CUresult (*ctxPop)(CUcontext *) = nullptr;
+    bool ok = false;
+};
+
+const GreenApi &green_api() {
+    static GreenApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        auto get = [](const char *name, void **out) {
+            cudaDriverEntryPointQueryResult q;
+            return cudaGetDriverEntryPoint(name, out, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess &&
+                   *out != nullptr;
+        };
+        api.ok = get("cuDeviceGet", reinterpret_cast<void **>(&api.deviceGet)) &&
+                 get("cuDeviceGetDevResource", reinterpret_cast<void **>(&api.getRes)) &&
+                 get("cuDevSmResourceSplitByCount", reinterpret_cast<void **>(&api.split)) &&
+                 get("cuDevResourceGenerateDesc", reinterpret_cast<void **>(&api.genDesc)) &&
+                 get("cuGreenCtxCreate", reinterpret_cast<void **>(&api.create)) &&
+                 get("cuGreenCtxStreamCreate", reinterpret_cast<void **>(&api.streamCreate)) &&
+                 get("cuCtxFromGreenCtx", reinterpret_cast<void **>(&api.ctxFromGreen)) &&
+                 get("cuCtxPushCurrent", reinterpret_cast<void **>(&api.ctxPush)) &&
+                 get("cuCtxPopCurrent", reinterpret_cast<void **>(&api.ctxPop));
+        (void)cudaGetLastError();
+    });
+    return api;
+}
+
+struct DevicePartition {
+    int scan_sms = 0, op_sms = 0;          // SMs of the two partitions as the driver cut them
+    cudaStream_t scan_stream = nullptr, op_stream = nullptr;
+    // (an event is recorded only on a stream of the context it was created in; waits may cross contexts)
+    cudaEvent_t built[2] = {nullptr, nullptr}, scanned[2] = {nullptr, nullptr};
+    bool tried = false, ok = false;
+};
+
+// per device, per size of the scan partition in units of eight SMs (the granularity of a split)
+DevicePartition g_partitions[64][10];
+
+// (the caller holds g_streams_mu and has made `device` current)  Null when the driver does not offer it.
+DevicePartition *device_partition(int device, int want_scan_sms, int num_sms) {
+    const GreenApi &api = green_api();
+    const int slot = (want_scan_sms + 7) / 8;
+    if (!api.ok || device < 0 || device >= 64 || slot < 1 || slot >= 10) return nullptr;
+    DevicePartition &d = g_partitions[device][slot];
+    if (d.tried) return d.ok ? &d : nullptr;
+    d.tried = true;
+    CUdevice dev;
+    CUdevResource all, scan_res, op_res;
+    unsigned int nb = 1;
+    if (api.deviceGet(&dev, device) != CUDA_SUCCESS) return nullptr;
+    if (api.getRes(dev, &all, CU_DEV_RESOURCE_TYPE_SM) != CUDA_SUCCESS) return nullptr;
+    if (api.split(&scan_res, &nb, &all, &op_res, 0, (unsigned int)(slot * 8)) != CUDA_SUCCESS || nb != 1) return nullptr;
+    d.scan_sms = (int)scan_res.sm.smCount;
+    d.op_sms = (int)op_res.sm.smCount;
+    if (d.scan_sms < want_scan_sms || d.op_sms < num_sms / 2) return nullptr;
+    int least = 0, greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
+    struct Half { CUdevResource *res; cudaStream_t *stream; cudaEvent_t *events; int priority; };
+    const Half halves[2] = {{&scan_res, &d.scan_stream, d.scanned, greatest}, {&op_res, &d.op_stream, d.built, least}};
+    for (const Half &h : halves) {
+        CUdevResourceDesc desc;
+        CUgreenCtx green;
+        CUcontext ctx, popped;
+        CUstream st;
+        if (api.genDesc(&desc, h.res, 1) != CUDA_SUCCESS) return nullptr;
+        if (api.create(&green, desc, dev, CU_GREEN_CTX_DEFAULT_STREAM) != CUDA_SUCCESS) return nullptr;
+        if (api.streamCreate(&st, green, CU_STREAM_NON_BLOCKING, h.priority) != CUDA_SUCCESS) return nullptr;
+        *h.stream = reinterpret_cast<cudaStream_t>(st);
+        if (api.ctxFromGreen(&ctx, green) != CUDA_SUCCESS || api.ctxPush(ctx) != CUDA_SUCCESS) return nullptr;
+        bool made = true;
+        for (int i = 0; i < 2; ++i) made = made && cudaEventCreateWithFlags(&h.events[i], cudaEventDisableTiming) == cudaSuccess;
+        api.ctxPop(&popped);
+        if (!made) return nullptr;
+    }
+    d.ok = true;
+    return &d;
+}
+
 std::atomic<int> g_split_overlap{1};
 
 }  // namespace
 
 int wkv7_split_overlap() { return g_split_overlap.load(); }
-void wkv7_set_split_overlap(int on) { g_split_overlap.store(on ? 1 : 0); }
+// 0: everything on the caller's stream; 1: overlapped, on SM partitions where the driver offers them;
+// 2: overlapped on the second stream without partitions.
+void wkv7_set_split_overlap(int on) { g_split_overlap.store(on < 0 || on > 2 ? 1 : on); }
 
 size_t wkv7_split_min_workspace_bytes(int64_t B, int64_t T, int64_t H, int64_t N) {
     (void)T;
@@ -1209,6 +1312,15 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     // length, else one buffer with the longest segment that fits.
     // (fp32 tensors: one operator CTA per SM and the three-stage scan, which does not fit beside it)
     bool overlap = p.bf16 && overlap_applies(chains, (size_t)nchunks, p.num_sms);
+    // The second stream and its events, or the two SM partitions with theirs, are shared by all calls on a device:
+    // the enqueueing of an overlapped call is serialised per process from here on.
+    std::unique_lock<std::mutex> lock(g_streams_mu, std::defer_lock);
+    DevicePartition *part = nullptr;
+    if (overlap) {
+        lock.lock();
+        if (wkv7_split_overlap() == 1) part = device_partition(p.device, (int)chains, p.num_sms);
+        if (part == nullptr && !shared_sm_overlap_pays(chains, p.num_sms)) overlap = false;
+    }
     size_t seg = preferred_segment(chains, (size_t)nchunks, overlap);
     const size_t fixed = fixed_part(chains);
     if (workspace_bytes < fixed) return (int)cudaErrorInvalidValue;
@@ -1269,8 +1381,11 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     const size_t smem1 = p.bf16 ? kSmem1 : kSmem1F32;
     cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (e != cudaSuccess) return (int)e;
-    // Beside an operator CTA only the two-stage scan fits on an SM; it is also the one for more chains than SMs.
-    const bool small_scan = overlap || (int64_t)chains > (int64_t)p.num_sms;
+    if (!overlap) part = nullptr;
+    cudaStream_t op_stream = part ? part->op_stream : stream;
+    // Beside an operator CTA only the two-stage scan fits; it is also the one for more chains than SMs.  On its own
+    // partition a scan CTA has an SM to itself.
+    const bool small_scan = (overlap && part == nullptr) || (int64_t)chains > (int64_t)p.num_sms;
     auto launch_scan = [&](cudaStream_t st, int buf, const float *s_in, float *s_out, int c0, int n, int check) -> cudaError_t {
         const unsigned char *ops = ws + lay.operators[buf];
         const float *vecs = reinterpret_cast<const float *>(ws + lay.vectors[buf]);
@@ -1300,10 +1415,12 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     };
     auto launch_operators = [&](int buf, int segment, int c0, int n) -> cudaError_t {
         const long long units = (long long)chains * n;
-        const long long places = (p.bf16 ? 2LL : 1LL) * p.num_sms - (overlap ? (long long)chains : 0);   // (see overlap_applies)
+        // (see overlap_applies; on its own partition the kernel fills every SM it has twice over)
+        const long long places = part ? 2LL * part->op_sms
+                                      : (p.bf16 ? 2LL : 1LL) * p.num_sms - (overlap ? (long long)chains : 0);
         const unsigned grid = (unsigned)(units < places ? units : places);
         // (the operator of (chain, chunk) sits at index chain * n + chunk - c0 of the buffer in both kernels)
-        k1<<<grid, kThreads1, smem1, stream>>>(omaps, ws + lay.operators[buf], reinterpret_cast<float *>(ws + lay.vectors[buf]),
+        k1<<<grid, kThreads1, smem1, op_stream>>>(omaps, ws + lay.operators[buf], reinterpret_cast<float *>(ws + lay.vectors[buf]),
                                                 flags, (int)p.T, (int)p.H, c0, n, (int)chains, counters + segment, status);
         count_launch();
         return cudaGetLastError();
@@ -1324,35 +1441,37 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
         }
         return 0;
     }
-    // Overlapped: operator kernels on the caller's stream, scans on the device's second (high-priority)
-    // stream; events order a scan after its operators, and an operator kernel after the scan that last
-    // read the buffer it is about to overwrite.  The enqueueing is serialised per process: the second
-    // stream and the events are shared by all calls on a device.
-    std::lock_guard<std::mutex> lock(g_streams_mu);
+    // Overlapped: operator kernels on the caller's stream (or the stream of the operator partition), scans on the
+    // device's second, high-priority stream (or the stream of the scan partition); events order a scan after its
+    // operators, and an operator kernel after the scan that last read the buffer it is about to overwrite.
     DeviceStreams *ds = device_streams(p.device);
     if (ds == nullptr) return (int)cudaErrorUnknown;
+    cudaStream_t scan_stream = part ? part->scan_stream : ds->side;
+    cudaEvent_t *built = part ? part->built : ds->built, *scanned = part ? part->scanned : ds->scanned;
     e = cudaEventRecord(ds->fork, stream);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(ds->side, ds->fork, 0);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(scan_stream, ds->fork, 0);
+    if (e == cudaSuccess && part) e = cudaStreamWaitEvent(op_stream, ds->fork, 0);
     if (e != cudaSuccess) return (int)e;
     int segment = 0;
     for (int c0 = 0; c0 < nchunks; c0 += (int)seg, ++segment) {
         const int n = (int)((size_t)(nchunks - c0) < seg ? (size_t)(nchunks - c0) : seg);
         const int buf = segment & 1;
         if (segment >= 2) {
-            e = cudaStreamWaitEvent(stream, ds->scanned[buf], 0);
+            e = cudaStreamWaitEvent(op_stream, scanned[buf], 0);
             if (e != cudaSuccess) return (int)e;
         }
         e = launch_operators(buf, segment, c0, n);
-        if (e == cudaSuccess) e = cudaEventRecord(ds->built[buf], stream);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(ds->side, ds->built[buf], 0);
+        if (e == cudaSuccess) e = cudaEventRecord(built[buf], op_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(scan_stream, built[buf], 0);
         if (e != cudaSuccess) return (int)e;
         const bool first = c0 == 0, last = c0 + n >= nchunks;
-        e = launch_scan(ds->side, buf, first ? p.s0 : carry, last ? p.s_out : carry, c0, n, last ? 1 : 0);
-        if (e == cudaSuccess) e = cudaEventRecord(ds->scanned[buf], ds->side);
+        e = launch_scan(scan_stream, buf, first ? p.s0 : carry, last ? p.s_out : carry, c0, n, last ? 1 : 0);
+        if (e == cudaSuccess) e = cudaEventRecord(scanned[buf], scan_stream);
         if (e != cudaSuccess) return (int)e;
     }
-    // join: the caller's stream continues after the last scan (scans run in order on their stream)
-    e = cudaStreamWaitEvent(stream, ds->scanned[(segment - 1) & 1], 0);
+    // join: the caller's stream continues after the last scan (scans run in order on their stream, and every
+    // operator kernel is ordered before the scan of its segment)
+    e = cudaStreamWaitEvent(stream, scanned[(segment - 1) & 1], 0);
     return (int)e;
 }
 

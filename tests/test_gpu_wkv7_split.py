@@ -202,15 +202,17 @@ def test_split_shard_equals_single(pkg, workloads, cuda):
 
 @pytest.mark.parametrize("alias", [False, True])
 def test_split_overlapped_scan_is_bitwise_the_serial_one(pkg, oracle, workloads, cuda, alias):
-    """Few chains and a long sequence: the call is cut into segments, and the scan of a segment runs on the
-    library's second stream beside the operator kernel of the next one.  Same kernels on the same data: the
+    """Few chains and a long sequence: the call is cut into segments, and the scan of a segment runs beside the
+    operator kernel of the next one, each on its own partition of the SMs.  Same kernels on the same data: the
     result must be bitwise that of the single-stream schedule, and both must match the oracle."""
     B, T, H = 1, 16384, 3
     inp = workloads.wkv7_inputs(B, T, H, 64, seed=81, dtype=torch.bfloat16, state="normal")
     y_ref, s_ref = _oracle(oracle, inp)
     before = pkg.kernel_launch_count()
     y1, s1 = _statepass(pkg, cuda, inp, pkg.WKV7_SPLIT, alias=alias)
-    assert pkg.kernel_launch_count() - before == 2 * 8 + 2      # 256 chunks in eight segments, then the two flagged-chain kernels
+    # 256 chunks in four segments, then the two flagged-chain kernels (one segment where the driver offers no SM partitions:
+    # with so few chains the schedule beside operator CTAs does not pay)
+    assert pkg.kernel_launch_count() - before in (2 * 4 + 2, 2 + 2)
     try:
         pkg.set_wkv7_overlap(False)
         before = pkg.kernel_launch_count()
