@@ -130,13 +130,17 @@ int rwkv7_get_wkv7_path(void);
  * the largest entry).  0 restores that automatic choice; 1, 2 or 4 force a cluster size for every
  * chain (1 makes results independent of how many chains a call holds).  Process-wide. */
 int rwkv7_set_wkv7_cluster(int cluster_size);
-/* The two-kernel prefill cuts a long call into segments of chunks.  With at most as many chains as SMs the
- * scan of a segment (one latency-bound CTA per chain) would leave most of the GPU idle, so it is enqueued on
- * a second, library-owned stream of the device and runs beside the operator kernel of the next segment;
- * events order the two streams and the caller's stream continues after the last scan, so the call keeps its
- * stream semantics.  The stream and five events per device are created on the first such call and kept
- * until the process exits; the enqueueing of overlapped calls is serialised per process.  0 puts every
- * kernel on the caller's stream instead (same results, bitwise).  Process-wide; default 1. */
+/* The two-kernel prefill cuts a long call into segments of chunks.  With few chains (at most 27 % as many as
+ * SMs) and at least 256 chunks, the scan of a segment (one latency-bound CTA per chain) runs beside the operator
+ * kernel of the next segment: the device's SMs are split once into two partitions (CUDA green contexts: the
+ * scans on as many SMs as chains, rounded up to eight, the operator kernels on the rest), each with a
+ * library-owned stream; events order the two streams and the caller's stream continues after the last scan, so
+ * the call keeps its stream semantics.  Where the driver offers no partitions, calls of 24 to 40 chains (on 148
+ * SMs) use a second stream of the primary context instead, the scan CTAs beside operator CTAs.  Partitions,
+ * streams and events are created per device on the first such call and kept until the process exits; the
+ * enqueueing of overlapped calls is serialised per process.  0 puts every kernel on the caller's stream (same
+ * results, bitwise), 1 is the schedule described (default), 2 forces the second-stream schedule without
+ * partitions.  Process-wide. */
 int rwkv7_set_wkv7_overlap(int on);
 /* Number of kernels this library has launched in this process (all devices,
  * all threads).  Benchmarks read it before and after a timed region. */
