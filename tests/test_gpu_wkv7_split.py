@@ -285,3 +285,25 @@ def test_split_fp32_automatic_choice_and_long_context(pkg, oracle, workloads, cu
     print(f"split fp32 long context: y {parity.headline(y, y_ref):.3e} state {parity.headline(s, s_ref):.3e}")
     parity.assert_close_f32(y, y_ref, 1e-3, "y")
     parity.assert_close_f32(s, s_ref, 1e-3, "state")
+
+
+def test_split_overlap_schedules_agree_bitwise(pkg, workloads, cuda):
+    """24 chains x 256 chunks: in sequence on the caller's stream (0), scans on their own SM partition beside the next
+    segment's operator kernel (1, the default), and the schedule without partitions, scan CTAs beside operator CTAs
+    (2): the same kernels' arithmetic on the same data, so y and the final state must agree bit for bit."""
+    inp = workloads.wkv7_inputs(1, 16384, 24, 64, seed=95, dtype=torch.bfloat16, device=cuda, state="normal")
+    seq = pkg.Wkv7PretrainForwardInputs(*[inp[n] for n in "rwkvab"])
+    outs = {}
+    try:
+        for mode in (0, 1, 2):
+            pkg.set_wkv7_overlap(mode)
+            before = pkg.kernel_launch_count()
+            o = pkg.wkv7_statepass_custom(inp["s0"], seq, reference_contract=False)
+            torch.cuda.synchronize()
+            outs[mode] = (o.output.clone(), o.next_state.clone(), pkg.kernel_launch_count() - before)
+            assert pkg.read_device_status(0) == 0
+    finally:
+        pkg.set_wkv7_overlap(1)
+    assert outs[0][2] == 2 + 2 and outs[2][2] == 2 * 4 + 2 and outs[1][2] in (2 * 4 + 2, 2 + 2)
+    for mode in (1, 2):
+        assert torch.equal(outs[mode][0], outs[0][0]) and torch.equal(outs[mode][1], outs[0][1])
