@@ -59,6 +59,10 @@ wkv7_decode_kernel(DecPtrs ptrs, const float *s0, T *__restrict__ y, float *s_ou
     const int tid = threadIdx.x;
     const int row0 = (tid / TPR) * R, c0 = (tid % TPR) * E;
 
+    // Launched with programmatic stream serialization: this grid's CTAs may take their places while the kernel
+    // before it on the stream (typically the previous layer's sweep) is still draining; nothing is read before
+    // that kernel has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float4 S[R][Q];
     if (s0 != nullptr) {
 #pragma unroll
@@ -74,6 +78,8 @@ wkv7_decode_kernel(DecPtrs ptrs, const float *s0, T *__restrict__ y, float *s_ou
             for (int m = 0; m < Q; ++m) S[rho][m] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 
+    // (this CTA's state loads are under way: the next kernel on the stream may start taking places)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int t = 0; t < Tlen; ++t) {
         const size_t o = (((size_t)bi * Tlen + t) * H + h) * kN;
         if (t > 0) __syncthreads();  // previous token's vectors fully consumed
@@ -146,15 +152,24 @@ wkv7_decode_kernel(DecPtrs ptrs, const float *s0, T *__restrict__ y, float *s_ou
 
 int launch_wkv7_decode(const Wkv7Args &p, cudaStream_t stream) {
     DecPtrs ptrs{{p.r, p.w, p.k, p.v, p.a, p.b}};
-    const unsigned grid = (unsigned)(p.B * p.H);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.B * p.H));
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
     if (p.bf16)
-        wkv7_decode_kernel<__nv_bfloat16, RWKV7_DECODE_ROWS><<<grid, 128, 0, stream>>>(ptrs, p.s0, reinterpret_cast<__nv_bfloat16 *>(p.y),
-                                                                    p.s_out, (int)p.T, (int)p.H);
+        e = cudaLaunchKernelEx(&cfg, wkv7_decode_kernel<__nv_bfloat16, RWKV7_DECODE_ROWS>, ptrs, p.s0,
+                               reinterpret_cast<__nv_bfloat16 *>(p.y), p.s_out, (int)p.T, (int)p.H);
     else
-        wkv7_decode_kernel<float, RWKV7_DECODE_ROWS><<<grid, 128, 0, stream>>>(ptrs, p.s0, reinterpret_cast<float *>(p.y), p.s_out,
-                                                            (int)p.T, (int)p.H);
-    count_launch();
-    return (int)cudaGetLastError();
+        e = cudaLaunchKernelEx(&cfg, wkv7_decode_kernel<float, RWKV7_DECODE_ROWS>, ptrs, p.s0, reinterpret_cast<float *>(p.y),
+                               p.s_out, (int)p.T, (int)p.H);
+    if (e == cudaSuccess) count_launch();
+    return (int)e;
 }
 
 }  // namespace rwkv7
