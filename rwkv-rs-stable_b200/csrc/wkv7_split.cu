@@ -37,6 +37,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <type_traits>
@@ -1235,7 +1236,13 @@ DevicePartition g_partitions[64][10];
 DevicePartition *device_partition(int device, int want_scan_sms, int num_sms) {
     const GreenApi &api = green_api();
     const int slot = (want_scan_sms + 7) / 8;
-    if (!api.ok || device < 0 || device >= 64 || slot < 1 || slot >= 10) return nullptr;
+    // A tool injected into the process (a profiler, a memory checker: they announce themselves through these
+    // variables) may not support kernels in green contexts: Nsight Compute 2025.2 fails to prepare them for
+    // profiling and ends the application.  Under such a tool the partitions are not used.
+    static const bool injected = std::getenv("CUDA_INJECTION64_PATH") != nullptr ||
+                                 std::getenv("NV_NSIGHT_INJECTION_PORT_BASE") != nullptr ||
+                                 std::getenv("NV_COMPUTE_PROFILER_PERFWORKS_DIR") != nullptr;
+    if (!api.ok || injected || device < 0 || device >= 64 || slot < 1 || slot >= 10) return nullptr;
     DevicePartition &d = g_partitions[device][slot];
     if (d.tried) return d.ok ? &d : nullptr;
     d.tried = true;
