@@ -135,7 +135,8 @@ int rwkv7_set_wkv7_cluster(int cluster_size);
  * kernel of the next segment: the device's SMs are split once into two partitions (CUDA green contexts: the
  * scans on as many SMs as chains, rounded up to eight, the operator kernels on the rest), each with a
  * library-owned stream; events order the two streams and the caller's stream continues after the last scan, so
- * the call keeps its stream semantics.  Where the driver offers no partitions, calls of 24 to 40 chains (on 148
+ * the call keeps its stream semantics.  Where the driver offers no partitions, or a profiler is injected into the
+ * process (Nsight Compute cannot profile kernels in green contexts), calls of 24 to 40 chains (on 148
  * SMs) use a second stream of the primary context instead, the scan CTAs beside operator CTAs.  Partitions,
  * streams and events are created per device on the first such call and kept until the process exits; the
  * enqueueing of overlapped calls is serialised per process.  0 puts every kernel on the caller's stream (same
