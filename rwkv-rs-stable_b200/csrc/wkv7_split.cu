@@ -1325,7 +1325,11 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
     DevicePartition *part = nullptr;
     if (overlap) {
         lock.lock();
-        if (wkv7_split_overlap() == 1) part = device_partition(p.device, (int)chains, p.num_sms);
+        // (a stream that is being captured into a graph stays within its own context: no partitions then)
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) capturing = cudaStreamCaptureStatusActive;
+        if (wkv7_split_overlap() == 1 && capturing == cudaStreamCaptureStatusNone)
+            part = device_partition(p.device, (int)chains, p.num_sms);
         if (part == nullptr && !shared_sm_overlap_pays(chains, p.num_sms)) overlap = false;
     }
     size_t seg = preferred_segment(chains, (size_t)nchunks, overlap);
