@@ -131,7 +131,7 @@ int rwkv7_get_wkv7_path(void);
  * chain (1 makes results independent of how many chains a call holds).  Process-wide. */
 int rwkv7_set_wkv7_cluster(int cluster_size);
 /* The two-kernel prefill cuts a long call into segments of chunks.  With few chains (at most 27 % as many as
- * SMs) and at least 256 chunks, the scan of a segment (one latency-bound CTA per chain) runs beside the operator
+ * SMs) and at least 192 chunks (128 with very few chains), the scan of a segment (one latency-bound CTA per chain) runs beside the operator
  * kernel of the next segment: the device's SMs are split once into two partitions (CUDA green contexts: the
  * scans on as many SMs as chains, rounded up to eight, the operator kernels on the rest), each with a
  * library-owned stream; events order the two streams and the caller's stream continues after the last scan, so

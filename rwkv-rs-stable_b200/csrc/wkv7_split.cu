@@ -1132,13 +1132,17 @@ WorkspaceLayout layout_for(size_t chains, size_t seg, int buffers) {
 // operator kernel then launches 2 SMs - chains CTAs) and run at half their pace: 32 x 1024 1381-1411, but 12 x 1024
 // 1204 and 64 x 512 1424, both worse than in sequence; that schedule is kept for 24 to 40 chains where the driver
 // offers no partitions.  Short sequences do not pay either way (32 chains x 128 chunks 257 against 236 us: the
-// first operator kernel and the last scan overlap nothing).  Hence: at most 27 % as many chains as SMs, at least
-// 256 chunks.
+// first operator kernel and the last scan overlap nothing; on partitions 32 x 128 216 against 207 us, but 24 x 192
+// 234 against 256 and 12 x 128 133 against 138).  Hence: at most 27 % as many chains as SMs and at least 192
+// chunks, or at most 11 % and at least 128.
 bool overlap_applies(size_t chains, size_t nchunks, int num_sms) {
-    return wkv7_split_overlap() != 0 && num_sms > 0 && chains * 100 <= (size_t)num_sms * 27 && nchunks >= 256;
+    return wkv7_split_overlap() != 0 && num_sms > 0 && chains * 100 <= (size_t)num_sms * 27 &&
+           (nchunks >= 192 || (nchunks >= 128 && chains * 100 <= (size_t)num_sms * 11));
 }
 // (the schedule beside operator CTAs, where partitions are not to be had)
-bool shared_sm_overlap_pays(size_t chains, int num_sms) { return chains * 100 >= (size_t)num_sms * 16; }
+bool shared_sm_overlap_pays(size_t chains, size_t nchunks, int num_sms) {
+    return chains * 100 >= (size_t)num_sms * 16 && nchunks >= 256;
+}
 
 size_t preferred_segment(size_t chains, size_t nchunks, bool overlap) {
     size_t seg = nchunks;
@@ -1330,7 +1334,7 @@ int launch_wkv7_split(const Wkv7Args &p, void *workspace, size_t workspace_bytes
         if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) capturing = cudaStreamCaptureStatusActive;
         if (wkv7_split_overlap() == 1 && capturing == cudaStreamCaptureStatusNone)
             part = device_partition(p.device, (int)chains, p.num_sms);
-        if (part == nullptr && !shared_sm_overlap_pays(chains, p.num_sms)) overlap = false;
+        if (part == nullptr && !shared_sm_overlap_pays(chains, (size_t)nchunks, p.num_sms)) overlap = false;
     }
     size_t seg = preferred_segment(chains, (size_t)nchunks, overlap);
     const size_t fixed = fixed_part(chains);
